@@ -1,0 +1,29 @@
+// Error reporting shared by every entry point of the C ABI. The reference ends
+// the process on a failed check (src/cpp/include/common.h:16-37: exit(1), or
+// cudaDeviceReset + abort); here a failure is a negative return code plus a
+// message kept per calling thread.
+#include "common.cuh"
+
+namespace cxg {
+
+static thread_local char g_last_error[512] = "";
+
+int set_error(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return CXG_OK;
+  return set_error(CXG_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+}  // namespace cxg
+
+extern "C" const char *cxg_last_error_string(void) { return cxg::g_last_error; }
+
+extern "C" int cxg_abi_version(void) { return 1; }

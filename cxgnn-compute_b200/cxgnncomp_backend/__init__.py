@@ -1,0 +1,399 @@
+"""Drop-in for the `cxgnncomp_backend` extension module of CxGNN-Compute.
+
+The reference builds this module with pybind11 (src/cpp/python_bindings/binding.cpp:122-130)
+around CUDA kernels that take `torch::Tensor`s. Here every function is a thin host-side
+wrapper: it checks the tensors, allocates the outputs with torch, and calls the matching
+entry point of `libcxgnn_b200.so` through its C ABI (include/cxgnn_b200.h) with raw device
+pointers on torch's current stream. Names, positional signatures and argument meaning are
+those of the reference, so code written against the reference imports this module unchanged.
+
+There is no CPU path: every function needs CUDA tensors and the compiled library, and
+raises when either is missing. A negative status from the library becomes a RuntimeError
+(the reference calls exit(1) or abort(), src/cpp/include/common.h:16-37).
+"""
+import ctypes
+import enum
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "..", "csrc", "libcxgnn_b200.so")
+
+CXG_F32, CXG_BF16 = 0, 1
+CXG_SUM, CXG_MEAN = 0, 1
+CXG_SPMM_ACCUMULATE = 1
+
+
+def _load():
+    path = os.path.abspath(_LIB_PATH)
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: build it with `python {os.path.join(os.path.dirname(path), 'build.py')}` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback for these operators.")
+    return ctypes.CDLL(path)
+
+
+_lib = _load()
+_vp, _i64, _i32, _u32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_uint32, ctypes.c_size_t
+
+
+class SpmmDesc(ctypes.Structure):
+    """Mirror of `cxg_spmm_desc`."""
+    _fields_ = [
+        ("ptr", _vp), ("idx", _vp), ("x", _vp), ("y", _vp), ("edge_val", _vp), ("edge_mask", _vp),
+        ("edge_rel", _vp), ("targets", _vp), ("n_dst", _i64), ("nnz", _i64), ("rel_stride", _i64),
+        ("feat", _i32), ("heads", _i32), ("dtype", _i32), ("ptr_bytes", _i32), ("idx_bytes", _i32),
+        ("reduce", _i32), ("flags", _u32), ("split_edges", _i32),
+    ]
+
+
+_lib.cxg_last_error_string.restype = ctypes.c_char_p
+_lib.cxg_abi_version.restype = ctypes.c_int
+
+
+def _sig(name, argtypes):
+    fn = getattr(_lib, name)
+    fn.argtypes = argtypes
+    fn.restype = ctypes.c_int
+    return fn
+
+
+_spmm_ws = _sig("cxg_spmm_csr_workspace_size", [_i64, _i64, _i32, _i32, _i32, ctypes.POINTER(_sz)])
+_spmm_fwd = _sig("cxg_spmm_csr", [ctypes.POINTER(SpmmDesc), _vp, _sz, _vp])
+_spmm_bwd = _sig("cxg_spmm_csr_backward", [ctypes.POINTER(SpmmDesc), _vp, _vp, _vp, _vp])
+
+
+def _check(rc, what):
+    if rc != 0:
+        msg = _lib.cxg_last_error_string().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed with status {rc}: {msg}")
+
+
+def _cuda(t, name, dtypes=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (this backend has no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtypes is not None and t.dtype not in dtypes:
+        raise RuntimeError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+    return t
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_FEAT_DTYPES = (torch.float32, torch.bfloat16)
+_INDEX_DTYPES = (torch.int64, torch.int32)
+_workspaces = {}
+
+# Rows with more edges than this are split into segments; 0 keeps the library default.
+# Tests lower it to exercise the split path on small graphs.
+SPLIT_EDGES = 0
+
+
+def _workspace(device, nbytes):
+    """Scratch buffer per (device, stream); grows on demand, contents never carry over."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _dtype_code(t):
+    return CXG_F32 if t.dtype == torch.float32 else CXG_BF16
+
+
+def _make_desc(ptr, idx, x, y, num_node, *, heads=1, feat=None, edge_val=None, edge_mask=None,
+               edge_rel=None, rel_stride=0, targets=None, reduce=CXG_SUM, accumulate=False):
+    _cuda(ptr, "ptr", _INDEX_DTYPES)
+    _cuda(idx, "idx", _INDEX_DTYPES)
+    d = SpmmDesc()
+    d.ptr, d.idx = ptr.data_ptr(), idx.data_ptr()
+    d.x = x.data_ptr() if x is not None else None
+    d.y = y.data_ptr() if y is not None else None
+    d.edge_val = edge_val.data_ptr() if edge_val is not None else None
+    d.edge_mask = edge_mask.data_ptr() if edge_mask is not None else None
+    d.edge_rel = edge_rel.data_ptr() if edge_rel is not None else None
+    d.targets = targets.data_ptr() if targets is not None else None
+    d.n_dst = int(num_node)
+    d.nnz = int(idx.shape[0])
+    d.rel_stride = int(rel_stride)
+    d.feat = int(feat)
+    d.heads = int(heads)
+    ref = x if x is not None else y
+    d.dtype = _dtype_code(ref)
+    d.ptr_bytes = ptr.element_size()
+    d.idx_bytes = idx.element_size()
+    d.reduce = reduce
+    d.flags = CXG_SPMM_ACCUMULATE if accumulate else 0
+    d.split_edges = SPLIT_EDGES
+    return d
+
+
+def _num_rows(ptr, num_node):
+    n = int(num_node)
+    if n <= 0:
+        n = ptr.shape[0] - 1  # "0 means all rows", src/cpp/src/aggr.cu:118
+    if n > ptr.shape[0] - 1:
+        raise RuntimeError(f"num_node {n} exceeds the {ptr.shape[0] - 1} rows of ptr")
+    return n
+
+
+def _run_spmm(desc, device):
+    need = _sz(0)
+    _check(_spmm_ws(desc.n_dst, desc.nnz, desc.feat, desc.heads, desc.split_edges, ctypes.byref(need)),
+           "cxg_spmm_csr_workspace_size")
+    ws = _workspace(device, need.value)
+    with torch.cuda.device(device):
+        _check(_spmm_fwd(ctypes.byref(desc), _p(ws), ws.numel(), _stream()), "cxg_spmm_csr")
+
+
+def _spmm_forward(x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, out=None, accumulate=False,
+                  edge_mask=None, edge_rel=None, rel_stride=0, targets=None):
+    """y = A x for the first `num_node` rows; x is [N_s, F] or [N_s, H, F]."""
+    _cuda(x, "x", _FEAT_DTYPES)
+    n = _num_rows(ptr, num_node)
+    heads = 1
+    if x.dim() == 3:
+        heads = x.shape[1]
+    elif x.dim() != 2:
+        raise RuntimeError("x must be [N, F] or [N, H, F]")
+    feat = x.shape[-1]
+    if edge_val is not None:
+        _cuda(edge_val, "edge_value", (torch.float32,))
+        ev_heads = edge_val.shape[1] if edge_val.dim() == 2 else 1
+        if ev_heads != heads and not (heads == 1 and ev_heads == 1):
+            raise RuntimeError(f"edge_value has {ev_heads} heads, x has {heads}")
+    if out is None:
+        shape = (n, heads, feat) if x.dim() == 3 else (n, feat)
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    desc = _make_desc(ptr, idx, x, out, n, heads=heads, feat=feat, edge_val=edge_val, edge_mask=edge_mask,
+                      edge_rel=edge_rel, rel_stride=rel_stride, targets=targets, reduce=reduce,
+                      accumulate=accumulate)
+    _run_spmm(desc, x.device)
+    return out
+
+
+def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, need_dx=True,
+                   need_dval=False, grad_x=None, edge_mask=None, edge_rel=None, rel_stride=0, targets=None,
+                   x_shape=None):
+    """Returns (dx fp32 or None, dval fp32 or None). `grad_x` is added into when given."""
+    grad_out = _cuda(grad_out.contiguous(), "grad_out", _FEAT_DTYPES)
+    n = _num_rows(ptr, num_node)
+    heads = grad_out.shape[1] if grad_out.dim() == 3 else 1
+    feat = grad_out.shape[-1]
+    if x_shape is None:
+        x_shape = x.shape
+    dx = None
+    if need_dx:
+        dx = grad_x if grad_x is not None else torch.zeros(x_shape, dtype=torch.float32, device=grad_out.device)
+        _cuda(dx, "grad_x", (torch.float32,))
+    dval = None
+    if need_dval:
+        dval = torch.zeros(edge_val.shape, dtype=torch.float32, device=grad_out.device)
+        if x.dtype != grad_out.dtype:
+            x = x.to(grad_out.dtype)
+    desc = _make_desc(ptr, idx, x if need_dval else None, None, n, heads=heads, feat=feat, edge_val=edge_val,
+                      edge_mask=edge_mask, edge_rel=edge_rel, rel_stride=rel_stride, targets=targets,
+                      reduce=reduce)
+    desc.dtype = _dtype_code(grad_out)
+    with torch.cuda.device(grad_out.device):
+        _check(_spmm_bwd(ctypes.byref(desc), _p(grad_out), _p(dx), _p(dval), _stream()),
+               "cxg_spmm_csr_backward")
+    return dx, dval
+
+
+# --------------------------------------------------------------------------------------
+# autograd-aware aggregation (reference: C++ torch::autograd::Function, src/cpp/include/aggr.h:13-33)
+# --------------------------------------------------------------------------------------
+class _SageFunction(torch.autograd.Function):
+    """SAGEFunction / SAGEEdgeValueFunction (src/cpp/src/aggr.cu:275-303).
+
+    The reference stashes raw device pointers of ptr/idx between forward and backward
+    (aggr.cu:116-117); the tensors themselves are saved here, so they cannot dangle.
+    """
+
+    @staticmethod
+    def forward(ctx, x, ptr, idx, edge_val, num_node, reduce):
+        ctx.num_node = num_node
+        ctx.reduce = reduce
+        ctx.save_for_backward(x, ptr, idx, edge_val if edge_val is not None else torch.empty(0))
+        ctx.has_val = edge_val is not None
+        return _spmm_forward(x, ptr, idx, num_node, edge_val=edge_val, reduce=reduce)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, ptr, idx, edge_val = ctx.saved_tensors
+        edge_val = edge_val if ctx.has_val else None
+        need_dx = ctx.needs_input_grad[0]
+        need_dval = ctx.has_val and ctx.needs_input_grad[3]
+        dx, dval = _spmm_backward(grad_out, x, ptr, idx, ctx.num_node, edge_val=edge_val, reduce=ctx.reduce,
+                                  need_dx=need_dx, need_dval=need_dval)
+        if dx is not None and dx.dtype != x.dtype:
+            dx = dx.to(x.dtype)
+        return dx, None, None, dval, None, None
+
+
+def sage_sum_forward(x, ptr, idx, num_node):
+    """out[r] = sum of x[idx[e]] over row r (binding.cpp:20, aggr.cu:390-393)."""
+    return _SageFunction.apply(x, ptr, idx, None, num_node, CXG_SUM)
+
+
+def sage_mean_forward(x, ptr, idx, num_node):
+    """out[r] = mean of x[idx[e]] over row r, 0 for empty rows (binding.cpp:19, aggr.cu:385-388)."""
+    return _SageFunction.apply(x, ptr, idx, None, num_node, CXG_MEAN)
+
+
+def sage_sum_forward_edge_value(x, ptr, idx, edge_value, num_node):
+    """out[r] = sum of edge_value[e] * x[idx[e]]; x [N,F] with value [E], or x [N,H,F] with value [E,H]
+    (binding.cpp:17, aggr.cu:377-383)."""
+    if edge_value.dim() == 2 and x.dim() == 2 and edge_value.shape[1] == 1:
+        edge_value = edge_value.reshape(-1)
+    return _SageFunction.apply(x, ptr, idx, edge_value, num_node, CXG_SUM)
+
+
+def sage_mean_forward_edge_value(x, ptr, idx, edge_value, num_node):
+    """The reference's kernel starts with assert(false) and its host code refuses the call
+    ("DO NOT use mean with edge value", aggr.cu:158,163); same refusal here."""
+    raise RuntimeError("sage_mean_forward_edge_value: DO NOT use mean with edge value")
+
+
+# --------------------------------------------------------------------------------------
+# raw SpMM family (no autograd), src/cpp/src/spmm_host.cu
+# --------------------------------------------------------------------------------------
+def run_spmm_configurable(ptr, idx, vin, num_node, grid_x=0, grid_y=0, block_x=0, block_y=0, rpb=0, cpb=0,
+                          cpw=0, grid_map=0, block_map=0):
+    """SpMM sum into a fresh [num_node, F] tensor (spmm_host.cu:6-55). The nine launch
+    parameters chosen by the reference's tuner are accepted and ignored: the kernel
+    picks its schedule from the row width and the degree of each row."""
+    if vin.dim() != 2:
+        raise RuntimeError("vin must be 2D")
+    return _spmm_forward(vin, ptr, idx, num_node)
+
+
+def run_spmm_configurable_int32(ptr, idx, vin, num_node, *tuner_args):
+    """int32 ptr/idx variant (spmm_host.cu:99-156)."""
+    _cuda(ptr, "ptr", (torch.int32,))
+    _cuda(idx, "idx", (torch.int32,))
+    return run_spmm_configurable(ptr, idx, vin, num_node)
+
+
+def run_spmm_configurable_bwd(ptr, idx, vin, grad_vout, num_node, *tuner_args):
+    """grad_vin = A^T grad_vout, shaped like vin (spmm_host.cu:57-97)."""
+    if grad_vout.dim() != 2:
+        raise RuntimeError("vin must be 2D")
+    dx, _ = _spmm_backward(grad_vout, vin, ptr, idx, num_node)
+    return dx if dx.dtype == vin.dtype else dx.to(vin.dtype)
+
+
+class SPMM_MULTIHEAD_SCHEDULE(enum.IntEnum):
+    """binding.cpp:58-62."""
+    Naive = 0
+    PreReduce = 1
+    Optimal = 2
+
+
+Naive = SPMM_MULTIHEAD_SCHEDULE.Naive
+PreReduce = SPMM_MULTIHEAD_SCHEDULE.PreReduce
+Optimal = SPMM_MULTIHEAD_SCHEDULE.Optimal
+
+
+def spmm_multihead(ptr, idx, val, vin, num_node, schedule=SPMM_MULTIHEAD_SCHEDULE.Optimal, block_size=256):
+    """Multi-head SpMM with per-(edge, head) values (spmm_host.cu:158-196).
+    Naive -> [num_node, H, F]; PreReduce / Optimal -> heads summed, [num_node, F]."""
+    if vin.dim() != 3:
+        raise RuntimeError("vin must be 3D, [num_node, num_head, feat_len]")
+    if val.dim() != 2:
+        raise RuntimeError("val must be 2D, [num_edge, num_head]")
+    if vin.shape[1] != val.shape[1]:
+        raise RuntimeError(f"num_head mismatch {vin.shape[1]} {val.shape[1]}")
+    out = _spmm_forward(vin, ptr, idx, num_node, edge_val=val)
+    if int(schedule) == int(SPMM_MULTIHEAD_SCHEDULE.Naive):
+        return out
+    return _head_sum(out)
+
+
+def _head_sum(out):
+    # Heads are added in head order with one fp32 accumulator per column.
+    acc = out[:, 0].float().clone()
+    for h in range(1, out.shape[1]):
+        acc += out[:, h].float()
+    return acc.to(out.dtype)
+
+
+def spmm_multihead_bwd(ptr, idx, val, grad_output, grad_x, num_node, schedule=SPMM_MULTIHEAD_SCHEDULE.Optimal,
+                       block_size=256):
+    """grad_x[idx[e], h, :] += val[e, h] * grad_output[r, h, :]  in place (spmm_host.cu:198-214)."""
+    _cuda(grad_x, "grad_x", (torch.float32,))
+    _spmm_backward(grad_output, None, ptr, idx, num_node, edge_val=val, grad_x=grad_x, x_shape=grad_x.shape)
+    return None
+
+
+def run_spmm_multihead_configurable(ptr, idx, val, vin, num_node, *tuner_args):
+    """Heads-summed multi-head SpMM, [num_node, F] (spmm_host.cu:216-256); tuner arguments ignored."""
+    return spmm_multihead(ptr, idx, val, vin, num_node, SPMM_MULTIHEAD_SCHEDULE.PreReduce)
+
+
+# --------------------------------------------------------------------------------------
+# masked / target-indexed / relational aggregation, accumulated INTO the caller's output
+# --------------------------------------------------------------------------------------
+def selective_aggr(x, ptr, idx, mask, out, num_node):
+    """out[r] += sum over the edges of row r whose mask is set (aggr.cu:478-492)."""
+    _cuda(mask, "mask", (torch.bool, torch.uint8))
+    _cuda(out, "out", (x.dtype,))
+    _spmm_forward(x, ptr, idx, num_node, out=out, accumulate=True, edge_mask=mask)
+
+
+def selective_aggr_bwd(grad_out, ptr, idx, mask, grad_x, num_center):
+    """grad_x[idx[e]] += grad_out[r] for the masked edges (aggr.cu:494-509)."""
+    _cuda(mask, "mask", (torch.bool, torch.uint8))
+    _spmm_backward(grad_out, None, ptr, idx, num_center, grad_x=grad_x, edge_mask=mask, x_shape=grad_x.shape)
+
+
+def target_aggr(x, ptr, idx, targets, out, num_node):
+    """out[targets[r]] += sum of x[idx[e]] over row r (aggr.cu:450-463). `targets` must not
+    repeat inside one call: each output row is owned by one group of lanes."""
+    _cuda(targets, "targets", (torch.int64,))
+    _cuda(out, "out", (x.dtype,))
+    _spmm_forward(x, ptr, idx, num_node, out=out, accumulate=True, targets=targets)
+
+
+def target_aggr_backward(grad_in, ptr, idx, targets, grad_out, num_node):
+    """grad_out[idx[e]] += grad_in[targets[r]] (aggr.cu:465-476)."""
+    _cuda(targets, "targets", (torch.int64,))
+    _spmm_backward(grad_in, None, ptr, idx, num_node, grad_x=grad_out, targets=targets, x_shape=grad_out.shape)
+
+
+class _AggrRelFunction(torch.autograd.Function):
+    """AggrRelFunction (src/cpp/src/rel_spmm.cu:37-135)."""
+
+    @staticmethod
+    def forward(ctx, x, ptr, idx, etype, num_node, num_rel):
+        ctx.save_for_backward(x, ptr, idx, etype)
+        ctx.num_node, ctx.num_rel = num_node, num_rel
+        stride = x.shape[0] // num_rel
+        return _spmm_forward(x, ptr, idx, num_node, edge_rel=etype, rel_stride=stride)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, ptr, idx, etype = ctx.saved_tensors
+        stride = x.shape[0] // ctx.num_rel
+        dx, _ = _spmm_backward(grad_out, x, ptr, idx, ctx.num_node, edge_rel=etype, rel_stride=stride)
+        return dx.to(x.dtype), None, None, None, None, None
+
+
+def aggr_rel(x, ptr, idx, etype, num_node, num_rel):
+    """out[r] = sum_e x[etype[e] * N + idx[e]] with x = [num_rel * N, F] already transformed per
+    relation; etype is int32 (binding.cpp:45, rel_spmm.cu:8-70)."""
+    _cuda(etype, "etype", (torch.int32,))
+    return _AggrRelFunction.apply(x, ptr, idx, etype, num_node, num_rel)

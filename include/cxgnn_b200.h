@@ -1,0 +1,140 @@
+/*
+ * cxgnn_b200.h — C ABI of libcxgnn_b200.so, the sm_100a aggregation engine that
+ * stands in for the kernels behind the `cxgnncomp_backend` extension module of
+ * CxGNN-Compute (src/cpp/python_bindings/binding.cpp:14-130).
+ *
+ * Conventions, all entry points:
+ *   - plain C, `extern "C"`; every pointer is a DEVICE pointer unless the
+ *     parameter name ends in `_host`;
+ *   - returns CXG_OK (0) or a negative CXG_E* code; never exits, aborts, resets
+ *     the device or throws; `cxg_last_error_string()` gives the reason for the
+ *     last failure on the calling thread;
+ *   - no allocation and no synchronisation: scratch memory is passed in by the
+ *     caller (`*_workspace_size` tells how much) and kernels are enqueued on
+ *     `stream` (a `cudaStream_t` passed as `void*`; NULL = the legacy default
+ *     stream, which is what the reference launches on);
+ *   - CSR_Layer graph format of the reference: `ptr[n_dst+1]`, `idx[nnz]`, row r
+ *     holds the source ids of destination r; features are row-major and
+ *     contiguous.
+ */
+#ifndef CXGNN_B200_H_
+#define CXGNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define CXG_OK 0
+#define CXG_EINVAL (-1)       /* bad size, flag or combination of arguments   */
+#define CXG_ENULL (-2)        /* a required pointer is NULL                   */
+#define CXG_EUNSUPPORTED (-3) /* valid request that this build does not cover */
+#define CXG_ECUDA (-4)        /* a CUDA call or kernel launch failed          */
+#define CXG_EWORKSPACE (-5)   /* workspace missing or too small               */
+#define CXG_ETIMEOUT (-6)     /* a bounded device-side wait ran out           */
+#define CXG_ELIMIT (-7)       /* size beyond a fixed limit of the entry point */
+
+/* ---- element types ------------------------------------------------------ */
+#define CXG_F32 0
+#define CXG_BF16 1
+
+/* ---- reductions ----------------------------------------------------------*/
+#define CXG_SUM 0
+#define CXG_MEAN 1
+
+/* ---- flags of cxg_spmm_csr ---------------------------------------------- */
+#define CXG_SPMM_ACCUMULATE 1u /* y[row] += result instead of y[row] = result */
+
+const char *cxg_last_error_string(void);
+int cxg_abi_version(void);
+
+/*
+ * Description of one CSR aggregation  y[t(r), h, :] (+)= red_{e in row r} v[e,h] * x[s(e), h, :]
+ * shared by the SpMM entry points below.
+ *
+ *   ptr        int64 (ptr_bytes 8) or int32 (ptr_bytes 4), n_dst+1 entries
+ *   idx        int64 (idx_bytes 8) or int32 (idx_bytes 4), source id per edge
+ *   x          [n_src, heads, feat]  dtype
+ *   y          [n_out, heads, feat]  dtype
+ *   edge_val   optional float32 [nnz, heads]; NULL = all ones
+ *   edge_mask  optional uint8/bool [nnz]; 0 = skip the edge          (selective_aggr)
+ *   edge_rel   optional int32 [nnz]; source row becomes rel*rel_stride + idx  (aggr_rel)
+ *   targets    optional int64 [n_dst]; output row of CSR row r; NULL = r      (target_aggr)
+ *   reduce     CXG_SUM or CXG_MEAN (mean divides by the row's edge count; rows
+ *              without edges give 0)
+ *
+ * Arithmetic: one fp32 accumulator per (row, column), edges added strictly in
+ * CSR order (fma when an edge value is given). Rows longer than the split
+ * threshold are cut into fixed segments whose partial sums are added in segment
+ * order, so results never depend on scheduling.
+ */
+typedef struct cxg_spmm_desc {
+  const void *ptr;
+  const void *idx;
+  const void *x;
+  void *y;
+  const float *edge_val;
+  const uint8_t *edge_mask;
+  const int32_t *edge_rel;
+  const int64_t *targets;
+  int64_t n_dst;
+  int64_t nnz;
+  int64_t rel_stride;
+  int32_t feat;
+  int32_t heads;
+  int32_t dtype;
+  int32_t ptr_bytes;
+  int32_t idx_bytes;
+  int32_t reduce;
+  uint32_t flags;
+  int32_t split_edges; /* rows with more edges are split; 0 = default (512) */
+} cxg_spmm_desc;
+
+/*
+ * Scratch bytes needed by cxg_spmm_csr for a graph with n_dst rows and nnz
+ * edges at row width heads*feat (split_edges as in the descriptor). Upper bound;
+ * depends on sizes only.
+ */
+int cxg_spmm_csr_workspace_size(int64_t n_dst, int64_t nnz, int32_t feat,
+                                int32_t heads, int32_t split_edges,
+                                size_t *bytes);
+
+/*
+ * CSR SpMM forward. Replaces, depending on the optional fields of `desc`:
+ *   sage_sum_forward / sage_mean_forward            src/cpp/src/aggr.cu:385-393
+ *   sage_sum_forward_edge_value (1 head / H heads)  src/cpp/src/aggr.cu:377-383
+ *   run_spmm_configurable{,_int32}                  src/cpp/src/spmm_host.cu:6-55,99-156
+ *   spmm_multihead, Naive schedule                  src/cpp/src/spmm_host.cu:158-181
+ *   selective_aggr                                  src/cpp/src/aggr.cu:478-492
+ *   target_aggr                                     src/cpp/src/aggr.cu:450-463
+ *   aggr_rel                                        src/cpp/src/rel_spmm.cu:37-70
+ * The workspace holds the split plan of long rows and their partial sums; it is
+ * rebuilt on every call and carries no state between calls.
+ */
+int cxg_spmm_csr(const cxg_spmm_desc *desc, void *workspace,
+                 size_t workspace_bytes, void *stream);
+
+/*
+ * CSR SpMM backward for the aggregation `desc` describes (desc->y is unused,
+ * desc->x is the forward input and only needed for dval):
+ *   dx[s(e),h,:]  += v[e,h] * dy[t(r),h,:]     (divided by the row's edge count for mean)
+ *   dval[e,h]      = <dy[t(r),h,:], x[s(e),h,:]>
+ * dy has desc->dtype; dx [n_src, heads, feat] and dval [nnz, heads] are float32,
+ * either may be NULL. dx is ADDED INTO, so the caller zero-fills it first (the
+ * reference does: torch::zeros_like, src/cpp/src/aggr.cu:196). The additions
+ * into dx are vector atomics whose order is not fixed, as in the reference.
+ * Replaces sageBackwardImpl (src/cpp/src/aggr.cu:189-273), run_spmm_configurable_bwd
+ * (src/cpp/src/spmm_host.cu:57-97), spmm_multihead_bwd (spmm_host.cu:198-214),
+ * selective_aggr_bwd / target_aggr_backward (aggr.cu:465-509) and aggr_rel's
+ * backward (src/cpp/src/rel_spmm.cu:106-135).
+ */
+int cxg_spmm_csr_backward(const cxg_spmm_desc *desc, const void *dy, float *dx,
+                          float *dval, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CXGNN_B200_H_ */
