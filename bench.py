@@ -1,0 +1,337 @@
+"""Benchmark of the aggregation hot path: one step = one CSR SpMM pass (sum) over the whole graph.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0). `value` is the whole-job algorithmic HBM throughput in GB/s:
+compulsory bytes of one pass (every touched feature row once in, every output row once out, the
+index stream, the row pointers) divided by the step time, inputs resident in HBM. `e2e` is the
+same metric through the `cxgnncomp_backend` call with the step's inputs copied from pinned host
+memory and its output copied back inside the timed region. `roofline` compares the SpMM call
+with the measured HBM copy bandwidth of this pool (MEASURED_PEAKS.json). `cpu_baseline` times the
+reference's CPU formulation (torch index_add_ / sparse.mm, all host threads) on a bounded row
+sample of the same workload.
+
+With N > 1 (torchrun, one rank per GPU) rows are split contiguously by edge count; every step each
+rank broadcasts its feature shard to all others over NCCL (the all-gather of the full-graph layer)
+and aggregates its own rows; total work is fixed ("strong" scaling).
+
+`--impl reference` times the reference's own CPU formulation only (rank 0), same metric and unit.
+Inputs are synthetic (seeded power-law graphs, N(0,1) features): the reference's datasets are not
+available offline.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "cxgnn-compute_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (nodes, undirected edges, feat, dtype, idx dtype, description)
+    "papers_like": (111_000_000, 744_500_000, 128, "bf16", "int32",
+                    "full-graph GCN aggregation, 111M nodes / 1.6B edges, F=128 bf16 (config 5)"),
+    "products_like": (2_449_029, 61_850_000, 128, "bf16", "int32",
+                      "2.45M nodes / 126M edges power-law graph, F=128 bf16 (graph of config 3)"),
+    "papers_tenth": (11_100_000, 74_450_000, 128, "bf16", "int32",
+                     "one tenth of config 5 (11.1M nodes / 160M edges, same mean degree), F=128 bf16: profiling case"),
+    "arxiv_like": (169_343, 1_081_572, 128, "f32", "int64",
+                   "GCN aggregation, 169,343 nodes / 2.33M edges, F=128 fp32 (config 1)"),
+}
+DTYPES = {"bf16": torch.bfloat16, "f32": torch.float32}
+L2_FLUSH_BYTES = 256 << 20
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 8 for n, v in zip(names, r[4:8]) if v == "Active"})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def algorithmic_bytes(n_dst, n_src_touched, nnz, feat, elem, idx_bytes):
+    """Compulsory bytes of one SpMM pass: touched input rows once, output rows once, idx, ptr."""
+    return n_src_touched * feat * elem + n_dst * feat * elem + nnz * idx_bytes + (n_dst + 1) * 8
+
+
+def cpu_baseline_sample(ptr, idx, feat, dtype, budget_s=20.0):
+    """Times the reference's CPU formulation (torch index_add_ and sparse.mm, fp32, all host threads;
+    test/2-benchmark/bench-gcn.py:45-60, cxgnncomp/codegen/torch_spmm.py:4-9) on a contiguous row sample
+    of the workload. Source rows are compacted so that the sample's features fit host memory.
+    `ptr`/`idx` may live on the GPU; only the sample is copied to the host."""
+    import oracle
+    n = ptr.shape[0] - 1
+    nnz = int(ptr[n])
+    torch.set_num_threads(os.cpu_count() or 1)
+    want_edges = min(nnz, 8_000_000)
+    r0 = n // 3
+    r1 = int(torch.searchsorted(ptr, ptr[r0] + want_edges).clamp(max=n))
+    r1 = max(r1, min(n, r0 + 1))
+    e0, e1 = int(ptr[r0]), int(ptr[r1])
+    sub_idx = idx[e0:e1].long()
+    uniq, inv = torch.unique(sub_idx, return_inverse=True)
+    sp = (ptr[r0:r1 + 1] - e0).cpu()
+    si = inv.cpu()
+    rows, n_src = r1 - r0, int(uniq.shape[0])
+    x = torch.randn(n_src, feat, generator=torch.Generator().manual_seed(1))
+    b_alg = algorithmic_bytes(rows, n_src, e1 - e0, feat, 4, 8)
+    best = {}
+    t_start = time.time()
+    for name, fn in (("index_add", lambda: oracle.torch_spmm_index_add(x, sp, si, rows)),
+                     ("sparse_mm", lambda: oracle.torch_spmm_sparse(x, sp, si, rows))):
+        fn()  # warm-up
+        ts = []
+        while len(ts) < 5 and (time.time() - t_start) < budget_s:
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        if ts:
+            best[name] = sorted(ts)[len(ts) // 2]
+    form = min(best, key=best.get)
+    return {"value": b_alg / best[form] / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"rows [{r0},{r1}) of the workload = {rows} rows / {e1 - e0} edges / {n_src} distinct sources, "
+                      f"fp32 int64, torch {form} (median of {len(ts)}), {best[form] * 1e3:.1f} ms",
+            "formulation": form, "ms": best[form] * 1e3}
+
+
+def build_workload(name, device, seed=0):
+    from cxgnncomp import synthetic
+    n, e_und, feat, dt, it, desc = WORKLOADS[name]
+    idx_dtype = torch.int32 if it == "int32" else torch.int64
+    ptr, idx = synthetic.powerlaw_graph(n, e_und, seed=seed, device=device, idx_dtype=idx_dtype)
+    return ptr, idx, n, feat, DTYPES[dt], desc
+
+
+def run_reference(args, rank):
+    """The reference's CPU formulation on host cores (there is no CPU kernel in the reference; its
+    torch formulation is what it validates against). Rank 0 only."""
+    if rank != 0:
+        return
+    name = args.workload
+    dev = torch.device("cuda:0") if torch.cuda.is_available() else torch.device("cpu")
+    ptr, idx, n, feat, dtype, desc = build_workload(name, dev)
+    ts = []
+    base = None
+    for _ in range(args.warmup + args.steps):
+        base = cpu_baseline_sample(ptr, idx, feat, dtype, budget_s=max(5.0, 60.0 / (args.warmup + args.steps)))
+        ts.append(base["ms"])
+    ms = sum(ts[args.warmup:]) / max(1, args.steps)
+    line = {"impl": "reference", "metric": "spmm_algorithmic_hbm_throughput", "value": base["value"], "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "description": desc, "sample": base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=os.environ.get("CXG_BENCH_WORKLOAD", "papers_like"),
+                    choices=sorted(WORKLOADS))
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    import cxgnncomp_backend as be
+    from cxgnncomp import synthetic, row_partition_by_nnz, local_rows
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ptr, idx, n, feat, dtype, desc = build_workload(args.workload, dev)
+    nnz = int(ptr[n])
+    elem = 2 if dtype == torch.bfloat16 else 4
+    idx_bytes = idx.element_size()
+    bounds = row_partition_by_nnz(ptr, world)
+    r0, r1 = bounds[rank], bounds[rank + 1]
+    if world > 1:
+        lptr, lidx = local_rows(ptr, idx, r0, r1)
+        full_ptr = ptr
+        del idx
+    else:
+        lptr, lidx, full_ptr = ptr, idx, ptr
+    torch.cuda.empty_cache()
+    n_local = r1 - r0
+
+    # features: every rank draws the same stream and keeps the whole matrix as its gather buffer
+    x_full = synthetic.node_features(n, feat, seed=0, device=dev, dtype=dtype)
+    y = torch.empty((n_local, feat), dtype=dtype, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    b_alg_total = algorithmic_bytes(n, n, nnz, feat, elem, idx_bytes)
+    b_alg_local = algorithmic_bytes(n_local, n, int(lptr[n_local]), feat, elem, idx_bytes)
+
+    def exchange():
+        """All ranks end up with every shard of x in x_full (NCCL broadcasts, one per source rank)."""
+        works = [dist.broadcast(x_full[bounds[j]:bounds[j + 1]], src=j, async_op=True) for j in range(world)]
+        for w in works:
+            w.wait()
+
+    def step():
+        if world > 1:
+            exchange()
+        return be._spmm_forward(x_full, lptr, lidx, n_local, out=y)
+
+    def timed(fn, k):
+        """k calls of fn, each between its own pair of events on the current stream, L2 flushed before."""
+        total = 0.0
+        for _ in range(k):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            total += a.elapsed_time(b)
+        return total
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = be.kernel_launch_count()
+    ms_total = timed(step, args.steps)
+    launches = be.kernel_launch_count() - launches0
+    barrier()
+    # kernel-only time of the SpMM call (no exchange), for the roofline
+    spmm_ms = timed(lambda: be._spmm_forward(x_full, lptr, lidx, n_local, out=y), args.steps) / args.steps
+    barrier()
+    clocks = sampler.stop() if sampler else None
+
+    t = torch.tensor([ms_total, spmm_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t[0]) / args.steps
+    spmm_ms = float(t[1])
+    value = b_alg_total / (ms_step * 1e-3) / 1e9
+
+    # end to end: inputs from pinned host memory, result back to the host, every step
+    e2e = None
+    if not args.no_e2e:
+        hx = torch.empty(x_full[r0:r1].shape, dtype=dtype).pin_memory()
+        hx.copy_(x_full[r0:r1])
+        hidx = torch.empty(lidx.shape, dtype=lidx.dtype).pin_memory()
+        hidx.copy_(lidx)
+        hptr = torch.empty(lptr.shape, dtype=lptr.dtype).pin_memory()
+        hptr.copy_(lptr)
+        hy = torch.empty(y.shape, dtype=dtype).pin_memory()
+        d_idx, d_ptr = torch.empty_like(lidx), torch.empty_like(lptr)
+
+        def e2e_step():
+            x_full[r0:r1].copy_(hx, non_blocking=True)
+            d_idx.copy_(hidx, non_blocking=True)
+            d_ptr.copy_(hptr, non_blocking=True)
+            if world > 1:
+                exchange()
+            out = be.run_spmm_configurable(d_ptr, d_idx, x_full, n_local)
+            hy.copy_(out, non_blocking=True)
+
+        ksteps = min(args.steps, 5)
+        e2e_step()
+        barrier()
+        e_ms = timed(e2e_step, ksteps) / ksteps
+        barrier()
+        te = torch.tensor([e_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        h2d = hx.numel() * elem + hidx.numel() * idx_bytes + hptr.numel() * 8
+        d2h = hy.numel() * elem
+        e2e = {"value": b_alg_total / (float(te[0]) * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": float(te[0]),
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": ksteps,
+               "api": "cxgnncomp_backend.run_spmm_configurable, inputs from pinned host memory"}
+        del hx, hidx, hptr, hy
+
+    peak, peak_src = load_peaks()
+    achieved = b_alg_local / (spmm_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": peak_src, "kernel": "cxg_spmm_csr (plan + spmm_rows + reduce)",
+                "ms": spmm_ms, "algorithmic_bytes": b_alg_local}
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline_sample(full_ptr, lidx, feat, dtype)
+
+    if rank == 0:
+        line = {"metric": "spmm_algorithmic_hbm_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+                "data": "synthetic",
+                "config": {"workload": args.workload, "description": desc, "nodes": n, "nnz": nnz, "feat": feat,
+                           "idx_bytes": idx_bytes, "partition": f"rows by edge count over {world} GPU(s)",
+                           "l2": "256 MiB written between timed steps; inputs exceed L2"},
+                "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
+                "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

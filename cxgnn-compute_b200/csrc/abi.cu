@@ -16,6 +16,10 @@ int set_error(int code, const char *fmt, ...) {
   return code;
 }
 
+static long long g_launches = 0;
+
+void count_launches(int n) { __atomic_fetch_add(&g_launches, static_cast<long long>(n), __ATOMIC_RELAXED); }
+
 int check_launch(const char *what) {
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return CXG_OK;
@@ -27,3 +31,7 @@ int check_launch(const char *what) {
 extern "C" const char *cxg_last_error_string(void) { return cxg::g_last_error; }
 
 extern "C" int cxg_abi_version(void) { return 1; }
+
+extern "C" long long cxg_kernel_launch_count(void) {
+  return __atomic_load_n(&cxg::g_launches, __ATOMIC_RELAXED);
+}

@@ -17,6 +17,8 @@ constexpr int kNumSM = 148;
 
 int set_error(int code, const char *fmt, ...);
 int check_launch(const char *what);
+// Adds n to the process-wide count of kernels this library has launched.
+void count_launches(int n);
 
 #define CXG_REQUIRE(cond, code, ...)                   \
   do {                                                 \

@@ -19,14 +19,19 @@
 // their fp32 partial rows go to scratch memory and a last pass adds them in
 // segment order. No atomics touch feature data, so results are reproducible.
 #include "common.cuh"
+#include "spmm_stream.cuh"
 
 namespace cxg {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kUnroll = 4;
-constexpr int kDefaultSplit = 512;
+constexpr int kUnroll = 8;
+constexpr int kDefaultSplit = 256;
+constexpr int kRowsPerGroup = 4;
+#ifndef CXG_SPMM_MIN_BLOCKS
+#define CXG_SPMM_MIN_BLOCKS 3  // resident CTAs per SM the row kernel is compiled for (register cap)
+#endif
 constexpr int kHeavyBlocksPerSM = 4;
 
 // Header words at the start of the workspace.
@@ -94,28 +99,60 @@ __global__ void spmm_plan_chunks(SpmmArgs a) {
 }
 
 // ---------------------------------------------------------------------------
+// Edge stream. idx (and the optional per-edge arrays) are read exactly once, so
+// they are loaded with an L2 evict-first policy and do not displace feature rows.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+__device__ __forceinline__ int64_t load_stream(const int64_t *p, uint64_t pol) {
+  int64_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.s64 %0, [%1], %2;" : "=l"(v) : "l"(p), "l"(pol));
+  return v;
+}
+
+__device__ __forceinline__ int64_t load_stream(const int32_t *p, uint64_t pol) {
+  int32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
+  return static_cast<int64_t>(v);
+}
+
+// Source row (or -1 when the edge is masked out) and single-head value of edge e.
+template <typename IdxT, int VALMODE>
+__device__ __forceinline__ void load_edge(const SpmmArgs &a, int64_t e, uint64_t pol, int64_t &nid,
+                                          float &val) {
+  const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
+  bool keep = a.edge_mask == nullptr || a.edge_mask[e] != 0;
+  nid = -1;
+  if (keep) {
+    nid = load_stream(idx + e, pol);
+    if (a.edge_rel != nullptr) nid += static_cast<int64_t>(__ldg(a.edge_rel + e)) * a.rel_stride;
+  }
+  if (VALMODE == 1) val = __ldg(a.edge_val + e);
+}
+
+// ---------------------------------------------------------------------------
 // Sum of edges [e_begin, e_end) into acc, CSR order, for the NV vectors of this
 // lane. VALMODE: 0 none, 1 one value per edge, 2 one value per (edge, head).
+// (nid0, val0) is this lane's edge of the first batch, already loaded by the
+// caller; the ids of batch b+1 are requested before the rows of batch b, so the
+// index stream never sits on the critical path.
 // ---------------------------------------------------------------------------
 template <typename VT, typename T, typename IdxT, int G, int NV, int VALMODE>
 __device__ __forceinline__ void aggregate_segment(const SpmmArgs &a, int64_t e_begin, int64_t e_end,
-                                                  int lg, unsigned gmask, const int (&col)[NV],
-                                                  const bool (&on)[NV], const int (&head)[NV],
-                                                  float (&acc)[NV][VT::kElems]) {
-  const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
+                                                  int lg, unsigned gmask, uint64_t pol, int64_t nid0,
+                                                  float val0, const int (&col)[NV], const bool (&on)[NV],
+                                                  const int (&head)[NV], float (&acc)[NV][VT::kElems]) {
   const T *x = reinterpret_cast<const T *>(a.x);
+  int64_t my_nid = nid0;
+  float my_val = val0;
   for (int64_t e0 = e_begin; e0 < e_end; e0 += G) {
-    int64_t my_nid = -1;
-    float my_val = 0.f;
-    int64_t e = e0 + lg;
-    if (e < e_end) {
-      bool keep = a.edge_mask == nullptr || a.edge_mask[e] != 0;
-      if (keep) {
-        my_nid = static_cast<int64_t>(__ldg(idx + e));
-        if (a.edge_rel != nullptr) my_nid += static_cast<int64_t>(__ldg(a.edge_rel + e)) * a.rel_stride;
-      }
-      if (VALMODE == 1) my_val = __ldg(a.edge_val + e);
-    }
+    int64_t next_nid = -1;
+    float next_val = 0.f;
+    if (e0 + G + lg < e_end) load_edge<IdxT, VALMODE>(a, e0 + G + lg, pol, next_nid, next_val);
     int64_t left = e_end - e0;
     int cnt = left < G ? static_cast<int>(left) : G;
     for (int j = 0; j < cnt; j += kUnroll) {
@@ -158,13 +195,18 @@ __device__ __forceinline__ void aggregate_segment(const SpmmArgs &a, int64_t e_b
         }
       }
     }
+    my_nid = next_nid;
+    my_val = next_val;
   }
 }
 
-// Blocks [0, heavy_blocks) walk the segments of long rows; the rest own the
-// short rows, one row per group of G lanes.
+// Blocks [0, heavy_blocks) walk the segments of long rows (grid-stride); every
+// other block owns a tile of kGroupsPerBlock * kRowsPerGroup consecutive short
+// rows. A group handles kRowsPerGroup rows of the tile one after the other; the
+// row pointers of all of them are fetched up front and the first ids of row k+1
+// are requested before the features of row k.
 template <typename VT, typename T, typename IdxT, int G, int NV, int VALMODE>
-__global__ void __launch_bounds__(kThreads) spmm_rows(SpmmArgs a) {
+__global__ void __launch_bounds__(kThreads, CXG_SPMM_MIN_BLOCKS) spmm_rows(SpmmArgs a) {
   constexpr int E = VT::kElems;
   constexpr int kGroupsPerBlock = kThreads / G;
   const int lane = threadIdx.x & 31;
@@ -172,90 +214,135 @@ __global__ void __launch_bounds__(kThreads) spmm_rows(SpmmArgs a) {
   const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << (lane & ~(G - 1)));
   const int group_in_block = threadIdx.x / G;
   const int nvec = a.width / E;  // vectors per feature row
+  const uint64_t pol = policy_evict_first();
   T *y = reinterpret_cast<T *>(a.y);
-
   const bool heavy = static_cast<int>(blockIdx.x) < a.heavy_blocks;
-  int64_t task, task_end, task_step;
+
+  int64_t task = 0, task_end = 0, task_step = 1;
+  int64_t rb[kRowsPerGroup], re[kRowsPerGroup];
   if (heavy) {
     task = static_cast<int64_t>(blockIdx.x) * kGroupsPerBlock + group_in_block;
     task_end = min(a.hdr[kHdrNumChunks], a.max_chunks);
     task_step = static_cast<int64_t>(a.heavy_blocks) * kGroupsPerBlock;
   } else {
-    task = (static_cast<int64_t>(blockIdx.x) - a.heavy_blocks) * kGroupsPerBlock + group_in_block;
-    task_end = a.n_dst;
-    task_step = task_end;  // one row per group
+    int64_t tile0 = (static_cast<int64_t>(blockIdx.x) - a.heavy_blocks) * kGroupsPerBlock * kRowsPerGroup;
+    task = tile0 + group_in_block;
+    task_step = kGroupsPerBlock;
+    task_end = min(a.n_dst, tile0 + static_cast<int64_t>(kGroupsPerBlock) * kRowsPerGroup);
+#pragma unroll
+    for (int k = 0; k < kRowsPerGroup; ++k) {
+      int64_t r = task + static_cast<int64_t>(k) * kGroupsPerBlock;
+      rb[k] = re[k] = 0;
+      if (r < task_end) {
+        rb[k] = load_ptr(a.ptr, r, a.ptr_bytes);
+        re[k] = load_ptr(a.ptr, r + 1, a.ptr_bytes);
+      }
+    }
   }
 
-  for (; task < task_end; task += task_step) {
-    int64_t row, e_begin, e_end, deg;
-    float *partial = nullptr;
-    if (heavy) {
-      int slot = a.chunk_slot[task];
-      row = a.heavy_row[slot];
-      int k = static_cast<int>(task) - a.heavy_base[slot];
-      int64_t rb = load_ptr(a.ptr, row, a.ptr_bytes);
-      int64_t re = load_ptr(a.ptr, row + 1, a.ptr_bytes);
-      deg = re - rb;
-      e_begin = rb + static_cast<int64_t>(k) * a.split;
-      e_end = min(re, e_begin + a.split);
-      partial = a.partials + task * a.width;
-    } else {
-      row = task;
-      e_begin = load_ptr(a.ptr, row, a.ptr_bytes);
-      e_end = load_ptr(a.ptr, row + 1, a.ptr_bytes);
-      deg = e_end - e_begin;
-      if (deg > a.split) continue;  // long row: done by the heavy blocks
-    }
+  // Range and first-batch ids of the task after the current one.
+  int64_t nxt_begin = 0, nxt_end = 0, nxt_row = -1, nxt_nid = -1;
+  float nxt_val = 0.f;
+  auto fetch_heavy = [&](int64_t t) {
+    nxt_row = -1;
+    nxt_nid = -1;
+    if (t >= task_end) return;
+    int slot = a.chunk_slot[t];
+    nxt_row = a.heavy_row[slot];
+    int c = static_cast<int>(t) - a.heavy_base[slot];
+    int64_t b = load_ptr(a.ptr, nxt_row, a.ptr_bytes);
+    int64_t e = load_ptr(a.ptr, nxt_row + 1, a.ptr_bytes);
+    nxt_begin = b + static_cast<int64_t>(c) * a.split;
+    nxt_end = min(e, nxt_begin + a.split);
+    if (nxt_begin + lg < nxt_end) load_edge<IdxT, VALMODE>(a, nxt_begin + lg, pol, nxt_nid, nxt_val);
+  };
+  auto fetch_light = [&](int64_t t, int64_t b, int64_t e) {
+    nxt_row = t;
+    nxt_nid = -1;
+    nxt_begin = b;
+    nxt_end = (e - b > a.split) ? b : e;  // long row: left to the heavy blocks
+    if (nxt_begin + lg < nxt_end) load_edge<IdxT, VALMODE>(a, nxt_begin + lg, pol, nxt_nid, nxt_val);
+  };
+
+  auto run = [&](int64_t row, int64_t e_begin, int64_t e_end, int64_t nid0, float val0, int64_t cur) {
+    const int64_t deg = heavy ? 1 : e_end - e_begin;
     // Column passes: G*NV vectors per pass (one pass whenever the row fits).
     for (int v0 = 0; v0 < nvec; v0 += G * NV) {
       int col[NV], head[NV];
       bool on[NV];
       float acc[NV][E];
 #pragma unroll
-      for (int k = 0; k < NV; ++k) {
-        int v = v0 + lg + k * G;
-        on[k] = v < nvec;
-        col[k] = v * E;
-        head[k] = on[k] ? col[k] / a.feat : 0;
+      for (int q = 0; q < NV; ++q) {
+        int v = v0 + lg + q * G;
+        on[q] = v < nvec;
+        col[q] = v * E;
+        head[q] = on[q] ? col[q] / a.feat : 0;
 #pragma unroll
-        for (int i = 0; i < E; ++i) acc[k][i] = 0.f;
+        for (int i = 0; i < E; ++i) acc[q][i] = 0.f;
       }
-      aggregate_segment<VT, T, IdxT, G, NV, VALMODE>(a, e_begin, e_end, lg, gmask, col, on, head,
-                                                     acc);
+      int64_t n0 = nid0;
+      float w0 = val0;
+      if (v0 > 0 && e_begin + lg < e_end) load_edge<IdxT, VALMODE>(a, e_begin + lg, pol, n0, w0);
+      aggregate_segment<VT, T, IdxT, G, NV, VALMODE>(a, e_begin, e_end, lg, gmask, pol, n0, w0, col, on,
+                                                     head, acc);
       if (heavy) {
+        float *partial = a.partials + cur * a.width;
 #pragma unroll
-        for (int k = 0; k < NV; ++k)
-          if (on[k]) {
+        for (int q = 0; q < NV; ++q)
+          if (on[q]) {
             if (E % 4 == 0) {
 #pragma unroll
               for (int i = 0; i < E; i += 4)
-                *reinterpret_cast<float4 *>(partial + col[k] + i) =
-                    make_float4(acc[k][i], acc[k][(i + 1) % E], acc[k][(i + 2) % E], acc[k][(i + 3) % E]);
+                *reinterpret_cast<float4 *>(partial + col[q] + i) =
+                    make_float4(acc[q][i], acc[q][(i + 1) % E], acc[q][(i + 2) % E], acc[q][(i + 3) % E]);
             } else {
 #pragma unroll
-              for (int i = 0; i < E; ++i) partial[col[k] + i] = acc[k][i];
+              for (int i = 0; i < E; ++i) partial[col[q] + i] = acc[q][i];
             }
           }
       } else {
         int64_t out_row = a.targets != nullptr ? __ldg(a.targets + row) : row;
         T *yr = y + out_row * a.width;
 #pragma unroll
-        for (int k = 0; k < NV; ++k)
-          if (on[k]) {
+        for (int q = 0; q < NV; ++q)
+          if (on[q]) {
             if (a.reduce == CXG_MEAN) {
               float d = static_cast<float>(deg);
 #pragma unroll
-              for (int i = 0; i < E; ++i) acc[k][i] = deg > 0 ? __fdiv_rn(acc[k][i], d) : 0.f;
+              for (int i = 0; i < E; ++i) acc[q][i] = deg > 0 ? __fdiv_rn(acc[q][i], d) : 0.f;
             }
             if (a.accumulate) {
               float old[E];
-              VT::to_float(old, VT::load_plain(yr + col[k]));
+              VT::to_float(old, VT::load_plain(yr + col[q]));
 #pragma unroll
-              for (int i = 0; i < E; ++i) acc[k][i] += old[i];
+              for (int i = 0; i < E; ++i) acc[q][i] += old[i];
             }
-            VT::store_stream(yr + col[k], VT::from_float(acc[k]));
+            VT::store_stream(yr + col[q], VT::from_float(acc[q]));
           }
       }
+    }
+  };
+
+  if (heavy) {
+    fetch_heavy(task);
+    while (task < task_end) {
+      const int64_t row = nxt_row, e_begin = nxt_begin, e_end = nxt_end, nid0 = nxt_nid, cur = task;
+      const float val0 = nxt_val;
+      task += task_step;
+      fetch_heavy(task);
+      run(row, e_begin, e_end, nid0, val0, cur);
+    }
+  } else {
+    fetch_light(task, rb[0], re[0]);
+#pragma unroll
+    for (int k = 0; k < kRowsPerGroup; ++k) {
+      const int64_t row = nxt_row, e_begin = nxt_begin, e_end = nxt_end, nid0 = nxt_nid;
+      const float val0 = nxt_val;
+      const bool live = row < task_end && (re[k] - rb[k] <= a.split);
+      if (k + 1 < kRowsPerGroup)
+        fetch_light(task + static_cast<int64_t>(k + 1) * kGroupsPerBlock, rb[k + 1 < kRowsPerGroup ? k + 1 : k],
+                    re[k + 1 < kRowsPerGroup ? k + 1 : k]);
+      if (live) run(row, e_begin, e_end, nid0, val0, 0);
     }
   }
 }
@@ -336,8 +423,8 @@ void launch_rows(SpmmArgs &a, int valmode, cudaStream_t st) {
     else if (nvec > 32)
       NV = 2;
   }
-  int64_t groups_per_block = kThreads / G;
-  int64_t light_blocks = (a.n_dst + groups_per_block - 1) / groups_per_block;
+  int64_t rows_per_block = static_cast<int64_t>(kThreads / G) * kRowsPerGroup;
+  int64_t light_blocks = (a.n_dst + rows_per_block - 1) / rows_per_block;
   dim3 grid(static_cast<unsigned>(a.heavy_blocks + light_blocks));
   if (!vector_ok) {
     launch_rows_val<Scalar<T>, T, IdxT, 32, 1>(a, valmode, grid, st);
@@ -396,7 +483,12 @@ extern "C" int cxg_spmm_csr_workspace_size(int64_t n_dst, int64_t nnz, int32_t f
   WorkspaceLayout L;
   int rc = plan_layout(n_dst, nnz, static_cast<int64_t>(feat) * heads, split, &L);
   CXG_REQUIRE(rc == CXG_OK, rc, "cxg_spmm_csr_workspace_size: graph too large for 32-bit segment ids");
-  *bytes = L.total;
+  // the streaming path tiles the edge array; its smallest automatic tile is 64 edges
+  StreamLayout S;
+  int tile = split_edges > 0 ? split_edges : 64;
+  rc = stream_layout(nnz, static_cast<int64_t>(feat) * heads, tile, &S);
+  CXG_REQUIRE(rc == CXG_OK, rc, "cxg_spmm_csr_workspace_size: graph too large for 32-bit tile ids");
+  *bytes = L.total > S.total ? L.total : S.total;
   return CXG_OK;
 }
 
@@ -425,6 +517,11 @@ extern "C" int cxg_spmm_csr(const cxg_spmm_desc *d, void *workspace, size_t work
   CXG_REQUIRE(d->edge_rel == nullptr || d->rel_stride > 0, CXG_EINVAL,
               "cxg_spmm_csr: edge_rel needs rel_stride > 0");
 
+  if (stream_eligible(d)) {
+    CXG_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, CXG_EINVAL,
+                "cxg_spmm_csr: workspace must be 16-byte aligned");
+    return stream_launch(d, workspace, workspace_bytes, as_stream(stream));
+  }
   SpmmArgs a;
   a.ptr = d->ptr;
   a.idx = d->idx;
@@ -489,5 +586,6 @@ extern "C" int cxg_spmm_csr(const cxg_spmm_desc *d, void *workspace, size_t work
     else
       spmm_reduce_long_rows<__nv_bfloat16><<<kNumSM * 2, kThreads, 0, st>>>(a);
   }
+  count_launches(may_split ? 4 : 1);
   return check_launch("cxg_spmm_csr");
 }

@@ -258,5 +258,6 @@ extern "C" int cxg_spmm_csr_backward(const cxg_spmm_desc *d, const void *dy, flo
     rc = d->idx_bytes == 8 ? launch_bwd<__nv_bfloat16, int64_t>(a, valmode, edge_grad, d->nnz, st)
                            : launch_bwd<__nv_bfloat16, int32_t>(a, valmode, edge_grad, d->nnz, st);
   if (rc != CXG_OK) return rc;
+  count_launches(1);
   return check_launch("cxg_spmm_csr_backward");
 }

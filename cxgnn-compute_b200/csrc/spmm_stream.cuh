@@ -1,0 +1,53 @@
+// Interface between cxg_spmm_csr and its edge-tiled streaming path (spmm_stream.cu).
+#pragma once
+#include "common.cuh"
+
+namespace cxg {
+
+// Header words of the streaming workspace.
+enum { kSHdrNumLong = 0, kSHdrError = 1 };
+// Row fetch variants: 16-byte async copies into shared memory (default), one bulk
+// async copy per row into shared memory.
+enum { kModeCpAsync = 0, kModeBulk = 1 };
+
+struct StreamArgs {
+  const void *ptr;
+  const void *idx;
+  const void *x;
+  void *y;
+  const float *edge_val;
+  const int32_t *edge_rel;
+  const int64_t *targets;
+  int64_t n_dst;
+  int64_t rel_stride;
+  int64_t max_tiles;
+  int width, feat, heads, ptr_bytes, reduce, accumulate;
+  int tile;         // edges per tile
+  int stage_edges;  // edges per ring stage
+  int stage_bytes;  // stage_edges * row bytes
+  int slot_offset;  // offset of the row slots inside a warp's shared memory
+  int warp_smem;    // shared memory per warp
+  int max_long;
+  int cpr_shift;  // log2(16-byte chunks per row), -1 when not a power of two
+  int mode;       // how feature rows are fetched: kModeCpAsync / kModeBulk
+  int32_t *hdr;
+  int64_t *tile_row;    // row that owns the first edge of each tile
+  int64_t *tail_row;    // row left unfinished at the end of each tile, or -1
+  int64_t *long_tiles;  // tiles whose unfinished row spans more than 64 tiles
+  float *partials;      // [tile][2][width]: head partial, tail partial
+};
+
+struct StreamLayout {
+  size_t hdr, tile_row, tail_row, long_tiles, partials, total;
+  int64_t max_tiles;
+  int max_long;
+};
+
+// True when the descriptor can take the streaming path (16-byte rows up to 1 KiB, no edge mask).
+bool stream_eligible(const cxg_spmm_desc *d);
+// Edges per tile for this call (desc->split_edges when set).
+int stream_tile_edges(const cxg_spmm_desc *d);
+int stream_layout(int64_t nnz, int64_t width, int tile, StreamLayout *L);
+int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_bytes, cudaStream_t st);
+
+}  // namespace cxg

@@ -26,7 +26,7 @@ CXG_SPMM_ACCUMULATE = 1
 
 
 def _load():
-    path = os.path.abspath(_LIB_PATH)
+    path = os.path.abspath(os.environ.get("CXGNN_B200_LIB", _LIB_PATH))
     if not os.path.exists(path):
         raise ImportError(
             f"{path} is missing: build it with `python {os.path.join(os.path.dirname(path), 'build.py')}` "
@@ -50,6 +50,12 @@ class SpmmDesc(ctypes.Structure):
 
 _lib.cxg_last_error_string.restype = ctypes.c_char_p
 _lib.cxg_abi_version.restype = ctypes.c_int
+_lib.cxg_kernel_launch_count.restype = ctypes.c_longlong
+
+
+def kernel_launch_count():
+    """Kernels launched by the library in this process so far."""
+    return int(_lib.cxg_kernel_launch_count())
 
 
 def _sig(name, argtypes):
@@ -97,6 +103,9 @@ _workspaces = {}
 # Rows with more edges than this are split into segments; 0 keeps the library default.
 # Tests lower it to exercise the split path on small graphs.
 SPLIT_EDGES = 0
+# OR-ed into cxg_spmm_desc.flags; CXG_SPMM_BULK_ROWS (4) selects the bulk-copy (TMA) row fetch.
+CXG_SPMM_BULK_ROWS = 4
+EXTRA_SPMM_FLAGS = int(os.environ.get("CXG_SPMM_FLAGS", "0"))
 
 
 def _workspace(device, nbytes):
@@ -131,11 +140,11 @@ def _make_desc(ptr, idx, x, y, num_node, *, heads=1, feat=None, edge_val=None, e
     d.feat = int(feat)
     d.heads = int(heads)
     ref = x if x is not None else y
-    d.dtype = _dtype_code(ref)
+    d.dtype = _dtype_code(ref) if ref is not None else CXG_F32
     d.ptr_bytes = ptr.element_size()
     d.idx_bytes = idx.element_size()
     d.reduce = reduce
-    d.flags = CXG_SPMM_ACCUMULATE if accumulate else 0
+    d.flags = (CXG_SPMM_ACCUMULATE if accumulate else 0) | EXTRA_SPMM_FLAGS
     d.split_edges = SPLIT_EDGES
     return d
 

@@ -47,9 +47,15 @@ extern "C" {
 
 /* ---- flags of cxg_spmm_csr ---------------------------------------------- */
 #define CXG_SPMM_ACCUMULATE 1u /* y[row] += result instead of y[row] = result */
+/* Row-fetch variant of the tiled kernel, kept for measurement; results are
+   bit-identical. Default: 16-byte async copies into shared memory. */
+#define CXG_SPMM_BULK_ROWS 4u /* one bulk async copy (TMA) per row into shared
+                                 memory, completion on an mbarrier             */
 
 const char *cxg_last_error_string(void);
 int cxg_abi_version(void);
+/* Kernels launched by this library in this process so far (all threads). */
+long long cxg_kernel_launch_count(void);
 
 /*
  * Description of one CSR aggregation  y[t(r), h, :] (+)= red_{e in row r} v[e,h] * x[s(e), h, :]
@@ -90,7 +96,7 @@ typedef struct cxg_spmm_desc {
   int32_t idx_bytes;
   int32_t reduce;
   uint32_t flags;
-  int32_t split_edges; /* rows with more edges are split; 0 = default (512) */
+  int32_t split_edges; /* rows with more edges are split; 0 = default (256) */
 } cxg_spmm_desc;
 
 /*

@@ -66,9 +66,10 @@ def _bf16_bits(x):
 
 
 def spmm(ptr, idx, x, edge_val=None, mean=False, edge_mask=None, edge_rel=None, rel_stride=0,
-         targets=None, out=None, n_dst=None):
+         targets=None, out=None, n_dst=None, tile=0):
     """Sequential-order fp32 SpMM (orc_spmm_csr). x: torch [N,F] or [N,H,F], fp32 or bf16.
-    Returns a torch tensor of x's dtype; `out` (same dtype) is accumulated into."""
+    Returns a torch tensor of x's dtype; `out` (same dtype) is accumulated into.
+    tile > 0 switches to the summation order of the CUDA streaming kernel at that tile size."""
     ptr_n, idx_n = _np(ptr, np.int64), _np(idx, np.int64)
     n = int(n_dst) if n_dst else len(ptr_n) - 1
     bf16 = x.dtype == torch.bfloat16
@@ -85,9 +86,16 @@ def spmm(ptr, idx, x, edge_val=None, mean=False, edge_mask=None, edge_rel=None, 
         ya = (_bf16_bits(out) if bf16 else _np(out, np.float32)).copy()
     else:
         ya = np.zeros(shape, dtype=np.uint16 if bf16 else np.float32)
-    lib().orc_spmm_csr(_ptr(ptr_n), _ptr(idx_n), _ptr(xa), _ptr(ya), _ptr(ev), _ptr(em), _ptr(er),
-                       ctypes.c_int64(rel_stride), _ptr(tg), ctypes.c_int64(n), feat, heads, int(mean),
-                       int(accumulate), int(bf16))
+    if tile:
+        # summation order of the CUDA streaming kernel with `tile` edges per tile (orc_spmm_csr_tiled)
+        assert em is None, "the tiled order has no edge mask"
+        lib().orc_spmm_csr_tiled(_ptr(ptr_n), _ptr(idx_n), _ptr(xa), _ptr(ya), _ptr(ev), _ptr(er),
+                                 ctypes.c_int64(rel_stride), _ptr(tg), ctypes.c_int64(n), feat, heads, int(mean),
+                                 int(accumulate), int(bf16), ctypes.c_int64(tile))
+    else:
+        lib().orc_spmm_csr(_ptr(ptr_n), _ptr(idx_n), _ptr(xa), _ptr(ya), _ptr(ev), _ptr(em), _ptr(er),
+                           ctypes.c_int64(rel_stride), _ptr(tg), ctypes.c_int64(n), feat, heads, int(mean),
+                           int(accumulate), int(bf16))
     if bf16:
         return torch.from_numpy(ya.view(np.int16)).view(torch.bfloat16)
     return torch.from_numpy(ya)

@@ -90,6 +90,78 @@ ORC_API void orc_spmm_csr(const int64_t *ptr, const int64_t *idx, const void *x,
   free(acc);
 }
 
+/*
+ * The same SpMM in the summation order of the sm_100a streaming kernel, so that its
+ * output can be checked bit for bit. This restates the CUDA library's order, not the
+ * reference's: the edge array is cut into tiles of `tile` edges; a row inside one tile
+ * is summed sequentially (identical to orc_spmm_csr); a row that crosses tile borders
+ * is summed per tile (each partial starting from 0), and its m partials are then added
+ * in tile order: sequentially when m <= 64, otherwise in 8 contiguous blocks
+ * [m*w/8, m*(w+1)/8) that are each added from 0 and then joined in block order.
+ */
+ORC_API void orc_spmm_csr_tiled(const int64_t *ptr, const int64_t *idx, const void *x, void *y,
+                                const float *edge_val, const int32_t *edge_rel, int64_t rel_stride,
+                                const int64_t *targets, int64_t n_dst, int feat, int heads, int mean,
+                                int accumulate, int bf16, int64_t tile) {
+  const int width = feat * heads;
+  const float *xf = (const float *)x;
+  const uint16_t *xh = (const uint16_t *)x;
+  float *yf = (float *)y;
+  uint16_t *yh = (uint16_t *)y;
+  float *acc = (float *)malloc(sizeof(float) * (size_t)width);
+  float *tot = (float *)malloc(sizeof(float) * (size_t)width);
+  for (int64_t r = 0; r < n_dst; ++r) {
+    int64_t b = ptr[r], e = ptr[r + 1];
+    for (int c = 0; c < width; ++c) tot[c] = 0.f;
+    if (e > b) {
+      int64_t t0 = b / tile, t1 = (e - 1) / tile, m = t1 - t0 + 1;
+      float *parts = (float *)malloc(sizeof(float) * (size_t)width * (size_t)m);
+      for (int64_t t = t0; t <= t1; ++t) {
+        int64_t sb = t * tile > b ? t * tile : b, se = (t + 1) * tile < e ? (t + 1) * tile : e;
+        for (int c = 0; c < width; ++c) acc[c] = 0.f;
+        for (int64_t j = sb; j < se; ++j) {
+          int64_t s = idx[j];
+          if (edge_rel) s += (int64_t)edge_rel[j] * rel_stride;
+          for (int c = 0; c < width; ++c) {
+            float v = bf16 ? bf16_to_f32(xh[s * width + c]) : xf[s * width + c];
+            if (edge_val)
+              acc[c] = fmaf(v, edge_val[j * heads + c / feat], acc[c]);
+            else
+              acc[c] += v;
+          }
+        }
+        memcpy(parts + (t - t0) * width, acc, sizeof(float) * (size_t)width);
+      }
+      if (m <= 64) {
+        memcpy(tot, parts, sizeof(float) * (size_t)width);
+        for (int64_t k = 1; k < m; ++k)
+          for (int c = 0; c < width; ++c) tot[c] += parts[k * width + c];
+      } else {
+        for (int w = 0; w < 8; ++w) {
+          int64_t kb = m * w / 8, ke = m * (w + 1) / 8;
+          for (int c = 0; c < width; ++c) acc[c] = 0.f;
+          for (int64_t k = kb; k < ke; ++k)
+            for (int c = 0; c < width; ++c) acc[c] += parts[k * width + c];
+          for (int c = 0; c < width; ++c) tot[c] = (w == 0) ? acc[c] : tot[c] + acc[c];
+        }
+      }
+      free(parts);
+    }
+    int64_t out = targets ? targets[r] : r;
+    for (int c = 0; c < width; ++c) {
+      float v = tot[c];
+      if (mean) v = (e > b) ? v / (float)(e - b) : 0.f;
+      if (accumulate) v += bf16 ? bf16_to_f32(yh[out * width + c]) : yf[out * width + c];
+      if (bf16)
+        yh[out * width + c] = f32_to_bf16(v);
+      else
+        yf[out * width + c] = v;
+    }
+  }
+  free(acc);
+  free(tot);
+}
+
 /* Same sum in double precision: the yardstick for rows that the GPU splits. */
 ORC_API void orc_spmm_csr_f64(const int64_t *ptr, const int64_t *idx, const void *x, double *y,
                               const float *edge_val, int64_t n_dst, int feat, int heads, int mean,

@@ -183,3 +183,20 @@ def test_rel_schedule_oracle():
         for l in range(2):
             assert out[9][r, l] == int((st < layers[l]).sum())
     assert total == idx.shape[0]
+
+
+def test_tiled_order_oracle():
+    """The restatement of the CUDA kernel's tile-wise order: identical to the sequential sum when no row
+    crosses a tile border, and within rounding of float64 otherwise."""
+    ptr, idx = random_csr(100, 80, 6, seed=50, hub=3000)
+    x = randn((80, 16), 51)
+    seq = oracle.spmm(ptr, idx, x)
+    assert torch.equal(oracle.spmm(ptr, idx, x, tile=1 << 40), seq)
+    for tile in (1, 7, 64):
+        t_ = oracle.spmm(ptr, idx, x, tile=tile)
+        inside = (ptr[:-1] // tile) == ((ptr[1:] - 1).clamp(min=0) // tile)
+        inside |= ptr[:-1] == ptr[1:]
+        assert torch.equal(t_[inside], seq[inside])
+        assert rel_err(t_, oracle.spmm_f64(ptr, idx, x)) < 1e-5
+    m = oracle.spmm(ptr, idx, x, tile=7, mean=True)
+    assert rel_err(m, oracle.spmm_f64(ptr, idx, x, mean=True)) < 1e-5
