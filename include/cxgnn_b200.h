@@ -140,6 +140,30 @@ int cxg_spmm_csr(const cxg_spmm_desc *desc, void *workspace,
 int cxg_spmm_csr_backward(const cxg_spmm_desc *desc, const void *dy, float *dx,
                           float *dval, void *stream);
 
+/*
+ * cxg_spmm_csr without a caller-provided workspace. No counterpart in the reference
+ * (its kernels need no scratch memory); added for callers that cannot allocate
+ * device memory at call time or cannot pass a scratch buffer across their binding:
+ * plugins inside a host program whose memory pool owns the device, serving loops
+ * that must avoid the device-wide synchronisation of cudaMalloc / cudaFree, thin
+ * FFI bindings that carry only the operator's tensors.
+ *
+ * The scratch lives in one fixed array of CXG_SPMM_STATIC_SCRATCH_BYTES inside the
+ * library, present on every GPU that loads the library until the process exits.
+ *   - A request that needs more scratch than that is refused with CXG_ELIMIT (the
+ *     message gives the need); nothing is launched. As a guide, 32 MiB covers the
+ *     169,343-node / 2.33M-edge graph at 128 fp32 features (about 15 MiB).
+ *   - All calls share the array. Its previous contents do not matter, but calls
+ *     that overlap on the GPU (other streams, other host threads) corrupt each
+ *     other: order them on the device.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress); make that call before starting any stream capture.
+ *   - It never calls cudaMalloc, cudaFree or any other allocating routine.
+ * Results are those of cxg_spmm_csr, bit for bit.
+ */
+#define CXG_SPMM_STATIC_SCRATCH_BYTES (32u << 20)
+int cxg_spmm_csr_static(const cxg_spmm_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
