@@ -1,0 +1,416 @@
+// Attention-side kernels of the GAT path for sm_100a: edge softmax forward / backward,
+// SDDMM on an edge list, and the small per-edge helpers that travel with them.
+//
+// Replaces edge_softmax_fwd / edge_softmax_bwd (src/cpp/src/edge_softmax.cu:3-95),
+// sddmm_multihead (src/cpp/src/sddmm_kernel.cu:3-25), gen_edge_value_degree and spmv_csr
+// (edge_softmax.cu:186-232), gather_fwd / gather_bwd (src/cpp/src/aggr.cu:42-62).
+//
+// Edge softmax. The reference runs one warp per (destination, head) and walks the row three
+// times with 4-byte accesses strided by the head count. Here one warp owns a destination and
+// carries up to four heads at once, so the source id of an edge is read once per pass and the
+// per-head scores of a source are one 16-byte sector. The arithmetic per (destination, head)
+// keeps the reference's order: lane l takes edges l, l+32, ...; the row maximum starts at
+// -100000; the row sum adds the lanes' partial sums with the shuffle-down tree 16, 8, 4, 2, 1;
+// the quotient is an exact fp32 division. Rows with more than kHeavyRow edges are handed to a
+// second kernel that puts a whole CTA on each of them (their sum order is a CTA tree instead).
+#include "common.cuh"
+
+namespace cxg {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kHeavyRow = 4096;
+constexpr int kHC = 4;  // heads carried together
+
+struct SoftmaxArgs {
+  const void *ptr;
+  const void *idx;
+  const float *att_dst;
+  const float *att_src;
+  const float *grad;     // backward: d(out)
+  float *out;            // forward: written; backward: read
+  uint8_t *mask;         // forward: written; backward: read
+  float *grad_dst;
+  float *grad_src;
+  int64_t n_dst;
+  int heads, ptr_bytes;
+  float slope;
+  int32_t *hdr;          // [0] number of heavy rows
+  int64_t *heavy;        // heavy row ids
+  int max_heavy;
+};
+
+__device__ __forceinline__ float warp_tree_sum(float v) {
+  // lane 0 ends with ((v0+v16)+(v8+v24))+..., the reference's shfl_down order
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  return __shfl_sync(0xffffffffu, v, 0);
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum / max of one value per thread (kThreads threads), result to all.
+__device__ __forceinline__ float block_sum(float v, float *sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) r += sh[w];
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float *sh) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = sh[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) r = fmaxf(r, sh[w]);
+  return r;
+}
+
+// Forward for one row; the STEP threads that share the row take edges first+k*STEP.
+// HEAVY = false: one warp, reference summation order. HEAVY = true: one CTA.
+template <typename IdxT, bool HEAVY>
+__device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh) {
+  constexpr int STEP = HEAVY ? kThreads : 32;
+  const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
+  const int H = a.heads;
+  const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
+  for (int h0 = 0; h0 < H; h0 += kHC) {
+    float dv[kHC], mx[kHC], part[kHC];
+#pragma unroll
+    for (int k = 0; k < kHC; ++k) {
+      dv[k] = h0 + k < H ? __ldg(a.att_dst + d * H + h0 + k) : 0.f;
+      mx[k] = -100000.f;
+      part[k] = 0.f;
+    }
+    for (int64_t i = b + first; i < e; i += STEP) {
+      const int64_t s = static_cast<int64_t>(__ldg(idx + i));
+#pragma unroll
+      for (int k = 0; k < kHC; ++k)
+        if (h0 + k < H) {
+          float t = dv[k] + __ldg(a.att_src + s * H + h0 + k);
+          t = fmaxf(t, t * a.slope);
+          a.out[i * H + h0 + k] = t;
+          a.mask[i * H + h0 + k] = t > 0.f;
+          mx[k] = fmaxf(mx[k], t);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kHC; ++k) mx[k] = HEAVY ? block_max(mx[k], sh) : warp_max(mx[k]);
+    for (int64_t i = b + first; i < e; i += STEP) {
+#pragma unroll
+      for (int k = 0; k < kHC; ++k)
+        if (h0 + k < H) {
+          const float p = expf(a.out[i * H + h0 + k] - mx[k]);
+          a.out[i * H + h0 + k] = p;
+          part[k] += p;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kHC; ++k) part[k] = HEAVY ? block_sum(part[k], sh) : warp_tree_sum(part[k]);
+    for (int64_t i = b + first; i < e; i += STEP) {
+#pragma unroll
+      for (int k = 0; k < kHC; ++k)
+        if (h0 + k < H) a.out[i * H + h0 + k] = __fdiv_rn(a.out[i * H + h0 + k], part[k]);
+    }
+  }
+}
+
+// Backward for one row (edge_softmax.cu:44-95): s = sum out*g; tmp = out*(g-s), times
+// slope where the forward pre-activation was not positive; grad_src[src] += tmp;
+// grad_dst = sum tmp, written only when the row has both signs (it is 0 otherwise).
+template <typename IdxT, bool HEAVY>
+__device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh) {
+  constexpr int STEP = HEAVY ? kThreads : 32;
+  const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
+  const int H = a.heads;
+  const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
+  for (int h0 = 0; h0 < H; h0 += kHC) {
+    float s[kHC], dg[kHC], pos[kHC], neg[kHC];
+#pragma unroll
+    for (int k = 0; k < kHC; ++k) s[k] = dg[k] = pos[k] = neg[k] = 0.f;
+    for (int64_t i = b + first; i < e; i += STEP)
+#pragma unroll
+      for (int k = 0; k < kHC; ++k)
+        if (h0 + k < H) s[k] += a.out[i * H + h0 + k] * a.grad[i * H + h0 + k];
+#pragma unroll
+    for (int k = 0; k < kHC; ++k) s[k] = HEAVY ? block_sum(s[k], sh) : warp_tree_sum(s[k]);
+    for (int64_t i = b + first; i < e; i += STEP) {
+      const int64_t src = static_cast<int64_t>(__ldg(idx + i));
+#pragma unroll
+      for (int k = 0; k < kHC; ++k)
+        if (h0 + k < H) {
+          float tmp = a.out[i * H + h0 + k] * (a.grad[i * H + h0 + k] - s[k]);
+          if (!a.mask[i * H + h0 + k]) {
+            tmp *= a.slope;
+            neg[k] = 1.f;
+          } else {
+            pos[k] = 1.f;
+          }
+          dg[k] += tmp;
+          atomicAdd(a.grad_src + src * H + h0 + k, tmp);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kHC; ++k) {
+      dg[k] = HEAVY ? block_sum(dg[k], sh) : warp_tree_sum(dg[k]);
+      pos[k] = HEAVY ? block_sum(pos[k], sh) : warp_tree_sum(pos[k]);
+      neg[k] = HEAVY ? block_sum(neg[k], sh) : warp_tree_sum(neg[k]);
+      if (first == 0 && h0 + k < H && pos[k] > 0.f && neg[k] > 0.f) a.grad_dst[d * H + h0 + k] = dg[k];
+    }
+  }
+}
+
+template <typename IdxT, bool BWD>
+__global__ void __launch_bounds__(kThreads) edge_softmax_rows(SoftmaxArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t d = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (d >= a.n_dst) return;
+  const int64_t deg = load_ptr(a.ptr, d + 1, a.ptr_bytes) - load_ptr(a.ptr, d, a.ptr_bytes);
+  if (deg > kHeavyRow) {  // left to the CTA-per-row kernel
+    if (lane == 0) {
+      int slot = atomicAdd(a.hdr, 1);
+      if (slot < a.max_heavy) a.heavy[slot] = d;
+    }
+    return;
+  }
+  if (BWD)
+    softmax_bwd_row<IdxT, false>(a, d, lane, nullptr);
+  else
+    softmax_fwd_row<IdxT, false>(a, d, lane, nullptr);
+}
+
+template <typename IdxT, bool BWD>
+__global__ void __launch_bounds__(kThreads) edge_softmax_heavy(SoftmaxArgs a) {
+  __shared__ float sh[kWarps];
+  const int n = min(a.hdr[0], a.max_heavy);
+  for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    if (BWD)
+      softmax_bwd_row<IdxT, true>(a, a.heavy[i], threadIdx.x, sh);
+    else
+      softmax_fwd_row<IdxT, true>(a, a.heavy[i], threadIdx.x, sh);
+  }
+}
+
+// out[e,h] = <src_feat[src[e],h,:], dst_feat[dst[e],(h),:]>; one warp per edge, the lanes of a
+// head add their products with a shuffle tree.
+template <typename IdxT>
+__global__ void __launch_bounds__(kThreads) sddmm_coo(const IdxT *src, const IdxT *dst, const float *src_feat,
+                                                     const float *dst_feat, float *out, int64_t n_edge, int feat,
+                                                     int heads, int per_head) {
+  const int lane = threadIdx.x & 31;
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (e >= n_edge) return;
+  const int64_t s = static_cast<int64_t>(src[e]), d = static_cast<int64_t>(dst[e]);
+  for (int h = 0; h < heads; ++h) {
+    const float *pa = src_feat + (s * heads + h) * feat;
+    const float *pb = dst_feat + (per_head ? (d * heads + h) : d) * static_cast<int64_t>(feat);
+    float r = 0.f;
+    for (int i = lane; i < feat; i += 32) r = fmaf(__ldg(pa + i), __ldg(pb + i), r);
+    r = warp_tree_sum(r);
+    if (lane == 0) out[e * heads + h] = r;
+  }
+}
+
+__global__ void edge_value_degree_kernel(const void *ptr, int ptr_bytes, float *out, int64_t n_dst) {
+  const int lane = threadIdx.x & 31;
+  const int64_t d = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (d >= n_dst) return;
+  const int64_t b = load_ptr(ptr, d, ptr_bytes), e = load_ptr(ptr, d + 1, ptr_bytes);
+  if (e <= b) return;
+  const float v = 1.f / static_cast<float>(e - b);
+  for (int64_t i = b + lane; i < e; i += 32) out[i] = v;
+}
+
+template <typename IdxT>
+__global__ void spmv_kernel(const void *ptr, int ptr_bytes, const IdxT *idx, const float *x, float *y,
+                            int64_t n_dst) {
+  const int lane = threadIdx.x & 31;
+  const int64_t d = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (d >= n_dst) return;
+  const int64_t b = load_ptr(ptr, d, ptr_bytes), e = load_ptr(ptr, d + 1, ptr_bytes);
+  float v = 0.f;
+  for (int64_t i = b + lane; i < e; i += 32) v += __ldg(x + static_cast<int64_t>(idx[i]));
+  v = warp_tree_sum(v);
+  if (lane == 0) y[d] = v;
+}
+
+// out[dest[e], :] += x_edge[e, :] (forward) / grad_edge[e, :] = grad_out[dest[e], :] (backward)
+template <typename IdxT, bool BWD>
+__global__ void gather_kernel(const float *in, const IdxT *dest, float *out, int64_t n_edge, int feat) {
+  const int64_t total = n_edge * feat;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = t / feat;
+    const int c = static_cast<int>(t - e * feat);
+    const int64_t v = static_cast<int64_t>(dest[e]);
+    if (BWD)
+      out[t] = in[v * feat + c];
+    else
+      atomicAdd(out + v * feat + c, in[t]);
+  }
+}
+
+int softmax_common(SoftmaxArgs &a, const void *ptr, const void *idx, int ptr_bytes, int idx_bytes, int64_t n_dst,
+                   int64_t nnz, int heads, void *workspace, size_t ws_bytes, const char *who) {
+  CXG_REQUIRE(n_dst >= 0 && nnz >= 0 && heads > 0, CXG_EINVAL, "%s: bad sizes", who);
+  CXG_REQUIRE((ptr_bytes == 4 || ptr_bytes == 8) && (idx_bytes == 4 || idx_bytes == 8), CXG_EINVAL,
+              "%s: index widths %d/%d", who, ptr_bytes, idx_bytes);
+  const int64_t max_heavy = nnz / kHeavyRow + 1;
+  const size_t need = 256 + static_cast<size_t>(max_heavy) * sizeof(int64_t);
+  CXG_REQUIRE(workspace != nullptr && ws_bytes >= need, CXG_EWORKSPACE, "%s: workspace %zu bytes, need %zu", who,
+              ws_bytes, need);
+  CXG_REQUIRE(max_heavy <= INT32_MAX, CXG_ELIMIT, "%s: too many long rows", who);
+  a.ptr = ptr, a.idx = idx, a.n_dst = n_dst, a.heads = heads, a.ptr_bytes = ptr_bytes;
+  a.hdr = reinterpret_cast<int32_t *>(workspace);
+  a.heavy = reinterpret_cast<int64_t *>(reinterpret_cast<char *>(workspace) + 256);
+  a.max_heavy = static_cast<int>(max_heavy);
+  return CXG_OK;
+}
+
+}  // namespace
+}  // namespace cxg
+
+using namespace cxg;
+
+extern "C" int cxg_edge_softmax_workspace_size(int64_t n_dst, int64_t nnz, size_t *bytes) {
+  CXG_REQUIRE(bytes != nullptr, CXG_ENULL, "cxg_edge_softmax_workspace_size: bytes is NULL");
+  CXG_REQUIRE(n_dst >= 0 && nnz >= 0, CXG_EINVAL, "cxg_edge_softmax_workspace_size: bad sizes");
+  *bytes = 256 + static_cast<size_t>(nnz / kHeavyRow + 1) * sizeof(int64_t);
+  return CXG_OK;
+}
+
+extern "C" int cxg_edge_softmax_forward(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
+                                        const float *att_dst, const float *att_src, float *out, uint8_t *mask,
+                                        int64_t n_dst, int64_t nnz, int heads, float slope, void *workspace,
+                                        size_t workspace_bytes, void *stream) {
+  SoftmaxArgs a = {};
+  int rc = softmax_common(a, ptr, idx, ptr_bytes, idx_bytes, n_dst, nnz, heads, workspace, workspace_bytes,
+                          "cxg_edge_softmax_forward");
+  if (rc != CXG_OK) return rc;
+  if (n_dst == 0 || nnz == 0) return CXG_OK;
+  CXG_REQUIRE(ptr && idx && att_dst && att_src && out && mask, CXG_ENULL, "cxg_edge_softmax_forward: NULL argument");
+  a.att_dst = att_dst, a.att_src = att_src, a.out = out, a.mask = mask, a.slope = slope;
+  cudaStream_t st = as_stream(stream);
+  if (cudaMemsetAsync(a.hdr, 0, 256, st) != cudaSuccess) return check_launch("cxg_edge_softmax_forward: memset");
+  const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
+  if (idx_bytes == 8) {
+    edge_softmax_rows<int64_t, false><<<grid, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int64_t, false><<<kNumSM, kThreads, 0, st>>>(a);
+  } else {
+    edge_softmax_rows<int32_t, false><<<grid, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int32_t, false><<<kNumSM, kThreads, 0, st>>>(a);
+  }
+  count_launches(2);
+  return check_launch("cxg_edge_softmax_forward");
+}
+
+extern "C" int cxg_edge_softmax_backward(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
+                                         const float *grad, const uint8_t *mask, const float *out, float *grad_dst,
+                                         float *grad_src, int64_t n_dst, int64_t nnz, int heads, float slope,
+                                         void *workspace, size_t workspace_bytes, void *stream) {
+  SoftmaxArgs a = {};
+  int rc = softmax_common(a, ptr, idx, ptr_bytes, idx_bytes, n_dst, nnz, heads, workspace, workspace_bytes,
+                          "cxg_edge_softmax_backward");
+  if (rc != CXG_OK) return rc;
+  if (n_dst == 0 || nnz == 0) return CXG_OK;
+  CXG_REQUIRE(ptr && idx && grad && mask && out && grad_dst && grad_src, CXG_ENULL,
+              "cxg_edge_softmax_backward: NULL argument");
+  a.grad = grad, a.mask = const_cast<uint8_t *>(mask), a.out = const_cast<float *>(out);
+  a.grad_dst = grad_dst, a.grad_src = grad_src, a.slope = slope;
+  cudaStream_t st = as_stream(stream);
+  if (cudaMemsetAsync(a.hdr, 0, 256, st) != cudaSuccess) return check_launch("cxg_edge_softmax_backward: memset");
+  const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
+  if (idx_bytes == 8) {
+    edge_softmax_rows<int64_t, true><<<grid, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int64_t, true><<<kNumSM, kThreads, 0, st>>>(a);
+  } else {
+    edge_softmax_rows<int32_t, true><<<grid, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int32_t, true><<<kNumSM, kThreads, 0, st>>>(a);
+  }
+  count_launches(2);
+  return check_launch("cxg_edge_softmax_backward");
+}
+
+extern "C" int cxg_sddmm_coo(const void *src, const void *dst, int idx_bytes, const float *src_feat,
+                             const float *dst_feat, float *out, int64_t n_edge, int feat, int heads,
+                             int dst_per_head, void *stream) {
+  CXG_REQUIRE(n_edge >= 0 && feat > 0 && heads > 0, CXG_EINVAL, "cxg_sddmm_coo: bad sizes");
+  CXG_REQUIRE(idx_bytes == 4 || idx_bytes == 8, CXG_EINVAL, "cxg_sddmm_coo: idx_bytes %d", idx_bytes);
+  if (n_edge == 0) return CXG_OK;
+  CXG_REQUIRE(src && dst && src_feat && dst_feat && out, CXG_ENULL, "cxg_sddmm_coo: NULL argument");
+  const unsigned grid = static_cast<unsigned>((n_edge + kWarps - 1) / kWarps);
+  cudaStream_t st = as_stream(stream);
+  if (idx_bytes == 8)
+    sddmm_coo<int64_t><<<grid, kThreads, 0, st>>>(static_cast<const int64_t *>(src), static_cast<const int64_t *>(dst),
+                                                  src_feat, dst_feat, out, n_edge, feat, heads, dst_per_head);
+  else
+    sddmm_coo<int32_t><<<grid, kThreads, 0, st>>>(static_cast<const int32_t *>(src), static_cast<const int32_t *>(dst),
+                                                  src_feat, dst_feat, out, n_edge, feat, heads, dst_per_head);
+  count_launches(1);
+  return check_launch("cxg_sddmm_coo");
+}
+
+extern "C" int cxg_edge_value_degree(const void *ptr, int ptr_bytes, float *out, int64_t n_dst, void *stream) {
+  CXG_REQUIRE(n_dst >= 0 && (ptr_bytes == 4 || ptr_bytes == 8), CXG_EINVAL, "cxg_edge_value_degree: bad arguments");
+  if (n_dst == 0) return CXG_OK;
+  CXG_REQUIRE(ptr && out, CXG_ENULL, "cxg_edge_value_degree: NULL argument");
+  const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
+  edge_value_degree_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(ptr, ptr_bytes, out, n_dst);
+  count_launches(1);
+  return check_launch("cxg_edge_value_degree");
+}
+
+extern "C" int cxg_spmv_csr(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes, const float *x, float *y,
+                            int64_t n_dst, void *stream) {
+  CXG_REQUIRE(n_dst >= 0 && (ptr_bytes == 4 || ptr_bytes == 8) && (idx_bytes == 4 || idx_bytes == 8), CXG_EINVAL,
+              "cxg_spmv_csr: bad arguments");
+  if (n_dst == 0) return CXG_OK;
+  CXG_REQUIRE(ptr && idx && x && y, CXG_ENULL, "cxg_spmv_csr: NULL argument");
+  const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
+  if (idx_bytes == 8)
+    spmv_kernel<int64_t><<<grid, kThreads, 0, as_stream(stream)>>>(ptr, ptr_bytes, static_cast<const int64_t *>(idx), x,
+                                                                  y, n_dst);
+  else
+    spmv_kernel<int32_t><<<grid, kThreads, 0, as_stream(stream)>>>(ptr, ptr_bytes, static_cast<const int32_t *>(idx), x,
+                                                                  y, n_dst);
+  count_launches(1);
+  return check_launch("cxg_spmv_csr");
+}
+
+extern "C" int cxg_gather_edges(const float *in, const void *dest, int idx_bytes, float *out, int64_t n_edge, int feat,
+                                int backward, void *stream) {
+  CXG_REQUIRE(n_edge >= 0 && feat > 0 && (idx_bytes == 4 || idx_bytes == 8), CXG_EINVAL,
+              "cxg_gather_edges: bad arguments");
+  if (n_edge == 0) return CXG_OK;
+  CXG_REQUIRE(in && dest && out, CXG_ENULL, "cxg_gather_edges: NULL argument");
+  const int64_t total = n_edge * feat;
+  const int64_t want = (total + kThreads - 1) / kThreads;
+  const unsigned grid = static_cast<unsigned>(want < kNumSM * 32 ? want : kNumSM * 32);
+  cudaStream_t st = as_stream(stream);
+#define CXG_GATHER(I, B) \
+  gather_kernel<I, B><<<grid, kThreads, 0, st>>>(in, static_cast<const I *>(dest), out, n_edge, feat)
+  if (idx_bytes == 8) {
+    if (backward)
+      CXG_GATHER(int64_t, true);
+    else
+      CXG_GATHER(int64_t, false);
+  } else {
+    if (backward)
+      CXG_GATHER(int32_t, true);
+    else
+      CXG_GATHER(int32_t, false);
+  }
+#undef CXG_GATHER
+  count_launches(1);
+  return check_launch("cxg_gather_edges");
+}

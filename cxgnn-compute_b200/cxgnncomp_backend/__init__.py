@@ -406,3 +406,144 @@ def aggr_rel(x, ptr, idx, etype, num_node, num_rel):
     relation; etype is int32 (binding.cpp:45, rel_spmm.cu:8-70)."""
     _cuda(etype, "etype", (torch.int32,))
     return _AggrRelFunction.apply(x, ptr, idx, etype, num_node, num_rel)
+
+
+# --------------------------------------------------------------------------------------
+# GAT: edge softmax, SDDMM, per-edge helpers
+# --------------------------------------------------------------------------------------
+_f, _int = ctypes.c_float, ctypes.c_int
+_es_ws = _sig("cxg_edge_softmax_workspace_size", [_i64, _i64, ctypes.POINTER(_sz)])
+_es_fwd = _sig("cxg_edge_softmax_forward", [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _i64, _i64, _int, _f, _vp, _sz, _vp])
+_es_bwd = _sig("cxg_edge_softmax_backward",
+               [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _f, _vp, _sz, _vp])
+_sddmm = _sig("cxg_sddmm_coo", [_vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _int, _int, _vp])
+_evd = _sig("cxg_edge_value_degree", [_vp, _int, _vp, _i64, _vp])
+_spmv = _sig("cxg_spmv_csr", [_vp, _vp, _int, _int, _vp, _vp, _i64, _vp])
+_gather = _sig("cxg_gather_edges", [_vp, _vp, _int, _vp, _i64, _int, _int, _vp])
+
+
+def _softmax_ws(device, n_dst, nnz):
+    need = _sz(0)
+    _check(_es_ws(n_dst, nnz, ctypes.byref(need)), "cxg_edge_softmax_workspace_size")
+    return _workspace(device, need.value)
+
+
+class _EdgeSoftmaxFunction(torch.autograd.Function):
+    """EdgeSoftMaxFunction (src/cpp/src/edge_softmax.cu:97-177)."""
+
+    @staticmethod
+    def forward(ctx, ptr, idx, att_dst, att_src, num_edge, relu_l):
+        _cuda(att_dst, "att_dst", (torch.float32,))
+        _cuda(att_src, "att_src", (torch.float32,))
+        _cuda(ptr, "ptr", _INDEX_DTYPES)
+        _cuda(idx, "idx", _INDEX_DTYPES)
+        n_dst, heads = att_dst.shape
+        if ptr.shape[0] < n_dst + 1:
+            raise RuntimeError("ptr has fewer rows than att_dst")
+        out = torch.empty((num_edge, heads), dtype=torch.float32, device=att_dst.device)
+        mask = torch.empty((num_edge, heads), dtype=torch.bool, device=att_dst.device)
+        ws = _softmax_ws(att_dst.device, n_dst, num_edge)
+        with torch.cuda.device(att_dst.device):
+            _check(_es_fwd(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(att_dst), _p(att_src), _p(out),
+                           _p(mask), n_dst, num_edge, heads, float(relu_l), _p(ws), ws.numel(), _stream()),
+                   "cxg_edge_softmax_forward")
+        ctx.save_for_backward(ptr, idx, out, mask)
+        ctx.shape = (n_dst, att_src.shape[0], heads, num_edge, float(relu_l))
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ptr, idx, out, mask = ctx.saved_tensors
+        n_dst, n_src, heads, num_edge, relu_l = ctx.shape
+        grad_out = _cuda(grad_out.contiguous(), "grad", (torch.float32,))
+        gd = torch.zeros((n_dst, heads), dtype=torch.float32, device=out.device)
+        gs = torch.zeros((n_src, heads), dtype=torch.float32, device=out.device)
+        ws = _softmax_ws(out.device, n_dst, num_edge)
+        with torch.cuda.device(out.device):
+            _check(_es_bwd(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(grad_out), _p(mask), _p(out),
+                           _p(gd), _p(gs), n_dst, num_edge, heads, relu_l, _p(ws), ws.numel(), _stream()),
+                   "cxg_edge_softmax_backward")
+        return None, None, gd, gs, None, None
+
+
+def edge_attention(ptr, idx, att_dst, att_src, num_edge, relu_l):
+    """softmax over each destination's edges of LeakyReLU(att_dst[d] + att_src[src]) -> [E, H]
+    (binding.cpp:22-23, keyword arguments ptr, idx, att_dst, att_src, num_edge, relu_l)."""
+    return _EdgeSoftmaxFunction.apply(ptr, idx, att_dst, att_src, int(num_edge), float(relu_l))
+
+
+def edge_value_degree(ptr, num_dst, num_edge):
+    """val[e] = 1 / in-degree of e's destination (binding.cpp:24-25)."""
+    _cuda(ptr, "ptr", _INDEX_DTYPES)
+    out = torch.empty((int(num_edge),), dtype=torch.float32, device=ptr.device)
+    with torch.cuda.device(ptr.device):
+        _check(_evd(_p(ptr), ptr.element_size(), _p(out), int(num_dst), _stream()), "cxg_edge_value_degree")
+    return out
+
+
+def spmv(ptr, idx, x, num_dst):
+    """y[d] = sum of x[idx[e]] over row d (binding.cpp:32)."""
+    _cuda(x, "x", (torch.float32,))
+    y = torch.empty((int(num_dst),), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(_spmv(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(x), _p(y), int(num_dst), _stream()),
+               "cxg_spmv_csr")
+    return y
+
+
+def run_sddmm(src, dst, src_feat, dst_feat, output, num_edge):
+    """output[e, h] = <src_feat[src[e], h, :], dst_feat[dst[e], :]> in place (binding.cpp:77,
+    sddmm_host.cu:4-14). A 3-D dst_feat [N, H, F] selects the head-wise product."""
+    _cuda(src_feat, "src_feat", (torch.float32,))
+    _cuda(dst_feat, "dst_feat", (torch.float32,))
+    _cuda(output, "output", (torch.float32,))
+    _cuda(src, "src", _INDEX_DTYPES)
+    _cuda(dst, "dst", (src.dtype,))
+    heads, feat = src_feat.shape[1], src_feat.shape[-1]
+    with torch.cuda.device(src_feat.device):
+        _check(_sddmm(_p(src), _p(dst), src.element_size(), _p(src_feat), _p(dst_feat), _p(output), int(num_edge), feat,
+                      heads, 1 if dst_feat.dim() == 3 else 0, _stream()), "cxg_sddmm_coo")
+    return None
+
+
+def run_sddmm_vertex_centric(ptr, idx, src_feat, dst_feat, num_node, *tuner_args):
+    """CSR form of run_sddmm: the destination of edge e is its row (sddmm_host.cu:16-60); returns [E, H].
+    The tuner's launch integers are ignored."""
+    n = _num_rows(ptr, num_node)
+    deg = (ptr[1:n + 1] - ptr[:n]).long()
+    dst = torch.repeat_interleave(torch.arange(n, device=ptr.device, dtype=idx.dtype), deg)
+    out = torch.zeros((idx.shape[0], src_feat.shape[1]), dtype=torch.float32, device=src_feat.device)
+    run_sddmm(idx, dst, src_feat, dst_feat, out, dst.shape[0])
+    return out
+
+
+class _GatherFunction(torch.autograd.Function):
+    """GatherFunction (src/cpp/src/aggr.cu:395-443)."""
+
+    @staticmethod
+    def forward(ctx, x_edge, dest, num_node):
+        _cuda(x_edge, "input", (torch.float32,))
+        _cuda(dest, "dest", _INDEX_DTYPES)
+        if num_node <= 0:
+            raise RuntimeError("gather: num_node must be positive")
+        ctx.save_for_backward(dest)
+        out = torch.zeros((num_node, x_edge.shape[1]), dtype=torch.float32, device=x_edge.device)
+        with torch.cuda.device(x_edge.device):
+            _check(_gather(_p(x_edge), _p(dest), dest.element_size(), _p(out), dest.shape[0], x_edge.shape[1], 0,
+                           _stream()), "cxg_gather_edges")
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (dest,) = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        g = torch.empty((dest.shape[0], grad_out.shape[1]), dtype=torch.float32, device=grad_out.device)
+        with torch.cuda.device(grad_out.device):
+            _check(_gather(_p(grad_out), _p(dest), dest.element_size(), _p(g), dest.shape[0], grad_out.shape[1], 1,
+                           _stream()), "cxg_gather_edges")
+        return g, None, None
+
+
+def gather(x_edge, dest, num_node):
+    """Scatter-add edge rows to their destination node: out[dest[e]] += x_edge[e] (binding.cpp:21)."""
+    return _GatherFunction.apply(x_edge, dest, int(num_node))

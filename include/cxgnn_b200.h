@@ -141,6 +141,64 @@ int cxg_spmm_csr_backward(const cxg_spmm_desc *desc, const void *dy, float *dx,
                           float *dval, void *stream);
 
 /*
+ * Edge softmax of GAT. For every destination d and head h over the edges e of row d:
+ *   t = att_dst[d,h] + att_src[idx[e],h];  t = max(t, t*slope)      (LeakyReLU)
+ *   out[e,h] = exp(t - max_row t) / sum_row exp(t - max_row t);     mask[e,h] = t > 0
+ * att_dst [n_dst, heads], att_src [n_src, heads], out [nnz, heads] float32, mask
+ * [nnz, heads] bytes. Replaces edge_attention / EdgeSoftMaxFunction::forward and
+ * edge_softmax_fwd (src/cpp/src/edge_softmax.cu:3-42,97-132). Same summation order per
+ * row as the reference for rows of up to 4096 edges; exp is the accurate expf where the
+ * reference uses the fast __expf. Workspace: cxg_edge_softmax_workspace_size bytes.
+ */
+int cxg_edge_softmax_workspace_size(int64_t n_dst, int64_t nnz, size_t *bytes);
+int cxg_edge_softmax_forward(const void *ptr, const void *idx, int ptr_bytes,
+                             int idx_bytes, const float *att_dst,
+                             const float *att_src, float *out, uint8_t *mask,
+                             int64_t n_dst, int64_t nnz, int heads, float slope,
+                             void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Backward of the edge softmax (edge_softmax_bwd, src/cpp/src/edge_softmax.cu:44-95,
+ * 143-170): with s = sum_row out*grad, tmp = out*(grad - s), times slope where mask is 0;
+ * grad_src[idx[e],h] += tmp (atomic); grad_dst[d,h] = sum_row tmp, written only for rows
+ * that have both mask values (it is zero otherwise). grad_dst [n_dst, heads] and grad_src
+ * [n_src, heads] must be zero-filled by the caller, as the reference does.
+ */
+int cxg_edge_softmax_backward(const void *ptr, const void *idx, int ptr_bytes,
+                              int idx_bytes, const float *grad, const uint8_t *mask,
+                              const float *out, float *grad_dst, float *grad_src,
+                              int64_t n_dst, int64_t nnz, int heads, float slope,
+                              void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * SDDMM on an edge list: out[e,h] = <src_feat[src[e],h,:], dst_feat[dst[e],:]>, src_feat
+ * [n_src, heads, feat], out [n_edge, heads]. dst_per_head = 0: dst_feat is [n_dst, feat]
+ * as in run_sddmm / sddmm_multihead (src/cpp/src/sddmm_host.cu:4-14, sddmm_kernel.cu:3-25);
+ * dst_per_head = 1: dst_feat is [n_dst, heads, feat] (the head-wise product that the
+ * gradient of a multi-head SpMM with respect to its edge values needs).
+ */
+int cxg_sddmm_coo(const void *src, const void *dst, int idx_bytes,
+                  const float *src_feat, const float *dst_feat, float *out,
+                  int64_t n_edge, int feat, int heads, int dst_per_head,
+                  void *stream);
+
+/* out[e] = 1 / (edges of e's row): edge_value_degree (src/cpp/src/edge_softmax.cu:186-214). */
+int cxg_edge_value_degree(const void *ptr, int ptr_bytes, float *out, int64_t n_dst,
+                          void *stream);
+
+/* y[d] = sum over row d of x[idx[e]]: spmv (src/cpp/src/edge_softmax.cu:216-244). */
+int cxg_spmv_csr(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
+                 const float *x, float *y, int64_t n_dst, void *stream);
+
+/*
+ * gather / GatherFunction (src/cpp/src/aggr.cu:42-62,395-448). backward = 0:
+ * out[dest[e],:] += in[e,:] (out [n_node, feat] zero-filled by the caller, atomic adds);
+ * backward = 1: out[e,:] = in[dest[e],:].
+ */
+int cxg_gather_edges(const float *in, const void *dest, int idx_bytes, float *out,
+                     int64_t n_edge, int feat, int backward, void *stream);
+
+/*
  * cxg_spmm_csr without a caller-provided workspace. No counterpart in the reference
  * (its kernels need no scratch memory); added for callers that cannot allocate
  * device memory at call time or cannot pass a scratch buffer across their binding:
