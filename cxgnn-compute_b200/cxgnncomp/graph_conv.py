@@ -1,0 +1,366 @@
+"""Layer modules of the aggregation path with the names and forward signatures of the reference
+(cxgnncomp/graph_conv.py). PyG's `Linear` / `glorot` and torch_scatter, which the reference imports, are
+replaced by plain torch (same initialisation: Xavier-uniform weights, zero bias)."""
+import math
+
+import torch
+import torch.nn.functional as F
+from torch.nn import Parameter
+
+import cxgnncomp_backend
+from cxgnncomp_backend import (edge_attention, sage_sum_forward_edge_value, sage_sum_forward, sage_mean_forward,
+                               selective_aggr, selective_aggr_bwd, aggr_rgcn_direct_func)
+
+from .graph_kernel import SpMMValOP
+from .timer import TimerOP
+from .typed_linear import TypedLinearE2EOP
+from .util import global_tuner
+
+
+def glorot(t):
+    """U(-a, a) with a = sqrt(6 / (fan_in + fan_out)) over the last two dimensions (PyG's glorot)."""
+    if t is not None:
+        a = math.sqrt(6.0 / (t.size(-2) + t.size(-1)))
+        t.data.uniform_(-a, a)
+
+
+class AggrOP(torch.autograd.Function):
+    """Sum aggregation through the tuner interface (graph_conv.py:34-77). Like the reference, the backward
+    applies the forward operator to the gradient, which is the transpose only for a symmetric graph with as
+    many destinations as sources; AggrDirectedOP is the general one."""
+
+    @staticmethod
+    def forward(ctx, x, ptr, idx, num_center):
+        ctx.save_for_backward(ptr, idx)
+        ctx.num_center = num_center
+        return global_tuner.tune_graph(num_center, idx.shape[0], x.shape[-1], cxgnncomp_backend.run_spmm_configurable,
+                                       [ptr, idx, x, num_center])
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ptr, idx = ctx.saved_tensors
+        grad = global_tuner.tune_graph(ctx.num_center, idx.shape[0], grad_out.shape[-1],
+                                       cxgnncomp_backend.run_spmm_configurable,
+                                       [ptr, idx, grad_out.contiguous(), ctx.num_center])
+        return grad, None, None, None
+
+
+class AggrDirectedOP(torch.autograd.Function):
+    """Sum aggregation with the true transpose as backward (graph_conv.py:80-114)."""
+
+    @staticmethod
+    def forward(ctx, x, ptr, idx, num_center):
+        ctx.save_for_backward(x, ptr, idx)
+        ctx.num_center = num_center
+        return global_tuner.tune_graph(num_center, idx.shape[0], x.shape[-1], cxgnncomp_backend.run_spmm_configurable,
+                                       [ptr, idx, x, num_center])
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, ptr, idx = ctx.saved_tensors
+        grad = global_tuner.tune_graph(ctx.num_center, idx.shape[0], grad_out.shape[-1],
+                                       cxgnncomp_backend.run_spmm_configurable_bwd,
+                                       [ptr, idx, x, grad_out.contiguous(), ctx.num_center])
+        return grad, None, None, None
+
+
+class MySageConv(torch.nn.Module):
+    """GraphSAGE, mean aggregator (graph_conv.py:117-159)."""
+
+    def __init__(self, in_channels, hidden_channels, root_weight=True, bias=True):
+        super().__init__()
+        self.in_channels = in_channels
+        self.hidden_channels = hidden_channels
+        self.root_weight = root_weight
+        self.lin_l = torch.nn.Linear(in_channels, hidden_channels, bias=bias)
+        if self.root_weight:
+            self.lin_r = torch.nn.Linear(in_channels, hidden_channels, bias=False)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        self.lin_l.reset_parameters()
+        if self.root_weight:
+            self.lin_r.reset_parameters()
+
+    def forward(self, x, ptr, idx, num_node):
+        if self.in_channels > self.hidden_channels:
+            out = sage_mean_forward(self.lin_l(x), ptr, idx, num_node)
+        else:
+            out = self.lin_l(sage_mean_forward(x, ptr, idx, num_node))
+        if self.root_weight:
+            out = out + self.lin_r(x[:num_node] if num_node != 0 else x)
+        return out
+
+
+class MyGINConv(torch.nn.Module):
+    """GIN with a mean aggregate, as the reference writes it (graph_conv.py:162-181)."""
+
+    def __init__(self, in_channels, hidden_channels):
+        super().__init__()
+        self.in_channels = in_channels
+        self.hidden_channels = hidden_channels
+        self.nn = torch.nn.Linear(in_channels, hidden_channels, bias=False)
+        self.init_eps = 0.2
+        self.eps = torch.nn.Parameter(torch.Tensor([self.init_eps]))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        self.nn.reset_parameters()
+        self.eps.data.fill_(self.init_eps)
+
+    def forward(self, x, ptr, idx, num_node):
+        out = sage_mean_forward(x, ptr, idx, num_node)
+        out = out + (1 + self.eps) * x[:num_node]
+        return self.nn(out)
+
+
+class RGCNOP(torch.autograd.Function):
+    """Per relation: transform every node, aggregate that relation's edges (graph_conv.py:205-243)."""
+
+    @staticmethod
+    def forward(ctx, x, weights, ptr, idx, rel, num_center):
+        ctx.save_for_backward(x, weights, ptr, idx, rel)
+        output = torch.zeros([num_center, weights.shape[-1]], device=x.device, dtype=x.dtype)
+        for i in range(weights.shape[0]):
+            selective_aggr(torch.mm(x, weights[i]), ptr, idx, (rel == i), output, num_center)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weights, ptr, idx, rel = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        grad_x = torch.zeros_like(x)
+        grad_weights = []
+        for i in range(weights.shape[0]):
+            g = torch.zeros([x.shape[0], grad_out.shape[-1]], device=x.device)
+            selective_aggr_bwd(grad_out, ptr, idx, (rel == i), g, grad_out.shape[0])
+            grad_x += torch.mm(g, weights[i].t())
+            grad_weights.append(torch.mm(x.t(), g))
+        return grad_x, torch.stack(grad_weights), None, None, None, None
+
+
+def RGCNOP_sorted(x, weights, src, dst, num_feat_per_rel, num_center):
+    """Edges pre-sorted by relation: per relation F.linear + index_add_ (graph_conv.py:246-257)."""
+    output = torch.zeros([num_center, weights.shape[-1]], device=x.device, dtype=x.dtype)
+    cnt = 0
+    for i in range(weights.shape[0]):
+        k = int(num_feat_per_rel[i])
+        s, d = src[cnt:cnt + k], dst[cnt:cnt + k]
+        cnt += k
+        output.index_add_(0, d, F.linear(x[s], weights[i].T))
+    return output
+
+
+class RGCNOP2(torch.autograd.Function):
+    """Aggregate per relation, then transform (graph_conv.py:260-291)."""
+
+    @staticmethod
+    def forward(ctx, x, weights, ptr, idx, rel, num_center):
+        output = torch.zeros([num_center, weights.shape[-1]], device=x.device, dtype=x.dtype)
+        aggr_outputs = []
+        for i in range(weights.shape[0]):
+            aggr = torch.zeros([num_center, weights.shape[-2]], device=x.device, dtype=x.dtype)
+            selective_aggr(x, ptr, idx, (rel == i), aggr, num_center)
+            output += torch.mm(aggr, weights[i])
+            aggr_outputs.append(aggr)
+        ctx.save_for_backward(x, weights, ptr, idx, rel, torch.stack(aggr_outputs))
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weights, ptr, idx, rel, aggr_outputs = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        grad_x = torch.zeros_like(x)
+        grad_weights = []
+        for i in range(weights.shape[0]):
+            grad_weights.append(torch.mm(aggr_outputs[i].t(), grad_out))
+            selective_aggr_bwd(torch.mm(grad_out, weights[i].t()), ptr, idx, (rel == i), grad_x, grad_out.shape[0])
+        return grad_x, torch.stack(grad_weights), None, None, None, None
+
+
+class RGCNOP3(torch.autograd.Function):
+    """Fused per-edge x . W[rel] aggregation, forward only (graph_conv.py:294-306; the reference's backward
+    returns random tensors, here it raises)."""
+
+    @staticmethod
+    def forward(ctx, x, weights, ptr, idx, rel, num_center):
+        return aggr_rgcn_direct_func(x, ptr, idx, weights, rel.int(), num_center)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        raise NotImplementedError("RGCNOP3 has no gradient in the reference")
+
+
+def run_rgcn4(x, ptr, idx, edge_types, linear, num_center, num_edge, preproccessed):
+    """Gather the source row of every edge, typed matmul per edge, segment-sum into the destinations
+    (graph_conv.py:309-326)."""
+    x_idxed = x[idx[:num_edge]]
+    out = TypedLinearE2EOP.apply(x_idxed, linear, edge_types, preproccessed)
+    new_idx = torch.arange(0, num_edge, device=x_idxed.device, dtype=idx.dtype)
+    return AggrDirectedOP.apply(out, ptr, new_idx, num_center)
+
+
+class MyRGCNConv(torch.nn.Module):
+    """RGCN layer: y[d] = (1 / deg d) * sum over edges of x[src] W[rel] (graph_conv.py:329-378). `norm`
+    selects the reference's total in-degree ("total", default) or the per-(destination, relation) degree
+    ("relation"); destinations without edges give 0 (the reference divides 0 by 0 there)."""
+
+    def __init__(self, in_channels, hidden_channels, num_rel, norm="total"):
+        super().__init__()
+        assert num_rel > 0
+        self.in_channels = in_channels
+        self.hidden_channels = hidden_channels
+        self.num_rel = num_rel
+        self.norm = norm
+        self.linear = torch.nn.Parameter(torch.empty(num_rel, in_channels, hidden_channels))
+        self.register_parameter("rel_weight", self.linear)
+        self.single_linear = torch.nn.Linear(in_channels, hidden_channels)
+        self.reset_parameters()
+        self.preprocessed = []
+
+    def reset_parameters(self):
+        glorot(self.linear)
+        self.single_linear.reset_parameters()
+
+    def forward(self, x, ptr, idx, edge_types, num_node):
+        if idx.shape[0] > 1e8:
+            return RGCNOP.apply(x, self.linear, ptr, idx, edge_types, num_node)
+        if len(self.preprocessed) == 0:
+            self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)
+        num_edge = edge_types.shape[0]
+        deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(x.dtype)
+        if self.norm == "relation":
+            # per-(destination, relation) degree: scale every edge's row before the segment sum
+            dst = torch.repeat_interleave(torch.arange(num_node, device=x.device), ptr[1:num_node + 1] - ptr[:num_node])
+            key = dst * self.num_rel + edge_types
+            cnt = torch.bincount(key, minlength=num_node * self.num_rel).to(x.dtype)
+            x_idxed = x[idx[:num_edge]]
+            out = TypedLinearE2EOP.apply(x_idxed, self.linear, edge_types, self.preprocessed)
+            out = out / cnt[key].unsqueeze(-1)
+            new_idx = torch.arange(0, num_edge, device=x.device, dtype=idx.dtype)
+            return AggrDirectedOP.apply(out, ptr, new_idx, num_node)
+        out = run_rgcn4(x, ptr, idx, edge_types, self.linear, num_node, num_edge, self.preprocessed)
+        return out / deg.unsqueeze(-1)
+
+
+class MyGATConv(torch.nn.Module):
+    """GAT layer (graph_conv.py:381-555): linear, per-head scores, edge softmax, weighted aggregation."""
+
+    def __init__(self, in_channels, out_channels, heads=1, concat=False, negative_slope=0.2, dropout=0.0, bias=True,
+                 layer=-1):
+        super().__init__()
+        assert heads > 0
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.heads = heads
+        self.concat = concat
+        self.negative_slope = negative_slope
+        self.dropout = dropout
+        self.layer = layer
+        self.lin_src = Parameter(torch.empty(heads * out_channels, in_channels))
+        self.att_src = Parameter(torch.empty(1, heads, out_channels))
+        self.att_dst = Parameter(torch.empty(1, heads, out_channels))
+        if bias:
+            self.bias = Parameter(torch.empty(heads * out_channels if concat else out_channels))
+        else:
+            self.bias = None
+        self.edge_softmax_schedule = "fused"
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        glorot(self.lin_src)
+        glorot(self.att_src)
+        glorot(self.att_dst)
+        if self.bias is not None:
+            self.bias.data.fill_(0)
+
+    def edge_softmax_fused(self, ptr, idx, att_src, att_dst, num_edge, relu_l):
+        return edge_attention(ptr=ptr, idx=idx, att_src=att_src, att_dst=att_dst, num_edge=num_edge, relu_l=relu_l)
+
+    def edge_softmax_opwise(self, ptr, idx, att_src, att_dst, num_edge, relu_l):
+        """Op-by-op softmax in torch (graph_conv.py:437-448; torch_scatter's gather_csr / segment_csr written
+        with repeat_interleave / segment_reduce)."""
+        deg = ptr[1:] - ptr[:-1]
+        alpha = F.leaky_relu(torch.index_select(att_src, 0, idx[:num_edge]) +
+                             torch.repeat_interleave(att_dst[:deg.shape[0]], deg, dim=0), relu_l)
+        with torch.no_grad():
+            amax = torch.repeat_interleave(torch.segment_reduce(alpha, "max", lengths=deg, unsafe=True), deg, dim=0)
+        alpha = torch.exp(alpha - amax)
+        asum = torch.repeat_interleave(torch.segment_reduce(alpha, "sum", lengths=deg, unsafe=True) + 1e-16, deg, dim=0)
+        return alpha / asum
+
+    def edge_softmax(self, ptr, idx, att_src, att_dst, num_edge, relu_l):
+        if self.edge_softmax_schedule == "fused":
+            return self.edge_softmax_fused(ptr, idx, att_src, att_dst, num_edge, relu_l)
+        return self.edge_softmax_opwise(ptr, idx, att_src, att_dst, num_edge, relu_l)
+
+    def forward_many(self, x, ptr, idx, num_dst, num_src, num_edge):
+        H, C = self.heads, self.out_channels
+        assert x.dim() == 2
+        x_src = x_dst = F.linear(x[:num_src], self.lin_src).view(-1, H, C)
+        alpha_src = (x_src * self.att_src).sum(dim=-1).view(-1, H)
+        alpha_dst = (x_dst[:num_dst] * self.att_dst).sum(dim=-1).view(-1, H)
+        edge_value = self.edge_softmax(ptr=ptr, idx=idx, att_src=alpha_src.contiguous(), att_dst=alpha_dst.contiguous(),
+                                       num_edge=num_edge, relu_l=self.negative_slope)
+        if self.heads == 1:
+            out = sage_sum_forward_edge_value(x_src.contiguous(), ptr, idx, edge_value.squeeze(-1).contiguous(), num_dst)
+        else:
+            out = SpMMValOP.apply(x_src.contiguous(), ptr, idx, edge_value, num_dst)
+        if self.concat:
+            out = out.view(-1, H * C)
+        elif out.dim() == 3:
+            out = out.mean(dim=1)
+        return out + self.bias if self.bias is not None else out
+
+    def forward_1(self, x, ptr, idx, num_dst, num_src, num_edge):
+        w = self.lin_src.T.view(-1, self.heads, self.out_channels)
+        alpha_src = torch.einsum("mn,nho,ho->mh", x, w, self.att_src.squeeze(0)).view(-1, self.heads)
+        alpha_dst = torch.einsum("mn,nho,ho->mh", x[:num_dst], w, self.att_dst.squeeze(0)).view(-1, self.heads)
+        edge_value = self.edge_softmax(ptr=ptr, idx=idx, att_src=alpha_src.contiguous(), att_dst=alpha_dst.contiguous(),
+                                       num_edge=num_edge, relu_l=self.negative_slope).reshape(-1)
+        if self.out_channels < self.in_channels:
+            out = sage_sum_forward_edge_value(torch.mm(x, self.lin_src.T), ptr, idx, edge_value, num_dst)
+        else:
+            out = torch.mm(sage_sum_forward_edge_value(x, ptr, idx, edge_value, num_dst), self.lin_src.T)
+        return out + self.bias if self.bias is not None else out
+
+    def forward(self, x, ptr, idx, num_dst, num_src, num_edge):
+        ptr = ptr[:num_dst + 1]
+        idx = idx[:num_edge]
+        if self.heads == 1:
+            return self.forward_1(x, ptr, idx, num_dst, num_src, num_edge)
+        return self.forward_many(x, ptr, idx, num_dst, num_src, num_edge)
+
+
+class MyGCNConv(torch.nn.Module):
+    """GCN layer (graph_conv.py:558-625): linear before the aggregation when it shrinks the features, sum
+    aggregation (AggrOP) or, with normalize=True, 1/in-degree edge weights."""
+
+    def __init__(self, in_channels, out_channels, normalize=False, bias=True):
+        super().__init__()
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.normalize = normalize
+        self.lin = torch.nn.Linear(in_channels, out_channels, bias=False)
+        self.bias = torch.nn.Parameter(torch.empty(out_channels)) if bias else None
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        glorot(self.lin.weight)
+        if self.bias is not None:
+            self.bias.data.fill_(0)
+
+    def gcn_norm(self, ptr, idx):
+        """edge value = 1 / in-degree of the edge's destination (graph_conv.py:587-596)."""
+        return cxgnncomp_backend.edge_value_degree(ptr, ptr.shape[0] - 1, idx.shape[0])
+
+    def forward(self, x, ptr, idx, num_node):
+        mm_before = self.in_channels > self.out_channels
+        out = self.lin(x) if mm_before else x
+        if self.normalize:
+            out = sage_sum_forward_edge_value(out, ptr, idx, self.gcn_norm(ptr, idx), num_node)
+        else:
+            out = AggrOP.apply(out, ptr, idx, num_node)
+        if not mm_before:
+            out = self.lin(out)
+        return out + self.bias if self.bias is not None else out

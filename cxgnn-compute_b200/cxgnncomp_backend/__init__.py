@@ -547,3 +547,7 @@ class _GatherFunction(torch.autograd.Function):
 def gather(x_edge, dest, num_node):
     """Scatter-add edge rows to their destination node: out[dest[e]] += x_edge[e] (binding.cpp:21)."""
     return _GatherFunction.apply(x_edge, dest, int(num_node))
+
+
+from ._rgcn import (pad_rel, pad_rel_idx, typed_linear, typed_linear_s2e, typed_linear_s2d,  # noqa: E402,F401
+                    aggr_rgcn_direct_func, rel_schedule, typed_matmul_raw)

@@ -1,0 +1,142 @@
+"""Relational (RGCN) part of the `cxgnncomp_backend` surface: pad_rel, typed_linear*, aggr_rgcn_direct_func,
+rel_schedule and the typed matmul entry used by `cxgnncomp.codegen.typed_matmul`
+(reference: init_rel_spmm / init_compute in src/cpp/python_bindings/binding.cpp:28,44-55)."""
+import ctypes
+
+import torch
+
+from . import (_check, _cuda, _p, _stream, _sig, _workspace, _vp, _i64, _sz, _num_rows, _INDEX_DTYPES, CXG_F32,
+               CXG_BF16)
+
+_int = ctypes.c_int
+_pad = _sig("cxg_pad_rel", [_vp, _vp, _vp, _int, _int, _i64, _vp])
+_tl = _sig("cxg_typed_linear", [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp])
+_direct = _sig("cxg_rgcn_direct", [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _i64, _int, _int, _vp])
+_relsched = _sig("cxg_rel_schedule_host", [_vp, _vp, _vp, _i64, _vp, _int, _int, _vp, _vp, _vp, _vp, _vp])
+_tmm_ws = _sig("cxg_typed_matmul_workspace_size", [_int, _int, _int, _int, ctypes.POINTER(_sz)])
+_tmm = _sig("cxg_typed_matmul", [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _int, _int, _vp, _sz,
+                                 _vp])
+
+
+def pad_rel(rel, count, thres, num_rel, base):
+    """In place: fill the num_rel*(thres-1) pad slots of `rel` behind position `base` (binding.cpp:51)."""
+    _cuda(rel, "rel", (torch.int64,))
+    _cuda(count, "count", (torch.int64,))
+    if rel.shape[0] < base + num_rel * (thres - 1):
+        raise RuntimeError("pad_rel: rel is shorter than base + num_rel * (thres - 1)")
+    with torch.cuda.device(rel.device):
+        _check(_pad(_p(rel), None, _p(count), int(thres), int(num_rel), int(base), _stream()), "cxg_pad_rel")
+
+
+def pad_rel_idx(rel, idx, count, thres, num_rel, base):
+    """pad_rel that also writes -1 into the pad slots of `idx` (binding.cpp:52)."""
+    _cuda(rel, "rel", (torch.int64,))
+    _cuda(idx, "idx", (torch.int64,))
+    _cuda(count, "count", (torch.int64,))
+    if min(rel.shape[0], idx.shape[0]) < base + num_rel * (thres - 1):
+        raise RuntimeError("pad_rel_idx: rel / idx shorter than base + num_rel * (thres - 1)")
+    with torch.cuda.device(rel.device):
+        _check(_pad(_p(rel), _p(idx), _p(count), int(thres), int(num_rel), int(base), _stream()), "cxg_pad_rel")
+
+
+def _typed_linear(x, w, out, types, src, dst, num):
+    _cuda(x, "x", (torch.float32,))
+    _cuda(w, "weights", (torch.float32,))
+    _cuda(out, "output", (torch.float32,))
+    _cuda(types, "types", (torch.int32,))
+    if src is not None:
+        _cuda(src, "src", (torch.int64,))
+    if dst is not None:
+        _cuda(dst, "dst", (torch.int64,))
+    if w.dim() != 3 or w.shape[1] != x.shape[1] or w.shape[2] != out.shape[1]:
+        raise RuntimeError("typed_linear: weights must be [R, in_feat, out_feat]")
+    with torch.cuda.device(x.device):
+        _check(_tl(_p(x), _p(w), _p(out), _p(types), _p(src), _p(dst), int(num), x.shape[0], x.shape[1], out.shape[1],
+                   w.shape[0], _stream()), "cxg_typed_linear")
+
+
+def typed_linear(x, weights, output, types, in_feat_tile):
+    """output[i] += x[i] @ weights[types[i]] (binding.cpp:48); in_feat_tile is a tiling hint and is ignored."""
+    _typed_linear(x, weights, output, types, None, None, x.shape[0])
+
+
+def typed_linear_s2e(x, weights, output, src_id, types, in_feat_tile):
+    """output[e] += x[src_id[e]] @ weights[types[e]] (binding.cpp:49)."""
+    _typed_linear(x, weights, output, types, src_id, None, src_id.shape[0])
+
+
+def typed_linear_s2d(x, weights, output, src_id, dst_id, types, in_feat_tile):
+    """output[dst_id[e]] += x[src_id[e]] @ weights[types[e]], atomic (binding.cpp:50)."""
+    _typed_linear(x, weights, output, types, src_id, dst_id, src_id.shape[0])
+
+
+def aggr_rgcn_direct_func(x, ptr, idx, weights, rel, num_node):
+    """out[d] = sum over row d of x[idx[e]] @ weights[rel[e]]; rel int32 (binding.cpp:47)."""
+    _cuda(x, "x", (torch.float32,))
+    _cuda(weights, "weights", (torch.float32,))
+    _cuda(rel, "rel", (torch.int32,))
+    _cuda(ptr, "ptr", _INDEX_DTYPES)
+    _cuda(idx, "idx", _INDEX_DTYPES)
+    if weights.dim() != 3 or weights.shape[1] != x.shape[1]:
+        raise RuntimeError(f"feat_len weight size {x.shape[1]} {weights.shape[1]}")
+    n = _num_rows(ptr, num_node)
+    out = torch.empty((n, weights.shape[2]), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(_direct(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(rel), _p(x), _p(weights), _p(out), n,
+                       x.shape[1], weights.shape[2], _stream()), "cxg_rgcn_direct")
+    return out
+
+
+def rel_schedule(csr_ptr, csr_idx, rel, num_node_in_layer, num_rel):
+    """Per-relation sub-graphs from CPU tensors (binding.cpp:28, schedule.cu:5-63): returns
+    [ptr_0, idx_0, target_0, ..., ptr_{R-1}, idx_{R-1}, target_{R-1}, rows_in_layer[R, L]], all int64 on the CPU."""
+    for t_, name, dt in ((csr_ptr, "csr_ptr", torch.int64), (csr_idx, "csr_idx", torch.int64), (rel, "rel", torch.int32),
+                         (num_node_in_layer, "num_node_in_layer", torch.int64)):
+        if t_.is_cuda or t_.dtype != dt or not t_.is_contiguous():
+            raise RuntimeError(f"rel_schedule: {name} must be a contiguous CPU tensor of {dt}")
+    n = csr_ptr.shape[0] - 1
+    nnz = int(csr_ptr[n])
+    layers = num_node_in_layer.shape[0] - 1
+    sp = torch.zeros((num_rel, n + 1), dtype=torch.int64)
+    si = torch.zeros((num_rel, max(nnz, 1)), dtype=torch.int64)
+    st = torch.zeros((num_rel, max(n, 1)), dtype=torch.int64)
+    counts = torch.zeros((num_rel, 2), dtype=torch.int64)
+    in_layer = torch.zeros((num_rel, max(layers, 1)), dtype=torch.int64)
+    _check(_relsched(csr_ptr.data_ptr(), csr_idx.data_ptr(), rel.data_ptr(), n, num_node_in_layer.data_ptr(), layers,
+                     num_rel, sp.data_ptr(), si.data_ptr(), st.data_ptr(), counts.data_ptr(), in_layer.data_ptr()),
+           "cxg_rel_schedule_host")
+    out = []
+    for r in range(num_rel):
+        rows, edges = int(counts[r, 0]), int(counts[r, 1])
+        # the host routine writes rows of stride nnz / n / n+1; slice each relation's part
+        out += [sp[r, :rows + 1].clone(), si.view(num_rel, -1)[r, :edges].clone(), st[r, :rows].clone()]
+    out.append(in_layer[:, :layers].clone())
+    return out
+
+
+def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None, seq_output=False, exact=False,
+                     out_rows=None):
+    """C = typed matmul through the C ABI. a [*, K], b [R, K, N], rel int64 per position; see cxg_typed_matmul.
+    C has `out_rows` rows (default: m_positions for sequential output, else m_valid)."""
+    _cuda(a, "a", (torch.float32, torch.bfloat16))
+    _cuda(b, "b", (a.dtype,))
+    _cuda(rel, "rel", (torch.int64,))
+    if src_idx is not None:
+        _cuda(src_idx, "src_idx", (torch.int64,))
+    if dst_idx is not None:
+        _cuda(dst_idx, "dst_idx", (torch.int64,))
+    num_rel, k, n = b.shape
+    if a.shape[1] != k:
+        raise RuntimeError("incompatible dimensions")
+    if out_rows is None:
+        out_rows = m_positions if (seq_output or src_idx is None) else m_valid
+    # rows that no position writes are left unset, like the reference's torch.empty output
+    c = torch.empty((int(out_rows), n), dtype=a.dtype, device=a.device)
+    dtype = CXG_F32 if a.dtype == torch.float32 else CXG_BF16
+    need = _sz(0)
+    _check(_tmm_ws(num_rel, k, n, dtype, ctypes.byref(need)), "cxg_typed_matmul_workspace_size")
+    ws = _workspace(a.device, need.value)
+    with torch.cuda.device(a.device):
+        _check(_tmm(_p(a), _p(b), _p(c), _p(rel), _p(src_idx), _p(dst_idx), int(m_positions), int(m_valid), k, n, num_rel,
+                    dtype, 0 if exact else 1, 1 if seq_output else 0, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")
+    return c

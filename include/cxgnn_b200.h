@@ -199,6 +199,67 @@ int cxg_gather_edges(const float *in, const void *dest, int idx_bytes, float *ou
                      int64_t n_edge, int feat, int backward, void *stream);
 
 /*
+ * Relation-bucket padding: pad_rel / pad_rel_idx (src/cpp/src/stitch_kernel.cu:3-53).
+ * rel (int64, length base + num_rel*(thres-1)) holds the relation of every item in
+ * rel[0..base); pad slot t belongs to relation t/(thres-1) and is turned into a member of it
+ * while that relation's count is short of a multiple of thres, else into the dummy relation
+ * num_rel. idx (optional, same length) gets -1 in every pad slot. count: int64 [num_rel].
+ */
+int cxg_pad_rel(int64_t *rel, int64_t *idx, const int64_t *count, int thres,
+                int num_rel, int64_t base, void *stream);
+
+/*
+ * Typed linear, one output row per item, exact fp32 (fma in k order):
+ *   src == NULL:              out[i]      += x[i]      . W[types[i]]   typed_linear
+ *   src != NULL, dst == NULL: out[i]      += x[src[i]] . W[types[i]]   typed_linear_s2e
+ *   src and dst:              out[dst[i]] += x[src[i]] . W[types[i]]   typed_linear_s2d (atomic)
+ * (run_typed_linear{,_s2e,_s2d}, src/cpp/src/rel_spmm.cu:231-358). x [n_rows_x, k],
+ * W [num_rel, k, n], types int32 [num].
+ */
+int cxg_typed_linear(const float *x, const float *w, float *out, const int32_t *types,
+                     const int64_t *src, const int64_t *dst, int64_t num,
+                     int64_t n_rows_x, int k, int n, int num_rel, void *stream);
+
+/*
+ * y[d,:] = sum over row d of x[idx[e],:] . W[rel[e]]: aggr_rgcn_direct_func
+ * (src/cpp/src/rel_spmm.cu:138-181,442-467). rel int32 [nnz], fp32.
+ */
+int cxg_rgcn_direct(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
+                    const int32_t *rel, const float *x, const float *w, float *y,
+                    int64_t n_dst, int k, int n, void *stream);
+
+/*
+ * Per-relation sub-graphs on the host: rel_schedule (src/cpp/src/schedule.cu:5-63).
+ * All pointers are HOST pointers; outputs are caller-allocated, row-major per relation:
+ * sub_ptr [num_rel][n_dst+1], sub_idx [num_rel][nnz], sub_target [num_rel][n_dst],
+ * counts [num_rel][2] = (rows kept, edges kept), n_in_layer [num_rel][num_layer].
+ */
+int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
+                          const int32_t *rel_host, int64_t n_dst,
+                          const int64_t *num_node_in_layer_host, int num_layer,
+                          int num_rel, int64_t *sub_ptr_host, int64_t *sub_idx_host,
+                          int64_t *sub_target_host, int64_t *counts_host,
+                          int64_t *n_in_layer_host);
+
+/*
+ * Typed matmul: C[oc(m),:] = A[ia(m),:] . W[rel[m]] for m in [0, m), where every aligned
+ * block of 128 positions holds one relation (rel[m] >= num_rel marks padding),
+ *   ia(m) = src_idx ? src_idx[m] : m          (positions with ia outside [0, m_valid) are padding)
+ *   oc(m) = dst_idx ? dst_idx[m] : (src_idx && !seq_output ? ia(m) : m).
+ * Replaces typed_matmul and its four Triton kernels (cxgnncomp/codegen/
+ * triton_typed_matmul.py:145-860). A [*, k], W [num_rel, k, n], C [*, n] of dtype (fp32/bf16).
+ * precision 1: tcgen05 tensor cores, fp32 accumulation in tensor memory (bf16 inputs, or fp32
+ * inputs as TF32 like the reference's tl.dot); needs k % 16 == 0 (bf16) / % 8 (fp32), n % 16
+ * == 0, n <= 256. precision 0: exact fp32 fma of every product (no tensor cores), any k, n.
+ */
+int cxg_typed_matmul_workspace_size(int num_rel, int k, int n, int dtype, size_t *bytes);
+int cxg_typed_matmul(const void *a, const void *w, void *c, const int64_t *rel,
+                     const int64_t *src_idx, const int64_t *dst_idx, int64_t m,
+                     int64_t m_valid, int k, int n, int num_rel, int dtype,
+                     int precision, int seq_output, void *workspace,
+                     size_t workspace_bytes, void *stream);
+
+/*
  * cxg_spmm_csr without a caller-provided workspace. No counterpart in the reference
  * (its kernels need no scratch memory); added for callers that cannot allocate
  * device memory at call time or cannot pass a scratch buffer across their binding:

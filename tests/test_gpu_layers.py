@@ -1,0 +1,166 @@
+"""Layer modules (MyGCNConv, MySageConv, MyGINConv, MyGATConv, MyRGCNConv) on the CUDA kernels against the same
+layers written with the torch formulations of the oracle, forward and backward, with identical seeded weights."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from helpers import random_csr, randn, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _sym_graph(n, avg, seed):
+    """Symmetric multigraph with self-loops (AggrOP's backward assumes A == A^T)."""
+    g = torch.Generator().manual_seed(seed)
+    e = n * avg // 2
+    u, v = torch.randint(0, n, (e,), generator=g), torch.randint(0, n, (e,), generator=g)
+    src = torch.cat([u, v, torch.arange(n)])
+    dst = torch.cat([v, u, torch.arange(n)])
+    key = torch.sort(dst * n + src).values
+    ptr = torch.searchsorted(key, torch.arange(n + 1) * n)
+    return ptr, key % n
+
+
+def test_gcn_layer(cuda):
+    import cxgnncomp
+    torch.manual_seed(0)
+    ptr, idx = _sym_graph(300, 8, 1)
+    for cin, cout, norm in [(64, 32, False), (32, 64, False), (48, 48, True)]:
+        conv = cxgnncomp.MyGCNConv(cin, cout, normalize=norm).cuda()
+        x = randn((300, cin), 2)
+        xg = x.cuda().requires_grad_(True)
+        out = conv(xg, ptr.cuda(), idx.cuda(), 300)
+        w, b = conv.lin.weight.detach().cpu(), conv.bias.detach().cpu()
+        xr = x.clone().requires_grad_(True)
+        ev = None
+        if norm:
+            deg = ptr[1:] - ptr[:-1]
+            ev = (1.0 / deg.float()).repeat_interleave(deg)
+        h = F.linear(xr, w) if cin > cout else xr
+        h = oracle.torch_spmm_index_add(h, ptr, idx, 300, edge_val=ev)
+        ref = (h if cin > cout else F.linear(h, w)) + b
+        assert rel_err(out.detach().cpu(), ref.detach()) < 1e-5
+        go = randn(ref.shape, 3)
+        out.backward(go.cuda())
+        ref.backward(go)
+        assert rel_err(xg.grad.cpu(), xr.grad) < 1e-5
+
+
+def test_sage_and_gin_layers(cuda):
+    import cxgnncomp
+    torch.manual_seed(1)
+    ptr, idx = random_csr(200, 260, 7, seed=4, hub=300)
+    p, i = ptr.cuda(), idx.cuda()
+    for cin, cout in [(100, 256), (256, 47)]:
+        conv = cxgnncomp.MySageConv(cin, cout).cuda()
+        x = randn((260, cin), 5)
+        xg = x.cuda().requires_grad_(True)
+        out = conv(xg, p, i, 200)
+        wl, bl, wr = conv.lin_l.weight.detach().cpu(), conv.lin_l.bias.detach().cpu(), conv.lin_r.weight.detach().cpu()
+        xr = x.clone().requires_grad_(True)
+        if cin > cout:
+            ref = oracle.torch_spmm_index_add(F.linear(xr, wl, bl), ptr, idx, 200, mean=True)
+        else:
+            ref = F.linear(oracle.torch_spmm_index_add(xr, ptr, idx, 200, mean=True), wl, bl)
+        ref = ref + F.linear(xr[:200], wr)
+        assert rel_err(out.detach().cpu(), ref.detach()) < 1e-5
+        go = randn(ref.shape, 6)
+        out.backward(go.cuda())
+        ref.backward(go)
+        assert rel_err(xg.grad.cpu(), xr.grad) < 1e-5
+    gin = cxgnncomp.MyGINConv(64, 32).cuda()
+    x = randn((260, 64), 7)
+    out = gin(x.cuda(), p, i, 200)
+    ref = F.linear(oracle.torch_spmm_index_add(x, ptr, idx, 200, mean=True) + 1.2 * x[:200], gin.nn.weight.detach().cpu())
+    assert rel_err(out.detach().cpu(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("heads,concat", [(4, True), (4, False), (1, False)])
+def test_gat_layer(cuda, heads, concat):
+    """Configuration 2 in small: 128 -> heads x 32, LeakyReLU 0.2, softmax per destination, fwd + bwd."""
+    import cxgnncomp
+    torch.manual_seed(2)
+    ptr, idx = random_csr(180, 180, 9, seed=8, hub=500)
+    C = 32
+    conv = cxgnncomp.MyGATConv(128, C, heads=heads, concat=concat).cuda()
+    x = randn((180, 128), 9)
+    xg = x.cuda().requires_grad_(True)
+    out = conv(xg, ptr.cuda(), idx.cuda(), 180, 180, idx.shape[0])
+    W = conv.lin_src.detach().cpu()
+    a_s, a_d, b = conv.att_src.detach().cpu(), conv.att_dst.detach().cpu(), conv.bias.detach().cpu()
+    xr = x.clone().requires_grad_(True)
+    h = F.linear(xr, W).view(-1, heads, C)
+    al_s, al_d = (h * a_s).sum(-1), (h * a_d).sum(-1)
+    ev = oracle.torch_edge_softmax_opwise(ptr, idx, al_s, al_d, idx.shape[0], 0.2)
+    agg = oracle.torch_spmm_index_add(h, ptr, idx, 180, edge_val=ev)
+    ref = (agg.reshape(-1, heads * C) if concat else agg.mean(1)) + b
+    # the reference's own tolerance against PyG's GATConv: atol 1e-4, rtol 1e-3 (test/1-kernels/valid-gat.py:110)
+    assert rel_err(out.detach().cpu(), ref.detach()) < 1e-5
+    go = randn(ref.shape, 10)
+    out.backward(go.cuda())
+    ref.backward(go)
+    assert rel_err(xg.grad.cpu(), xr.grad) < 1e-4
+    # the op-wise schedule gives the same layer
+    conv.edge_softmax_schedule = "opwise"
+    out2 = conv(x.cuda(), ptr.cuda(), idx.cuda(), 180, 180, idx.shape[0])
+    assert rel_err(out2.detach().cpu(), ref.detach()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-3), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("norm", ["total", "relation"])
+def test_rgcn_layer(cuda, dtype, tol, norm):
+    """Configuration 4 in small: 8 relations, 128 -> 64, edges bucketed by relation, typed matmul on the tensor
+    cores (TF32 for fp32 inputs, as the reference's tl.dot), segment sum, degree normalisation."""
+    import cxgnncomp
+    torch.manual_seed(3)
+    R = 8
+    ptr, idx = random_csr(250, 250, 10, seed=11, hub=700, empty_frac=0.05)
+    rel = torch.randint(0, R, (idx.shape[0],), generator=torch.Generator().manual_seed(12))
+    conv = cxgnncomp.MyRGCNConv(128, 64, R, norm=norm).cuda().to(dtype)
+    x = randn((250, 128), 13).to(dtype)
+    xg = x.cuda().requires_grad_(True)
+    out = conv(xg, ptr.cuda(), idx.cuda(), rel.cuda(), 250)
+    W = conv.linear.detach().cpu()
+    per_edge = oracle.typed_linear_f64(x.float(), W.float(), rel, src=idx)
+    dst = oracle.dst_of_edges(ptr)
+    deg = (ptr[1:] - ptr[:-1]).clamp(min=1).double()
+    if norm == "relation":
+        cnt = torch.bincount(dst * R + rel, minlength=250 * R).double()
+        ref = torch.zeros(250, 64, dtype=torch.float64).index_add_(0, dst, per_edge / cnt[dst * R + rel].unsqueeze(-1))
+    else:
+        ref = torch.zeros(250, 64, dtype=torch.float64).index_add_(0, dst, per_edge) / deg.unsqueeze(-1)
+        # the reference's sorted formulation gives the same numbers (typed_linear.py:262-310)
+        assert rel_err(oracle.torch_rgcn_sorted(x.float(), W.float(), ptr, idx, rel, 250) / deg.float().unsqueeze(-1), ref) < 1e-5
+    assert rel_err(out.detach().float().cpu(), ref) < tol
+    if dtype == torch.float32:
+        go = randn(ref.shape, 14)
+        out.backward(go.cuda())
+        # gradient w.r.t. x and W against autograd through the sorted torch formulation
+        xr = x.clone().requires_grad_(True)
+        Wr = W.clone().requires_grad_(True)
+        if norm == "total":
+            r2 = oracle.torch_rgcn_sorted(xr, Wr, ptr, idx, rel, 250) / deg.float().unsqueeze(-1)
+            r2.backward(go)
+            assert rel_err(xg.grad.cpu(), xr.grad) < tol
+            assert rel_err(conv.linear.grad.cpu(), Wr.grad) < tol
+
+
+def test_model_stack_sage(cuda):
+    """3-layer SAGE over a CSR_Layer batch (node prefixes per layer), as GNN.forward_cxg runs it."""
+    import cxgnncomp
+    torch.manual_seed(4)
+    ptr, idx = random_csr(400, 400, 6, seed=15)
+    idx = idx % 150  # sources inside every layer's node prefix, as in a sampled batch
+    # layer prefixes: 40 seeds <- 150 <- 300 <- 400 nodes
+    nodes = [40, 150, 300, 400]
+    edges = [int(ptr[n]) for n in nodes[:3]]
+    batch = cxgnncomp.Batch(randn((400, 100), 16).cuda(), ptr.cuda(), idx.cuda(), nodes, edges)
+    model = cxgnncomp.SAGE(100, 64, 47, 3).cuda().eval()
+    out = model(batch)
+    assert out.shape == (40, 47)
+    assert torch.allclose(out.exp().sum(-1).cpu(), torch.ones(40), atol=1e-4)
+    model.train()
+    loss = F.nll_loss(model(batch), torch.randint(0, 47, (40,)).cuda())
+    loss.backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())

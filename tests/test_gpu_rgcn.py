@@ -1,0 +1,138 @@
+"""Relational path: relation-bucket padding (integer, exact), typed linear (exact fp32), typed matmul on the
+tensor cores (bf16 and TF32, tolerance), aggr_rgcn_direct, against the CPU oracle."""
+import pytest
+import torch
+
+import oracle
+from helpers import random_csr, randn, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _preprocess(types, num_rel, thres):
+    """TypedLinearE2EOP.preprocess (cxgnncomp/typed_linear.py:74-87) with a stable sort."""
+    import cxgnncomp_backend as be
+    count = torch.bincount(types, minlength=num_rel)
+    new_types = torch.empty(types.shape[0] + num_rel * (thres - 1), dtype=torch.int64, device=types.device)
+    new_types[:types.shape[0]] = types
+    be.pad_rel(new_types, count, thres, num_rel, types.shape[0])
+    sorted_types, indices = torch.sort(new_types, stable=True)
+    return new_types, sorted_types, indices, count
+
+
+@pytest.mark.parametrize("thres", [2, 8, 128, 256])
+def test_pad_rel_bit_exact(cuda, thres):
+    import cxgnncomp_backend as be
+    num_rel = 5
+    g = torch.Generator().manual_seed(thres)
+    types = torch.randint(0, num_rel, (1003,), generator=g)
+    types[types == 3] = 1  # an empty relation
+    count = torch.bincount(types, minlength=num_rel)
+    buf = torch.full((1003 + num_rel * (thres - 1),), -7, dtype=torch.int64)
+    buf[:1003] = types
+    want, want_idx = oracle.pad_rel(buf, count, thres, num_rel, 1003, idx=torch.zeros_like(buf))
+    got = buf.clone().cuda()
+    be.pad_rel(got, count.cuda(), thres, num_rel, 1003)
+    assert torch.equal(got.cpu(), want)
+    got2, gi = buf.clone().cuda(), torch.zeros_like(buf).cuda()
+    be.pad_rel_idx(got2, gi, count.cuda(), thres, num_rel, 1003)
+    assert torch.equal(got2.cpu(), want) and torch.equal(gi.cpu(), want_idx)
+    # every relation's bucket is a multiple of thres (what the typed matmul relies on)
+    tot = torch.bincount(got.cpu(), minlength=num_rel + 1)
+    assert torch.all(tot[:num_rel] % thres == 0)
+
+
+def test_typed_linear_variants_exact(cuda):
+    import cxgnncomp_backend as be
+    g = torch.Generator().manual_seed(1)
+    R, K, N, E = 4, 48, 40, 900
+    x = randn((300, K), 2)
+    w = randn((R, K, N), 3) * 0.2
+    types = torch.randint(0, R, (E,), generator=g, dtype=torch.int32)
+    src = torch.randint(0, 300, (E,), generator=g)
+    dst = torch.randint(0, 70, (E,), generator=g)
+    xg, wg = x.cuda(), w.cuda()
+    # typed_linear: one row of x per item
+    out = torch.zeros(300, N, device="cuda")
+    t300 = torch.randint(0, R, (300,), generator=g, dtype=torch.int32)
+    be.typed_linear(xg, wg, out, t300.cuda(), 32)
+    assert rel_err(out.cpu(), oracle.typed_linear_f64(x, w, t300.long())) < 1e-5
+    # s2e
+    out = torch.zeros(E, N, device="cuda")
+    be.typed_linear_s2e(xg, wg, out, src.cuda(), types.cuda(), 32)
+    per_edge = oracle.typed_linear_f64(x, w, types.long(), src=src)
+    assert rel_err(out.cpu(), per_edge) < 1e-5
+    # s2d: scatter-add into destinations
+    out = torch.zeros(70, N, device="cuda")
+    be.typed_linear_s2d(xg, wg, out, src.cuda(), dst.cuda(), types.cuda(), 32)
+    want = torch.zeros(70, N, dtype=torch.float64).index_add_(0, dst, per_edge)
+    assert rel_err(out.cpu(), want) < 1e-5
+
+
+def test_rgcn_direct(cuda):
+    import cxgnncomp_backend as be
+    ptr, idx = random_csr(90, 80, 6, seed=4, hub=300)
+    g = torch.Generator().manual_seed(5)
+    R, K, N = 3, 32, 64
+    x, w = randn((80, K), 6), randn((R, K, N), 7) * 0.3
+    rel = torch.randint(0, R, (idx.shape[0],), generator=g, dtype=torch.int32)
+    got = be.aggr_rgcn_direct_func(x.cuda(), ptr.cuda(), idx.cuda(), w.cuda(), rel.cuda(), 90).cpu()
+    per_edge = oracle.typed_linear_f64(x, w, rel.long(), src=idx)
+    want = torch.zeros(90, N, dtype=torch.float64).index_add_(0, oracle.dst_of_edges(ptr), per_edge)
+    assert rel_err(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype,k,n,tol", [(torch.bfloat16, 128, 64, 1e-2), (torch.bfloat16, 64, 48, 1e-2),
+                                           (torch.bfloat16, 32, 256, 1e-2), (torch.float32, 128, 64, 2e-3),
+                                           (torch.float32, 64, 16, 2e-3)])
+@pytest.mark.parametrize("thres", [128, 256])
+def test_typed_matmul_tensor_cores(cuda, dtype, k, n, tol, thres):
+    """E2E typed matmul as TypedLinearE2EOP runs it: positions sorted by relation and padded to multiples of
+    thres, A rows and C rows addressed by the same index (typed_linear.py:89-112). bf16 within 1e-2, fp32
+    inputs go through TF32 like the reference's tl.dot (its own checks use 1e-2, codegen/util.py:5-15)."""
+    import cxgnncomp_backend as be
+    R, E = 5, 3000
+    g = torch.Generator().manual_seed(k + n)
+    types = torch.randint(0, R, (E,), generator=g)
+    types[types == 2] = 4  # an empty relation in the middle
+    a = randn((E, k), 8).to(dtype)
+    w = (randn((R, k, n), 9) * 0.2).to(dtype)
+    _, sorted_types, indices, _ = _preprocess(types.cuda(), R, thres)
+    c = be.typed_matmul_raw(a.cuda(), w.cuda(), sorted_types, sorted_types.shape[0], E, src_idx=indices)
+    want = oracle.typed_linear_f64(a, w, types)
+    assert c.shape == (E, n)
+    assert rel_err(c.float().cpu(), want) < tol
+    # every real row was computed (the reference launches cdiv(E, BLOCK_M) tiles over the padded array and
+    # leaves the last rows unset, triton_typed_matmul.py:776-782; not reproduced)
+    row_err = (c.float().cpu().double() - want).abs().amax(1) / want.abs().amax().clamp(min=1e-30)
+    assert float(row_err.max()) < tol
+    # exact mode: fp32 fma of every product
+    ce = be.typed_matmul_raw(a.cuda(), w.cuda(), sorted_types, sorted_types.shape[0], E, src_idx=indices, exact=True)
+    assert rel_err(ce.float().cpu(), want) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_typed_matmul_index_variants(cuda):
+    """No index, sequential output, and separate source / destination indices (the four kernels of
+    triton_typed_matmul.py:145-749)."""
+    import cxgnncomp_backend as be
+    R, K, N = 3, 64, 32
+    g = torch.Generator().manual_seed(11)
+    # no index: positions are rows of A, already grouped in blocks of 128 per relation
+    rel = torch.repeat_interleave(torch.tensor([0, 2, 1, 2]), 128)
+    a, w = randn((512, K), 12).bfloat16(), (randn((R, K, N), 13) * 0.2).bfloat16()
+    c = be.typed_matmul_raw(a.cuda(), w.cuda(), rel.cuda(), 512, 512)
+    assert rel_err(c.float().cpu(), oracle.typed_linear_f64(a, w, rel)) < 1e-2
+    # sequential output: gather rows of x, write position-major
+    x = randn((200, K), 14).bfloat16()
+    src = torch.randint(0, 200, (384,), generator=g)
+    rel3 = torch.repeat_interleave(torch.tensor([1, 0, 2]), 128)
+    c = be.typed_matmul_raw(x.cuda(), w.cuda(), rel3.cuda(), 384, 200, src_idx=src.cuda(), seq_output=True)
+    assert c.shape == (384, N)
+    assert rel_err(c.float().cpu(), oracle.typed_linear_f64(x, w, rel3, src=src)) < 1e-2
+    # source and destination index
+    dst = torch.randperm(384, generator=g)
+    c = be.typed_matmul_raw(x.cuda(), w.cuda(), rel3.cuda(), 384, 200, src_idx=src.cuda(), dst_idx=dst.cuda(),
+                            out_rows=384)
+    want = torch.zeros(384, N, dtype=torch.float64)
+    want[dst] = oracle.typed_linear_f64(x, w, rel3, src=src)
+    assert rel_err(c.float().cpu(), want) < 1e-2
