@@ -12,7 +12,7 @@ reference's CPU formulation (torch index_add_ / sparse.mm, all host threads) on 
 sample of the same workload.
 
 With N > 1 (torchrun, one rank per GPU) rows are split contiguously by edge count; every step each
-rank broadcasts its feature shard to all others over NCCL (the all-gather of the full-graph layer)
+rank's feature shard is all-gathered over NCCL into every rank's local buffer
 and aggregates its own rows; total work is fixed ("strong" scaling).
 
 `--impl reference` times the reference's own CPU formulation only (rank 0), same metric and unit.
@@ -192,9 +192,16 @@ def main():
         run_reference(args, rank)
         return
 
+    # Libraries below (NCCL prints its version banner) write to file descriptor 1; keep it clean for the
+    # one JSON line by pointing it at stderr until the result is printed.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch.distributed as dist
     import cxgnncomp_backend as be
-    from cxgnncomp import synthetic, row_partition_by_nnz, local_rows
+    from cxgnncomp import synthetic
+    from cxgnncomp.distributed import RowPartition, exchange_features
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local_rank)
@@ -211,10 +218,10 @@ def main():
     nnz = int(ptr[n])
     elem = 2 if dtype == torch.bfloat16 else 4
     idx_bytes = idx.element_size()
-    bounds = row_partition_by_nnz(ptr, world)
-    r0, r1 = bounds[rank], bounds[rank + 1]
+    part = RowPartition(ptr, world)
+    r0, r1 = part.rows(rank)
     if world > 1:
-        lptr, lidx = local_rows(ptr, idx, r0, r1)
+        lptr, lidx = part.local_graph(ptr, idx, rank)
         full_ptr = ptr
         del idx
     else:
@@ -222,18 +229,25 @@ def main():
     torch.cuda.empty_cache()
     n_local = r1 - r0
 
-    # features: every rank draws the same stream and keeps the whole matrix as its gather buffer
+    # features: every rank draws the same stream; with several ranks the matrix is re-laid out as the
+    # [world, shard_rows, F] gather buffer that the all-gather fills
     x_full = synthetic.node_features(n, feat, seed=0, device=dev, dtype=dtype)
+    if world > 1:
+        xg = torch.zeros((part.gather_rows(), feat), dtype=dtype, device=dev)
+        for j in range(world):
+            b0, b1 = part.rows(j)
+            part.shard(xg, j).copy_(x_full[b0:b1])
+        x_full = xg
+        del xg
+    x_own = part.shard(x_full, rank) if world > 1 else x_full
     y = torch.empty((n_local, feat), dtype=dtype, device=dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     b_alg_total = algorithmic_bytes(n, n, nnz, feat, elem, idx_bytes)
     b_alg_local = algorithmic_bytes(n_local, n, int(lptr[n_local]), feat, elem, idx_bytes)
 
     def exchange():
-        """All ranks end up with every shard of x in x_full (NCCL broadcasts, one per source rank)."""
-        works = [dist.broadcast(x_full[bounds[j]:bounds[j + 1]], src=j, async_op=True) for j in range(world)]
-        for w in works:
-            w.wait()
+        """All ranks end up with every shard of x in x_full (one NCCL all-gather)."""
+        exchange_features(x_full, part, rank)
 
     def step():
         if world > 1:
@@ -276,8 +290,8 @@ def main():
     # end to end: inputs from pinned host memory, result back to the host, every step
     e2e = None
     if not args.no_e2e:
-        hx = torch.empty(x_full[r0:r1].shape, dtype=dtype).pin_memory()
-        hx.copy_(x_full[r0:r1])
+        hx = torch.empty(x_own.shape, dtype=dtype).pin_memory()
+        hx.copy_(x_own)
         hidx = torch.empty(lidx.shape, dtype=lidx.dtype).pin_memory()
         hidx.copy_(lidx)
         hptr = torch.empty(lptr.shape, dtype=lptr.dtype).pin_memory()
@@ -286,7 +300,7 @@ def main():
         d_idx, d_ptr = torch.empty_like(lidx), torch.empty_like(lptr)
 
         def e2e_step():
-            x_full[r0:r1].copy_(hx, non_blocking=True)
+            x_own.copy_(hx, non_blocking=True)
             d_idx.copy_(hidx, non_blocking=True)
             d_ptr.copy_(hptr, non_blocking=True)
             if world > 1:
@@ -328,7 +342,8 @@ def main():
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
                 "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 

@@ -1,0 +1,62 @@
+"""Host logic of the multi-GPU full-graph layer with two gloo ranks on CPU: the edge-balanced row partition is the
+same on every rank, the feature exchange rebuilds the full matrix everywhere, and the per-rank aggregations
+(computed here by the CPU oracle, since the CUDA kernels need a GPU) assemble to the single-process result."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "cxgnn-compute_b200"), os.path.join(ROOT, "tests")):
+        sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from cxgnncomp import synthetic
+    from cxgnncomp.distributed import RowPartition, dist_aggregate
+    ptr, idx = synthetic.powerlaw_graph(3000, 20000, seed=1)
+    x = synthetic.node_features(3000, 16, seed=1)
+    part = RowPartition(ptr, world)
+    r0, r1 = part.rows(rank)
+    lptr, lidx = part.local_graph(ptr, idx, rank)
+    x_gather = torch.zeros(part.gather_rows(), x.shape[1])
+    part.shard(x_gather, rank).copy_(x[r0:r1])  # this rank only knows its own shard
+
+    def aggregate(xf, p, i, n, out):
+        return oracle.spmm(p, i, xf)
+
+    y_local = dist_aggregate(x_gather, lptr, lidx, part, rank, aggregate)
+    for j in range(world):
+        b0, b1 = part.rows(j)
+        assert torch.equal(part.shard(x_gather, j), x[b0:b1]), "exchange did not deliver every shard"
+    # column ids were renumbered into the gather layout: they address the same feature rows
+    _, gidx = part.local_graph(ptr, idx, rank, gather_ids=False)
+    assert torch.equal(x_gather[lidx], x[gidx])
+    torch.save({"bounds": part.bounds, "y": y_local, "nnz": int(lptr[-1])}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_partition_exchange_aggregate(tmp_path):
+    world = 2
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    sys.path.insert(0, os.path.join(ROOT, "cxgnn-compute_b200"))
+    import oracle
+    from cxgnncomp import synthetic
+    ptr, idx = synthetic.powerlaw_graph(3000, 20000, seed=1)
+    x = synthetic.node_features(3000, 16, seed=1)
+    full = oracle.spmm(ptr, idx, x)
+    parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
+    assert parts[0]["bounds"] == parts[1]["bounds"]
+    assert torch.equal(torch.cat([p["y"] for p in parts]), full)
+    nnz = [p["nnz"] for p in parts]
+    assert sum(nnz) == idx.shape[0]
+    max_deg = int((ptr[1:] - ptr[:-1]).max())
+    assert abs(nnz[0] - nnz[1]) <= 2 * max_deg  # balanced by edges up to one row
