@@ -48,6 +48,9 @@ WORKLOADS = {
 }
 DTYPES = {"bf16": torch.bfloat16, "f32": torch.float32}
 L2_FLUSH_BYTES = 256 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tiled kernel on one GPU, from ncu
+# captures of these workloads (profiles/spmm_stream_papers.md); None where no capture exists.
+NCU_DRAM_BYTES = {"papers_like": 300.59e9, "papers_tenth": 24.67e9}
 
 
 def load_peaks():
@@ -326,7 +329,8 @@ def main():
     peak, peak_src = load_peaks()
     achieved = b_alg_local / (spmm_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_src, "kernel": "cxg_spmm_csr (plan + spmm_rows + reduce)",
+                "traffic": NCU_DRAM_BYTES.get(args.workload) if world == 1 else None, "peak_source": peak_src,
+                "kernel": "cxg_spmm_csr (plan + spmm_stream + fix kernels)",
                 "ms": spmm_ms, "algorithmic_bytes": b_alg_local}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

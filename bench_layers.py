@@ -148,13 +148,14 @@ def config2(steps, flush):
             "cpu_cores": torch.get_num_threads(), "max_rel_err_fwd": err, "max_rel_err_grad_x": err_g}
 
 
-def config4(steps, flush):
+def config4(steps, flush, scale=1.0):
     """RGCN layer, 8 relations, 1.94 M nodes / 21 M edges, 128 -> 64, fp32 (TF32 products) and bf16."""
     import cxgnncomp
     import cxgnncomp_backend as be
     import oracle
     from cxgnncomp import synthetic
     n, e_und = synthetic.CONFIG_SHAPES["rgcn_like"]
+    n, e_und = int(n * scale), int(e_und * scale)  # scale < 1 keeps the mean degree (for profiler captures)
     dev = torch.device("cuda")
     ptr, idx = synthetic.powerlaw_graph(n, e_und, seed=0, device=dev)
     nnz = idx.shape[0]
@@ -166,9 +167,14 @@ def config4(steps, flush):
         conv = cxgnncomp.MyRGCNConv(128, 64, 8).cuda().to(dtype)
         x = synthetic.node_features(n, 128, seed=0, device=dev, dtype=dtype)
         with torch.no_grad():
-            conv(x, ptr, idx, rel_t, n)  # builds the relation buckets once, like the reference caches them
-            t_layer = gpu_ms(lambda: conv(x, ptr, idx, rel_t, n), steps, flush)
-            st, num_item, indices, _ = conv.preprocessed
+            t_sched = {}
+            for sched in ("e2e", "fused_gather", "fused_scatter"):
+                conv.schedule = sched
+                conv(x, ptr, idx, rel_t, n)  # builds the relation buckets once, like the reference caches them
+                t_sched[sched] = gpu_ms(lambda: conv(x, ptr, idx, rel_t, n), steps, flush)
+            conv.schedule = "fused_gather"
+            t_layer = t_sched["fused_gather"]
+            st, num_item, indices = conv.preprocessed[:3]
             xe = x[idx]
             t_mm = gpu_ms(lambda: be.typed_matmul_raw(xe, conv.linear.data, st, st.shape[0], nnz, src_idx=indices),
                           steps, flush)
@@ -188,7 +194,7 @@ def config4(steps, flush):
                 continue
             ref = oracle.typed_linear_f64(xc, W, rc[e0:e1], src=ic[e0:e1]).sum(0) / (e1 - e0)
             errs.append(float((y[r].float().cpu().double() - ref).abs().max() / ref.abs().max().clamp(min=1e-30)))
-        out[name] = {"layer_ms": t_layer, "typed_matmul_ms": t_mm, "typed_matmul_tflops": flops / t_mm / 1e9,
+        out[name] = {"layer_ms": t_layer, "layer_ms_by_schedule": t_sched, "typed_matmul_ms": t_mm, "typed_matmul_tflops": flops / t_mm / 1e9,
                      "typed_matmul_frac_tensor_peak": flops / t_mm / 1e9 / tens,
                      "typed_matmul_b_alg_GBps": b_mm / t_mm / 1e6, "typed_matmul_frac_hbm_peak": b_mm / t_mm / 1e6 / hbm,
                      "max_rel_err_sampled_rows": max(errs)}
@@ -210,12 +216,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c2,c4")
     ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--c4-scale", type=float, default=1.0, help="shrink configuration 4 (nodes and edges) by this factor")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "needs a CUDA device"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     table = {"c1": config1, "c2": config2, "c4": config4}
     for c in args.configs.split(","):
-        print(json.dumps(table[c](args.steps, flush)), flush=True)
+        res = table[c](args.steps, flush, args.c4_scale) if c == "c4" else table[c](args.steps, flush)
+        print(json.dumps(res), flush=True)
 
 
 if __name__ == "__main__":

@@ -6,21 +6,25 @@
 // (cxgnncomp/codegen/triton_typed_matmul.py:145-749: no index / single index / single index with
 // sequential output / source + destination index), whose tl.dot is a TF32 mma.sync on Ampere.
 //
-// One CTA (128 threads) owns one 128-position tile at a time:
-//   1. the 128 gathered rows of A are copied into shared memory in the K-major "core matrix"
-//      layout the tensor core reads without swizzle (8 rows x 16 bytes per core matrix), padding
-//      rows as zeros; W[rel] (pre-transposed once to [N][K]) is copied the same way when the
-//      relation differs from the previous tile's;
-//   2. one thread issues K/16 (bf16) or K/8 (tf32) `tcgen05.mma` instructions with M = 128,
-//      N = n, accumulating fp32 in tensor memory, and commits them to an mbarrier;
-//   3. after the barrier each warp reads its 32 accumulator lanes with `tcgen05.ld`, converts and
-//      writes the rows of C to their scattered destinations.
-// The work is HBM-bound at RGCN shapes (K = 128, N = 64: 43 flop per byte in bf16), so several
-// small CTAs per SM overlap each other's copy / MMA / store phases instead of a warp-specialised
-// pipeline inside one CTA.
+// A persistent, warp-specialised CTA per SM owns a contiguous range of 128-position tiles (so the
+// relation changes at most num_rel times per CTA) and runs three roles that meet only at mbarriers:
+//   * 4 producer warps gather the 128 rows of A of a tile with 16-byte `cp.async` copies into one
+//     stage of a shared-memory ring, in the K-major "core matrix" layout the tensor core reads
+//     without swizzle (8 rows x 16 bytes per core matrix; padding rows are zero-filled by a copy
+//     of size 0). Up to `stages` tiles are in flight per CTA, which is what keeps HBM busy: the
+//     op is memory-bound at RGCN shapes (K = 128, N = 64: 43 flop per byte in bf16). W[rel]
+//     (pre-transposed once to [N][K]) is copied the same way when the relation changes, after
+//     the MMAs that read the previous one have drained;
+//   * one thread issues K/16 (bf16) or K/8 (tf32) `tcgen05.mma` instructions per tile with M = 128,
+//     N = n, accumulating fp32 in one of two tensor-memory buffers, and commits them to the
+//     barrier that frees the stage and to the one that hands the accumulator to the epilogue;
+//   * 4 epilogue warps read their 32 accumulator lanes with `tcgen05.ld`, convert, and write (or
+//     atomically add) the rows of C at their scattered destinations while the next tile's MMAs
+//     run into the other buffer.
 //
-// Waits are bounded: if the MMA barrier does not complete within about a second the CTA records
-// an error, releases its tensor memory and returns.
+// Every wait is bounded: a role that waits longer than about a second raises a CTA-wide abort
+// flag and an error status; all roles then leave their loops, the copies in flight are waited
+// for, the tensor memory is released and the kernel returns.
 #include "common.cuh"
 
 namespace cxg {
@@ -32,7 +36,16 @@ int typed_rows_launch(const void *a, const void *w, void *out, const void *rel, 
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kMmThreads = 128;
+constexpr int kEpiWarps = 4, kProdWarps = 4;
+constexpr int kMmaWarp = kEpiWarps;                              // warp 4
+constexpr int kMmThreads = 32 * (kEpiWarps + 1 + kProdWarps);    // 288
+constexpr int kMaxStages = 6;
+#ifndef TMM_RPI
+#define TMM_RPI 8
+#endif
+constexpr int kRpi = TMM_RPI, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction
+constexpr int kSlots = 4 * (8 / kRpi);           // rows of a tile whose chunks one producer thread copies
+constexpr int kSmemBudget = 226 * 1024;
 constexpr long long kWaitCycles = 1ll << 31;
 
 struct TmmArgs {
@@ -44,7 +57,9 @@ struct TmmArgs {
   const int64_t *dst;
   int64_t m, m_valid;
   int k, n, num_rel, out_follows_src;
-  int tmem_cols;
+  int atomic;  // add the rows into a float32 C with vector reductions instead of storing them
+  int tmem_cols;  // columns of ONE accumulator buffer (two are allocated)
+  int stages;     // shared-memory stages of A
   int32_t *status;  // [0] error flag
 };
 
@@ -111,140 +126,311 @@ __global__ void transpose_w(const T *w, T *wt, int num_rel, int k, int n) {
   }
 }
 
+struct Barriers {
+  uint64_t full[kMaxStages];   // producers -> MMA: the stage holds a tile (128 arrivals)
+  uint64_t empty[kMaxStages];  // MMA -> producers: the MMAs that read the stage are done (1 commit)
+  uint64_t acc_full[2];        // MMA -> epilogue (1 commit)
+  uint64_t acc_empty[2];       // epilogue -> MMA (128 arrivals)
+};
+
+// Bounded wait on phase `parity`; false after a time-out here or an abort raised by another role.
+__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status) {
+  const uint32_t b = smem_addr(bar);
+  if (mbar_try_wait(b, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(b, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicExch(status, 1);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// 16-byte asynchronous copy; CA = through L1 (adjacent lanes' chunks merge into one request per line, which
+// is what a gather of re-used rows wants), otherwise L2 only (faster when every row is read once).
+template <bool CA>
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int bytes) {
+  if (CA)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+  else
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Wait until at most `pending` of this thread's copy groups are still in flight.
+__device__ __forceinline__ void cp_async_wait(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+  }
+}
+
 // T = __nv_bfloat16 (kind::f16, 16 K per instruction) or float (kind::tf32, 8 K per instruction).
-template <typename T>
-__global__ void __launch_bounds__(kMmThreads) typed_mm_tc(TmmArgs a) {
+template <typename T, bool CA>
+__global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
   constexpr bool TF32 = sizeof(T) == 4;
   constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t mma_bar;
+  __shared__ __align__(8) Barriers bars;
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_slot;
+  volatile int *abort_flag = &abort_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunks = a.k / EPC;             // 16-byte chunks per row
   const uint32_t lbo = 128;                 // next core matrix along K
   const uint32_t sbo = chunks * 128;        // next 8-row group
-  uint8_t *smem_a = smem;                   // 128 rows
-  uint8_t *smem_b = smem + static_cast<size_t>(kTileM) * a.k * sizeof(T);  // n rows
-  const uint32_t bar = smem_addr(&mma_bar);
+  const int S = a.stages;
+  const size_t a_bytes = static_cast<size_t>(kTileM) * a.k * sizeof(T);
+  uint8_t *smem_b = smem;                                          // n rows of W[rel]^T
+  uint8_t *smem_a = smem + static_cast<size_t>(a.n) * a.k * sizeof(T);  // S stages of 128 rows
 
-  if (warp == 0) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
-                 "r"(static_cast<uint32_t>(a.tmem_cols))
+                 "r"(static_cast<uint32_t>(2 * a.tmem_cols))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+    abort_slot = 0;
+    for (int s = 0; s < kMaxStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.full[s])), "r"(32 * kProdWarps) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars.empty[s])) : "memory");
+    }
+    for (int b = 0; b < 2; ++b) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars.acc_full[b])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc_empty[b])), "r"(32 * kEpiWarps) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_d = tmem_base_slot;
-  const uint32_t idesc = make_idesc(TF32 ? 2 : 1, kTileM, a.n);
 
   const T *A = static_cast<const T *>(a.a);
-  const T *Wt = static_cast<const T *>(a.wt);
-  T *C = static_cast<T *>(a.c);
   const int64_t n_tiles = (a.m + kTileM - 1) / kTileM;
-  int64_t loaded_rel = -1;
-  uint32_t parity = 0;
-  bool dead = false;
+  const int64_t tile_lo = n_tiles * blockIdx.x / gridDim.x, tile_hi = n_tiles * (blockIdx.x + 1) / gridDim.x;
 
-  for (int64_t tile = blockIdx.x; tile < n_tiles && !dead; tile += gridDim.x) {
-    const int64_t m0 = tile * kTileM;
-    const int64_t r = a.rel[m0];
-    if (r < 0 || r >= a.num_rel) continue;  // a tile of padding only
-    // ---- A: thread t copies 16-byte chunks; 8 consecutive threads take 8 consecutive rows of
-    // one chunk column, so a warp writes 512 contiguous bytes of shared memory.
-    const int r8 = tid & 7, c_lo = tid >> 3;  // c_lo in [0,16)
-    for (int g = 0; g < kTileM / 8; ++g) {
-      const int64_t pos = m0 + g * 8 + r8;
-      int64_t ia = -1;
-      if (pos < a.m) ia = a.src != nullptr ? a.src[pos] : pos;
-      const bool ok = ia >= 0 && ia < a.m_valid;
-      for (int c = c_lo; c < chunks; c += 16) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (ok) v = __ldg(reinterpret_cast<const uint4 *>(A + ia * a.k) + c);
-        *reinterpret_cast<uint4 *>(smem_a + static_cast<size_t>(g) * sbo + c * 128 + r8 * 16) = v;
-      }
-    }
-    if (r != loaded_rel) {
-      const T *wr = Wt + r * static_cast<int64_t>(a.n) * a.k;
-      for (int g = 0; g < a.n / 8; ++g)
-        for (int c = c_lo; c < chunks; c += 16)
-          *reinterpret_cast<uint4 *>(smem_b + static_cast<size_t>(g) * sbo + c * 128 + r8 * 16) =
-              __ldg(reinterpret_cast<const uint4 *>(wr + static_cast<int64_t>(g * 8 + r8) * a.k) + c);
-      loaded_rel = r;
-    }
-    // make the generic-proxy writes visible to the tensor core (async proxy)
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a0 = smem_addr(smem_a), b0 = smem_addr(smem_b);
-      const int steps = chunks / 2;  // two chunks (32 bytes) of K per instruction
-      for (int j = 0; j < steps; ++j)
-        mma_ss<TF32>(tmem_d, make_desc(a0 + j * 256, lbo, sbo), make_desc(b0 + j * 256, lbo, sbo), idesc, j > 0 ? 1u : 0u);
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-    }
-    // ---- wait for the accumulators
-    if (!mbar_try_wait(bar, parity)) {
-      const long long t0 = clock64();
-      while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kWaitCycles) {
-          dead = true;
-          break;
-        }
-      }
-    }
-    if (dead) {
-      atomicExch(a.status, 1);
-      break;
-    }
-    parity ^= 1u;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // ---- epilogue: warp w owns accumulator lanes 32w .. 32w+31 = tile rows
-    const int64_t pos = m0 + warp * 32 + lane;
-    int64_t oc = -1;
-    if (pos < a.m) {
-      const int64_t ia = a.src != nullptr ? a.src[pos] : pos;
-      if (ia >= 0 && ia < a.m_valid) oc = a.dst != nullptr ? a.dst[pos] : (a.out_follows_src ? ia : pos);
-    }
-    const uint32_t taddr = tmem_d + (static_cast<uint32_t>(warp * 32) << 16);
-    for (int c0 = 0; c0 < a.n; c0 += 8) {
-      uint32_t v[8];
-      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                   : "r"(taddr + c0));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (oc >= 0) {
-        T *o = C + oc * a.n + c0;
-        if (TF32) {
-          *reinterpret_cast<uint4 *>(o) = make_uint4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<uint4 *>(o + 4) = make_uint4(v[4], v[5], v[6], v[7]);
-        } else {
-          uint32_t p[4];
+  if (warp > kMmaWarp) {
+    // ================= producers: gather A (and W on a relation change) =================
+    const int pw = warp - kMmaWarp - 1;          // 0..3: owns row groups 4 pw .. 4 pw + 3 of a tile
+    // one copy instruction of a warp covers kRpi rows x kCpi consecutive 16-byte chunks
+    const int rsub = lane / kCpi, cq = lane % kCpi;
+    const T *Wt = static_cast<const T *>(a.wt);
+    int64_t loaded_rel = -1;
+    int64_t it = 0;        // tiles issued by this CTA
+    int64_t signalled = 0; // tiles whose full barrier this thread has arrived on
+    bool alive = true;
+    // arrive on the full barrier of every issued tile except the newest `keep` ones
+    auto signal_upto = [&](int keep) {
+      if (it - signalled <= keep) return;
+      cp_async_wait(keep);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      for (; signalled < it - keep; ++signalled) mbar_arrive(&bars.full[signalled % S]);
+    };
+    // the relation and the row indices of a tile are fetched one tile ahead, off the critical path
+    auto fetch = [&](int64_t tile, int64_t &r, int64_t (&ia)[kSlots]) {
+      const int64_t m0 = tile * kTileM;
+      r = tile < tile_hi ? a.rel[m0] : -1;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
-            p[q] = *reinterpret_cast<uint32_t *>(&t);
+      for (int gi = 0; gi < kSlots; ++gi) {
+        const int64_t pos = m0 + pw * 32 + gi * kRpi + rsub;  // warp pw owns rows 32 pw .. 32 pw + 31
+        ia[gi] = -1;
+        if (tile < tile_hi && pos < a.m) ia[gi] = a.src != nullptr ? a.src[pos] : pos;
+      }
+    };
+    int64_t r_next, ia_next[kSlots];
+    fetch(tile_lo, r_next, ia_next);
+    for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
+      const int64_t r = r_next;
+      int64_t ia[kSlots];
+#pragma unroll
+      for (int gi = 0; gi < kSlots; ++gi) ia[gi] = ia_next[gi];
+      fetch(tile + 1, r_next, ia_next);
+      if (r < 0 || r >= a.num_rel) continue;  // a tile of padding only
+      if (r != loaded_rel) {
+        // every MMA issued so far reads the old W: hand over what is pending and let them finish
+        signal_upto(0);
+        for (int64_t j = (it > S ? it - S : 0); j < it && alive; ++j)
+          alive = wait_bar(&bars.empty[j % S], static_cast<uint32_t>((j / S) & 1), abort_flag, a.status);
+        if (!alive) break;
+        const T *wr = Wt + r * static_cast<int64_t>(a.n) * a.k;
+        const uint32_t b0 = smem_addr(smem_b);
+        for (int row = pw * kRpi + rsub; row < a.n; row += kProdWarps * kRpi)
+          for (int c = cq; c < chunks; c += kCpi)
+            cp_async16<false>(b0 + (row >> 3) * sbo + c * 128 + (row & 7) * 16, wr + static_cast<int64_t>(row) * a.k + c * EPC, 16);
+        loaded_rel = r;
+      }
+      const int s = static_cast<int>(it % S);
+      if (it >= S) {
+        alive = wait_bar(&bars.empty[s], static_cast<uint32_t>(((it / S) - 1) & 1), abort_flag, a.status);
+        if (!alive) break;
+      }
+      const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+#pragma unroll
+      for (int gi = 0; gi < kSlots; ++gi) {
+        const int row = pw * 32 + gi * kRpi + rsub;  // row of the tile
+        const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
+        const T *src_row = ok ? A + ia[gi] * a.k : A;
+        const int bytes = ok ? 16 : 0;  // size 0 writes zeros
+        const uint32_t d0 = a0 + (row >> 3) * sbo + (row & 7) * 16;
+        for (int c = cq; c < chunks; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ++it;
+      signal_upto(S - 1);
+    }
+    if (alive) signal_upto(0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(TF32 ? 2 : 1, kTileM, a.n);
+      const uint32_t b0 = smem_addr(smem_b);
+      const int steps = chunks / 2;  // two chunks (32 bytes) of K per instruction
+      int64_t it = 0;
+      bool alive = true;
+      int64_t r_next = tile_lo < tile_hi ? a.rel[tile_lo * kTileM] : -1;
+      for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
+        const int64_t r = r_next;
+        r_next = tile + 1 < tile_hi ? a.rel[(tile + 1) * kTileM] : -1;
+        if (r < 0 || r >= a.num_rel) continue;
+        const int s = static_cast<int>(it % S), buf = static_cast<int>(it & 1);
+        alive = wait_bar(&bars.full[s], static_cast<uint32_t>((it / S) & 1), abort_flag, a.status);
+        if (alive && it >= 2)
+          alive = wait_bar(&bars.acc_empty[buf], static_cast<uint32_t>(((it >> 1) - 1) & 1), abort_flag, a.status);
+        if (!alive) break;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+        const uint32_t d = tmem_d + buf * a.tmem_cols;
+        for (int j = 0; j < steps; ++j)
+          mma_ss<TF32>(d, make_desc(a0 + j * 256, lbo, sbo), make_desc(b0 + j * 256, lbo, sbo), idesc, j > 0 ? 1u : 0u);
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_addr(&bars.empty[s]))
+                     : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_addr(&bars.acc_full[buf]))
+                     : "memory");
+        ++it;
+      }
+      // the epilogue of the last tiles must be over before the tensor memory goes away: it arrives on
+      // acc_empty, which the final __syncthreads of the epilogue warps also orders.
+    }
+    __syncwarp();
+  } else {
+    // ================= epilogue: warp w owns accumulator lanes 32w .. 32w+31 = tile rows =================
+    T *C = static_cast<T *>(a.c);
+    int64_t it = 0;
+    bool alive = true;
+    // relation, source and destination index of this thread's row, fetched one tile ahead
+    auto fetch = [&](int64_t tile, int64_t &r, int64_t &sv, int64_t &dv) {
+      const int64_t m0 = tile * kTileM, pos = m0 + warp * 32 + lane;
+      r = tile < tile_hi ? a.rel[m0] : -1;
+      sv = -1, dv = -1;
+      if (tile < tile_hi && pos < a.m) {
+        sv = a.src != nullptr ? a.src[pos] : pos;
+        dv = a.dst != nullptr ? a.dst[pos] : -2;  // -2: no destination index
+      }
+    };
+    int64_t r_next, sv_next, dv_next;
+    fetch(tile_lo, r_next, sv_next, dv_next);
+    for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
+      const int64_t r = r_next, sv = sv_next, dv = dv_next;
+      fetch(tile + 1, r_next, sv_next, dv_next);
+      if (r < 0 || r >= a.num_rel) continue;
+      int64_t oc = -1;
+      if (sv >= 0 && sv < a.m_valid) oc = dv != -2 ? dv : (a.out_follows_src ? sv : tile * kTileM + warp * 32 + lane);
+      const int buf = static_cast<int>(it & 1);
+      alive = wait_bar(&bars.acc_full[buf], static_cast<uint32_t>((it >> 1) & 1), abort_flag, a.status);
+      if (!alive) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + buf * a.tmem_cols;
+      for (int c0 = 0; c0 < a.n; c0 += 16) {
+        uint32_t v[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr + c0));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 16 >= a.n) {  // the accumulator buffer is in registers: give it back to the MMA thread
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&bars.acc_empty[buf]);
+        }
+        if (oc >= 0 && a.atomic) {
+          float *o = static_cast<float *>(a.c) + oc * a.n + c0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4 * q), "f"(__uint_as_float(v[4 * q])),
+                         "f"(__uint_as_float(v[4 * q + 1])), "f"(__uint_as_float(v[4 * q + 2])),
+                         "f"(__uint_as_float(v[4 * q + 3]))
+                         : "memory");
+        } else if (!a.atomic) {
+          // pack the 16 columns into 16-byte quads of the output type, then trade quads with the
+          // neighbouring lane so that two adjacent lanes write the two halves of one 32-byte sector
+          constexpr int NQ = TF32 ? 4 : 2;
+          uint4 q[NQ];
+          if (TF32) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q[j % NQ] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            uint32_t p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+              p[j] = *reinterpret_cast<uint32_t *>(&t);
+            }
+            q[0] = make_uint4(p[0], p[1], p[2], p[3]);
+            q[1] = make_uint4(p[4], p[5], p[6], p[7]);
           }
-          *reinterpret_cast<uint4 *>(o) = make_uint4(p[0], p[1], p[2], p[3]);
+          const bool odd = lane & 1;
+          const int64_t oc_a = __shfl_sync(0xffffffffu, oc, lane & ~1), oc_b = __shfl_sync(0xffffffffu, oc, lane | 1);
+          T *row_a = C + oc_a * a.n + c0, *row_b = C + oc_b * a.n + c0;
+          constexpr int QE = 16 / sizeof(T);  // elements per quad
+#pragma unroll
+          for (int h = 0; h < NQ / 2; ++h) {
+            const uint4 keep = odd ? q[2 * h + 1] : q[2 * h], send = odd ? q[2 * h] : q[2 * h + 1];
+            uint4 got;
+            got.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
+            got.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
+            got.z = __shfl_xor_sync(0xffffffffu, send.z, 1);
+            got.w = __shfl_xor_sync(0xffffffffu, send.w, 1);
+            const int col = (2 * h + (odd ? 1 : 0)) * QE;
+            // row of the even lane: its own quad 2h, and its quad 2h+1 written by the odd lane. (One store
+            // instruction for both lanes, so that the two halves leave as one sector.)
+            const uint4 va = odd ? got : keep, vb = odd ? keep : got;
+            if (oc_a >= 0) st_global_v4(row_a + col, va);
+            if (oc_b >= 0) st_global_v4(row_b + col, vb);
+          }
         }
       }
+      ++it;
     }
-    // the next tile overwrites shared and tensor memory: order this tile's reads before it
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
   }
 
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0)
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d),
-                 "r"(static_cast<uint32_t>(a.tmem_cols))
+                 "r"(static_cast<uint32_t>(2 * a.tmem_cols))
                  : "memory");
+  }
 }
 
 }  // namespace
@@ -262,7 +448,9 @@ extern "C" int cxg_typed_matmul_workspace_size(int num_rel, int k, int n, int dt
 
 extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int64_t *rel, const int64_t *src_idx,
                                 const int64_t *dst_idx, int64_t m, int64_t m_valid, int k, int n, int num_rel, int dtype,
-                                int precision, int seq_output, void *workspace, size_t workspace_bytes, void *stream) {
+                                int precision, int flags, void *workspace, size_t workspace_bytes, void *stream) {
+  const int seq_output = (flags & CXG_TMM_SEQ_OUTPUT) ? 1 : 0;
+  const int atomic = (flags & CXG_TMM_ATOMIC_F32) ? 1 : 0;
   CXG_REQUIRE(m >= 0 && m_valid >= 0 && k > 0 && n > 0 && num_rel > 0, CXG_EINVAL, "cxg_typed_matmul: bad sizes");
   CXG_REQUIRE(dtype == CXG_F32 || dtype == CXG_BF16, CXG_EINVAL, "cxg_typed_matmul: dtype %d", dtype);
   CXG_REQUIRE(precision == 0 || precision == 1, CXG_EINVAL, "cxg_typed_matmul: precision %d", precision);
@@ -270,8 +458,11 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   CXG_REQUIRE(a && w && c && rel, CXG_ENULL, "cxg_typed_matmul: NULL argument");
   cudaStream_t st = as_stream(stream);
   const int follows = (src_idx != nullptr && dst_idx == nullptr && !seq_output) ? 1 : 0;
-  if (precision == 0)  // exact fp32 accumulation of every product, no tensor cores
-    return typed_rows_launch(a, w, c, rel, 8, src_idx, dst_idx, m, m_valid, k, n, num_rel, dtype, 0, follows, st);
+  if (precision == 0) {  // exact fp32 accumulation of every product, no tensor cores
+    CXG_REQUIRE(!atomic || dtype == CXG_F32, CXG_EUNSUPPORTED, "cxg_typed_matmul: exact mode adds atomically in fp32 only");
+    return typed_rows_launch(a, w, c, rel, 8, src_idx, dst_idx, m, m_valid, k, n, num_rel, dtype, atomic ? 2 : 0, follows,
+                             st);
+  }
 
   const int elem = dtype == CXG_F32 ? 4 : 2;
   const int epc = 16 / elem;
@@ -279,8 +470,12 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
               k, 2 * epc);
   CXG_REQUIRE(n % 16 == 0 && n >= 16 && n <= 256, CXG_EUNSUPPORTED,
               "cxg_typed_matmul: N = %d must be a multiple of 16 in [16, 256] on the tensor path", n);
-  const size_t smem = static_cast<size_t>(kTileM + n) * k * elem;
-  CXG_REQUIRE(smem <= 200 * 1024, CXG_ELIMIT, "cxg_typed_matmul: tile of %zu bytes exceeds shared memory", smem);
+  const size_t a_bytes = static_cast<size_t>(kTileM) * k * elem, b_bytes = static_cast<size_t>(n) * k * elem;
+  CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
+              "cxg_typed_matmul: one tile of %zu bytes exceeds shared memory", a_bytes + b_bytes);
+  int stages = static_cast<int>((kSmemBudget - b_bytes) / a_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  const size_t smem = b_bytes + stages * a_bytes;
   CXG_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (k * elem) % 16 == 0 &&
                   (n * elem) % 16 == 0,
               CXG_EINVAL, "cxg_typed_matmul: A, C and their rows must be 16-byte aligned");
@@ -293,32 +488,33 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   TmmArgs t;
   t.a = a, t.c = c, t.rel = rel, t.src = src_idx, t.dst = dst_idx;
   t.m = m, t.m_valid = m_valid, t.k = k, t.n = n, t.num_rel = num_rel, t.out_follows_src = follows;
+  t.atomic = atomic;
   t.status = reinterpret_cast<int32_t *>(workspace);
   void *wt = reinterpret_cast<char *>(workspace) + 256;
   t.wt = wt;
   int cols = 32;
   while (cols < n) cols <<= 1;
-  t.tmem_cols = cols;
+  t.tmem_cols = cols;  // two buffers: 2 * cols <= 512
+  t.stages = stages;
   if (cudaMemsetAsync(t.status, 0, 256, st) != cudaSuccess) return check_launch("cxg_typed_matmul: memset");
   const int64_t n_tiles = (m + kTileM - 1) / kTileM;
-  // CTAs per SM: limited by shared memory and by 512 tensor-memory columns
-  int per_sm = static_cast<int>((220 * 1024) / (smem + 1024));
-  if (per_sm > 512 / cols) per_sm = 512 / cols;
-  if (per_sm > 8) per_sm = 8;
-  if (per_sm < 1) per_sm = 1;
-  int64_t grid = static_cast<int64_t>(kNumSM) * per_sm;
+  // one persistent CTA per SM (its shared-memory ring fills the SM), contiguous tile ranges
+  int64_t grid = kNumSM;
   if (grid > n_tiles) grid = n_tiles;
-  cudaError_t e;
+  // rows that are gathered several times each go through L1, rows read once bypass it
+  const bool ca = src_idx != nullptr && m_valid * 2 <= m;
+  cudaError_t e = cudaSuccess;
+  auto launch = [&](auto kernel) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), kMmThreads, smem, st>>>(t);
+  };
   if (dtype == CXG_F32) {
     transpose_w<float><<<kNumSM, 256, 0, st>>>(static_cast<const float *>(w), static_cast<float *>(wt), num_rel, k, n);
-    e = cudaFuncSetAttribute(typed_mm_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e == cudaSuccess) typed_mm_tc<float><<<static_cast<unsigned>(grid), kMmThreads, smem, st>>>(t);
+    if (ca) launch(typed_mm_tc<float, true>); else launch(typed_mm_tc<float, false>);
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),
                                                        static_cast<__nv_bfloat16 *>(wt), num_rel, k, n);
-    e = cudaFuncSetAttribute(typed_mm_tc<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
-    if (e == cudaSuccess) typed_mm_tc<__nv_bfloat16><<<static_cast<unsigned>(grid), kMmThreads, smem, st>>>(t);
+    if (ca) launch(typed_mm_tc<__nv_bfloat16, true>); else launch(typed_mm_tc<__nv_bfloat16, false>);
   }
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_typed_matmul: %s", cudaGetErrorString(e));
   count_launches(2);

@@ -200,18 +200,72 @@ def run_rgcn4(x, ptr, idx, edge_types, linear, num_center, num_edge, preproccess
     return AggrDirectedOP.apply(out, ptr, new_idx, num_center)
 
 
+class RGCNFusedOP(torch.autograd.Function):
+    """y[d] = sum over the edges of d of x[src[e]] @ W[rel[e]] with the gather of x fused into the
+    typed matmul (the reference materialises x[idx] as an [E, K] tensor first, graph_conv.py:317).
+    scatter=False: the matmul writes one row per edge, a segment sum follows (deterministic).
+    scatter=True: the matmul adds every row straight into y[dst[e]] (vector atomics, no [E, N] tensor).
+    The backward runs the same kernel the other way: rows of grad_y gathered by destination, multiplied by
+    W[rel]^T and added into grad_x[src]."""
+
+    @staticmethod
+    def forward(ctx, x, weights, ptr, sorted_types, src_sorted, dst_sorted, indices, num_center, num_edge, scatter,
+                count):
+        ctx.save_for_backward(x, weights, sorted_types, src_sorted, dst_sorted)
+        ctx.num_center = num_center
+        ctx.count = count
+        positions = sorted_types.shape[0]
+        if scatter:
+            y = torch.zeros((num_center, weights.shape[-1]), dtype=torch.float32, device=x.device)
+            cxgnncomp_backend.typed_matmul_raw(x, weights, sorted_types, positions, x.shape[0], src_idx=src_sorted,
+                                               dst_idx=dst_sorted, atomic_out=y)
+            return y.to(x.dtype)
+        out_e = cxgnncomp_backend.typed_matmul_raw(x, weights, sorted_types, positions, x.shape[0], src_idx=src_sorted,
+                                                   dst_idx=indices, out_rows=positions)
+        seg = torch.arange(0, num_edge, device=x.device, dtype=torch.int64)
+        return cxgnncomp_backend.run_spmm_configurable(ptr, seg, out_e, num_center)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weights, sorted_types, src_sorted, dst_sorted = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        grad_x = grad_w = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            cxgnncomp_backend.typed_matmul_raw(grad_out, weights.transpose(1, 2).contiguous(), sorted_types,
+                                               sorted_types.shape[0], grad_out.shape[0], src_idx=dst_sorted,
+                                               dst_idx=src_sorted, atomic_out=gx)
+            grad_x = gx.to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            # the valid positions are sorted by relation: relation r owns count[r] consecutive ones
+            grad_w = torch.zeros_like(weights)
+            keep = (src_sorted >= 0).nonzero().squeeze(1)
+            src_v, dst_v = src_sorted[keep], dst_sorted[keep]
+            c = 0
+            for r, n_r in enumerate(ctx.count.tolist()):
+                if n_r:
+                    grad_w[r] = torch.mm(x[src_v[c:c + n_r]].t().float(),
+                                         grad_out[dst_v[c:c + n_r]].float()).to(weights.dtype)
+                c += n_r
+        return grad_x, grad_w, None, None, None, None, None, None, None, None, None
+
+
 class MyRGCNConv(torch.nn.Module):
     """RGCN layer: y[d] = (1 / deg d) * sum over edges of x[src] W[rel] (graph_conv.py:329-378). `norm`
     selects the reference's total in-degree ("total", default) or the per-(destination, relation) degree
-    ("relation"); destinations without edges give 0 (the reference divides 0 by 0 there)."""
+    ("relation"); destinations without edges give 0 (the reference divides 0 by 0 there). `schedule`:
+    "e2e" is the reference's sequence (gather x[idx], typed matmul per edge, segment sum); "fused_gather"
+    (default) reads the source rows inside the typed matmul; "fused_scatter" also adds the products straight
+    into the destination rows (atomic, so the order of the additions is not fixed)."""
 
-    def __init__(self, in_channels, hidden_channels, num_rel, norm="total"):
+    def __init__(self, in_channels, hidden_channels, num_rel, norm="total", schedule="fused_gather"):
         super().__init__()
         assert num_rel > 0
         self.in_channels = in_channels
         self.hidden_channels = hidden_channels
         self.num_rel = num_rel
         self.norm = norm
+        self.schedule = schedule
         self.linear = torch.nn.Parameter(torch.empty(num_rel, in_channels, hidden_channels))
         self.register_parameter("rel_weight", self.linear)
         self.single_linear = torch.nn.Linear(in_channels, hidden_channels)
@@ -229,17 +283,31 @@ class MyRGCNConv(torch.nn.Module):
             self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)
         num_edge = edge_types.shape[0]
         deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(x.dtype)
+        if self.norm == "total" and self.schedule != "e2e":
+            if len(self.preprocessed) == 4:  # first call on this graph: positions -> source / destination node
+                sorted_types, _, indices, _ = self.preprocessed
+                dst = torch.repeat_interleave(torch.arange(num_node, device=x.device),
+                                              ptr[1:num_node + 1] - ptr[:num_node])
+                ok = indices < num_edge
+                safe = indices.clamp(max=num_edge - 1)
+                minus = torch.full_like(indices, -1)
+                self.preprocessed = self.preprocessed + [torch.where(ok, idx[:num_edge][safe].long(), minus),
+                                                         torch.where(ok, dst[safe], minus)]
+            sorted_types, _, indices, count, src_sorted, dst_sorted = self.preprocessed
+            out = RGCNFusedOP.apply(x, self.linear, ptr, sorted_types, src_sorted, dst_sorted, indices, num_node,
+                                    num_edge, self.schedule == "fused_scatter", count)
+            return out / deg.unsqueeze(-1)
         if self.norm == "relation":
             # per-(destination, relation) degree: scale every edge's row before the segment sum
             dst = torch.repeat_interleave(torch.arange(num_node, device=x.device), ptr[1:num_node + 1] - ptr[:num_node])
             key = dst * self.num_rel + edge_types
             cnt = torch.bincount(key, minlength=num_node * self.num_rel).to(x.dtype)
             x_idxed = x[idx[:num_edge]]
-            out = TypedLinearE2EOP.apply(x_idxed, self.linear, edge_types, self.preprocessed)
+            out = TypedLinearE2EOP.apply(x_idxed, self.linear, edge_types, self.preprocessed[:4])
             out = out / cnt[key].unsqueeze(-1)
             new_idx = torch.arange(0, num_edge, device=x.device, dtype=idx.dtype)
             return AggrDirectedOP.apply(out, ptr, new_idx, num_node)
-        out = run_rgcn4(x, ptr, idx, edge_types, self.linear, num_node, num_edge, self.preprocessed)
+        out = run_rgcn4(x, ptr, idx, edge_types, self.linear, num_node, num_edge, self.preprocessed[:4])
         return out / deg.unsqueeze(-1)
 
 

@@ -115,9 +115,10 @@ def rel_schedule(csr_ptr, csr_idx, rel, num_node_in_layer, num_rel):
 
 
 def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None, seq_output=False, exact=False,
-                     out_rows=None):
+                     out_rows=None, atomic_out=None):
     """C = typed matmul through the C ABI. a [*, K], b [R, K, N], rel int64 per position; see cxg_typed_matmul.
-    C has `out_rows` rows (default: m_positions for sequential output, else m_valid)."""
+    C has `out_rows` rows (default: m_positions for sequential output, else m_valid). With `atomic_out` (a
+    float32 [*, N] tensor) the rows are ADDED into it with vector atomics instead (rows may repeat)."""
     _cuda(a, "a", (torch.float32, torch.bfloat16))
     _cuda(b, "b", (a.dtype,))
     _cuda(rel, "rel", (torch.int64,))
@@ -128,15 +129,23 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
     num_rel, k, n = b.shape
     if a.shape[1] != k:
         raise RuntimeError("incompatible dimensions")
-    if out_rows is None:
-        out_rows = m_positions if (seq_output or src_idx is None) else m_valid
-    # rows that no position writes are left unset, like the reference's torch.empty output
-    c = torch.empty((int(out_rows), n), dtype=a.dtype, device=a.device)
+    flags = 1 if seq_output else 0
+    if atomic_out is not None:
+        _cuda(atomic_out, "atomic_out", (torch.float32,))
+        if atomic_out.shape[1] != n:
+            raise RuntimeError("atomic_out must be [*, N]")
+        c = atomic_out
+        flags |= 2
+    else:
+        if out_rows is None:
+            out_rows = m_positions if (seq_output or src_idx is None) else m_valid
+        # rows that no position writes are left unset, like the reference's torch.empty output
+        c = torch.empty((int(out_rows), n), dtype=a.dtype, device=a.device)
     dtype = CXG_F32 if a.dtype == torch.float32 else CXG_BF16
     need = _sz(0)
     _check(_tmm_ws(num_rel, k, n, dtype, ctypes.byref(need)), "cxg_typed_matmul_workspace_size")
     ws = _workspace(a.device, need.value)
     with torch.cuda.device(a.device):
         _check(_tmm(_p(a), _p(b), _p(c), _p(rel), _p(src_idx), _p(dst_idx), int(m_positions), int(m_valid), k, n, num_rel,
-                    dtype, 0 if exact else 1, 1 if seq_output else 0, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")
+                    dtype, 0 if exact else 1, flags, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")
     return c

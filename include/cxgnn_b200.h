@@ -251,12 +251,18 @@ int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
  * precision 1: tcgen05 tensor cores, fp32 accumulation in tensor memory (bf16 inputs, or fp32
  * inputs as TF32 like the reference's tl.dot); needs k % 16 == 0 (bf16) / % 8 (fp32), n % 16
  * == 0, n <= 256. precision 0: exact fp32 fma of every product (no tensor cores), any k, n.
+ * flags: CXG_TMM_SEQ_OUTPUT as above; CXG_TMM_ATOMIC_F32 adds the rows into C, which is then
+ * float32 [*, n] whatever dtype is (vector atomics; rows of C may be hit by many positions, e.g.
+ * oc = destination node of an edge, which fuses the segment sum of the RGCN layer into the
+ * matmul; the caller zero-fills C; the order of the additions is not fixed).
  */
+#define CXG_TMM_SEQ_OUTPUT 1
+#define CXG_TMM_ATOMIC_F32 2
 int cxg_typed_matmul_workspace_size(int num_rel, int k, int n, int dtype, size_t *bytes);
 int cxg_typed_matmul(const void *a, const void *w, void *c, const int64_t *rel,
                      const int64_t *src_idx, const int64_t *dst_idx, int64_t m,
                      int64_t m_valid, int k, int n, int num_rel, int dtype,
-                     int precision, int seq_output, void *workspace,
+                     int precision, int flags, void *workspace,
                      size_t workspace_bytes, void *stream);
 
 /*

@@ -108,8 +108,9 @@ def test_gat_layer(cuda, heads, concat):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-3), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("norm", ["total", "relation"])
-def test_rgcn_layer(cuda, dtype, tol, norm):
+@pytest.mark.parametrize("norm,schedule", [("total", "e2e"), ("total", "fused_gather"), ("total", "fused_scatter"),
+                                           ("relation", "e2e")])
+def test_rgcn_layer(cuda, dtype, tol, norm, schedule):
     """Configuration 4 in small: 8 relations, 128 -> 64, edges bucketed by relation, typed matmul on the tensor
     cores (TF32 for fp32 inputs, as the reference's tl.dot), segment sum, degree normalisation."""
     import cxgnncomp
@@ -117,7 +118,7 @@ def test_rgcn_layer(cuda, dtype, tol, norm):
     R = 8
     ptr, idx = random_csr(250, 250, 10, seed=11, hub=700, empty_frac=0.05)
     rel = torch.randint(0, R, (idx.shape[0],), generator=torch.Generator().manual_seed(12))
-    conv = cxgnncomp.MyRGCNConv(128, 64, R, norm=norm).cuda().to(dtype)
+    conv = cxgnncomp.MyRGCNConv(128, 64, R, norm=norm, schedule=schedule).cuda().to(dtype)
     x = randn((250, 128), 13).to(dtype)
     xg = x.cuda().requires_grad_(True)
     out = conv(xg, ptr.cuda(), idx.cuda(), rel.cuda(), 250)

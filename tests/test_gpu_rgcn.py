@@ -136,3 +136,31 @@ def test_typed_matmul_index_variants(cuda):
     want = torch.zeros(384, N, dtype=torch.float64)
     want[dst] = oracle.typed_linear_f64(x, w, rel3, src=src)
     assert rel_err(c.float().cpu(), want) < 1e-2
+
+
+@pytest.mark.parametrize("dtype,k,n,tol", [(torch.bfloat16, 64, 32, 1e-2), (torch.float32, 128, 64, 2e-3)])
+def test_typed_matmul_long_ranges(cuda, dtype, k, n, tol):
+    """More tiles than 148 x ring depth: every persistent CTA walks a range of tiles that wraps its
+    shared-memory ring and both accumulator buffers several times and crosses relation boundaries."""
+    import cxgnncomp_backend as be
+    R, E = 6, 150_000
+    g = torch.Generator().manual_seed(k)
+    types = torch.randint(0, R, (E,), generator=g)
+    src = torch.randint(0, 5000, (E,), generator=g)
+    x = randn((5000, k), 21).to(dtype)
+    w = (randn((R, k, n), 22) * 0.2).to(dtype)
+    _, sorted_types, indices, _ = _preprocess(types.cuda(), R, 128)
+    ok = indices < E
+    src_sorted = torch.where(ok, src.cuda()[indices.clamp(max=E - 1)], torch.full_like(indices, -1))
+    c = be.typed_matmul_raw(x.cuda(), w.cuda(), sorted_types, sorted_types.shape[0], 5000, src_idx=src_sorted,
+                            dst_idx=indices, out_rows=sorted_types.shape[0])
+    want = oracle.typed_linear_f64(x, w, types, src=src)
+    assert rel_err(c[:E].float().cpu(), want) < tol
+    # the same products added into 300 destination rows (vector atomics, fp32 output)
+    dst = torch.randint(0, 300, (E,), generator=g)
+    dst_sorted = torch.where(ok, dst.cuda()[indices.clamp(max=E - 1)], torch.full_like(indices, -1))
+    y = torch.zeros((300, n), dtype=torch.float32, device="cuda")
+    be.typed_matmul_raw(x.cuda(), w.cuda(), sorted_types, sorted_types.shape[0], 5000, src_idx=src_sorted,
+                        dst_idx=dst_sorted, atomic_out=y)
+    want_y = torch.zeros((300, n), dtype=torch.float64).index_add_(0, dst, want)
+    assert rel_err(y.cpu(), want_y) < tol
