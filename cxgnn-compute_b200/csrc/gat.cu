@@ -387,6 +387,43 @@ extern "C" int cxg_spmv_csr(const void *ptr, const void *idx, int ptr_bytes, int
   return check_launch("cxg_spmv_csr");
 }
 
+namespace cxg {
+namespace {
+// out[r, f] = sum over h (in head order, one fp32 accumulator) of in[r, h, f]
+template <typename T>
+__global__ void head_sum_kernel(const T *in, T *out, int64_t n_row, int heads, int feat) {
+  const int64_t total = n_row * feat;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / feat;
+    const int f = static_cast<int>(i - r * feat);
+    const T *p = in + r * heads * feat + f;
+    float acc = to_f32(p[0]);
+    for (int h = 1; h < heads; ++h) acc += to_f32(p[static_cast<int64_t>(h) * feat]);
+    out[i] = from_f32<T>(acc);
+  }
+}
+}  // namespace
+}  // namespace cxg
+
+extern "C" int cxg_head_sum(const void *in, void *out, int64_t n_row, int heads, int feat, int dtype, void *stream) {
+  CXG_REQUIRE(n_row >= 0 && heads > 0 && feat > 0 && (dtype == CXG_F32 || dtype == CXG_BF16), CXG_EINVAL,
+              "cxg_head_sum: bad arguments");
+  if (n_row == 0) return CXG_OK;
+  CXG_REQUIRE(in && out, CXG_ENULL, "cxg_head_sum: NULL argument");
+  const int64_t want = (n_row * feat + kThreads - 1) / kThreads;
+  const unsigned grid = static_cast<unsigned>(want < kNumSM * 32 ? want : kNumSM * 32);
+  cudaStream_t st = as_stream(stream);
+  if (dtype == CXG_F32)
+    head_sum_kernel<float><<<grid, kThreads, 0, st>>>(static_cast<const float *>(in), static_cast<float *>(out), n_row,
+                                                      heads, feat);
+  else
+    head_sum_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(in),
+                                                              static_cast<__nv_bfloat16 *>(out), n_row, heads, feat);
+  count_launches(1);
+  return check_launch("cxg_head_sum");
+}
+
 extern "C" int cxg_gather_edges(const float *in, const void *dest, int idx_bytes, float *out, int64_t n_edge, int feat,
                                 int backward, void *stream) {
   CXG_REQUIRE(n_edge >= 0 && feat > 0 && (idx_bytes == 4 || idx_bytes == 8), CXG_EINVAL,

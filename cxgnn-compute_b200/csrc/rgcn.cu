@@ -228,3 +228,51 @@ extern "C" int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx
   }
   return CXG_OK;
 }
+
+// topo_sort (src/cpp/src/schedule.cu:72-124) on host arrays: a breadth-first release of the nodes whose
+// remaining in-degree is 0. When nothing is releasable and nodes remain, one pass over the nodes
+// releases every node of remaining degree 1 and, if any node has a larger degree, the first node of
+// the smallest such degree, which is how the reference walks through cycles. `order` receives the
+// nodes in release order; *n_order the number released (n_node unless the walk got stuck).
+extern "C" int cxg_topo_sort_host(const int64_t *ptr_host, const int64_t *idx_host, const int64_t *degree_host,
+                                  int64_t n_node, int64_t *order_host, int64_t *n_order) {
+  CXG_REQUIRE(n_node >= 0, CXG_EINVAL, "cxg_topo_sort_host: bad size");
+  CXG_REQUIRE(n_order != nullptr, CXG_ENULL, "cxg_topo_sort_host: n_order is NULL");
+  *n_order = 0;
+  if (n_node == 0) return CXG_OK;
+  CXG_REQUIRE(ptr_host && idx_host && degree_host && order_host, CXG_ENULL, "cxg_topo_sort_host: NULL argument");
+  std::vector<int64_t> left(degree_host, degree_host + n_node);
+  std::vector<int64_t> ready;  // FIFO: `head` is the next node to release
+  ready.reserve(static_cast<size_t>(n_node));
+  size_t head = 0;
+  for (int64_t v = 0; v < n_node; ++v)
+    if (left[v] == 0) ready.push_back(v);
+  int64_t done = 0;
+  while (done < n_node) {
+    for (; head < ready.size() && done < n_node; ++head) {
+      const int64_t v = ready[head];
+      order_host[done++] = v;
+      for (int64_t e = ptr_host[v]; e < ptr_host[v + 1]; ++e)
+        if (--left[idx_host[e]] == 0) ready.push_back(idx_host[e]);
+    }
+    if (done >= n_node) break;
+    int64_t best = n_node, pick = -1;
+    for (int64_t v = 0; v < n_node; ++v) {
+      if (left[v] > 1 && left[v] < best) {
+        best = left[v];
+        pick = v;
+      } else if (left[v] == 1) {
+        left[v] = 0;
+        ready.push_back(v);
+      }
+    }
+    if (pick >= 0) {
+      left[pick] = 0;
+      ready.push_back(pick);
+    } else if (head == ready.size()) {
+      break;
+    }
+  }
+  *n_order = done;
+  return CXG_OK;
+}

@@ -256,7 +256,10 @@ class MyRGCNConv(torch.nn.Module):
     ("relation"); destinations without edges give 0 (the reference divides 0 by 0 there). `schedule`:
     "e2e" is the reference's sequence (gather x[idx], typed matmul per edge, segment sum); "fused_gather"
     (default) reads the source rows inside the typed matmul; "fused_scatter" also adds the products straight
-    into the destination rows (atomic, so the order of the additions is not fixed)."""
+    into the destination rows (atomic, so the order of the additions is not fixed); "transform_first" multiplies
+    every node by every relation's weight (one batched GEMM) and aggregates rows of that [R * N, out] table
+    with `aggr_rel`, the ordering of TypedLinearS2DMMAggrOP (typed_linear.py:191-221): it moves `out` instead of
+    `in` values per edge and wins when the mean degree exceeds num_rel * out / in."""
 
     def __init__(self, in_channels, hidden_channels, num_rel, norm="total", schedule="fused_gather"):
         super().__init__()
@@ -283,6 +286,11 @@ class MyRGCNConv(torch.nn.Module):
             self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)
         num_edge = edge_types.shape[0]
         deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(x.dtype)
+        if self.norm == "total" and self.schedule == "transform_first":
+            xw = torch.matmul(x.unsqueeze(0), self.linear)  # [R, N_src, out]
+            out = cxgnncomp_backend.aggr_rel(xw.reshape(-1, xw.shape[-1]), ptr, idx, edge_types.int(), num_node,
+                                             self.num_rel)
+            return out / deg.unsqueeze(-1)
         if self.norm == "total" and self.schedule != "e2e":
             if len(self.preprocessed) == 4:  # first call on this graph: positions -> source / destination node
                 sorted_types, _, indices, _ = self.preprocessed

@@ -317,6 +317,55 @@ PreReduce = SPMM_MULTIHEAD_SCHEDULE.PreReduce
 Optimal = SPMM_MULTIHEAD_SCHEDULE.Optimal
 
 
+class REDUCEOP(enum.IntEnum):
+    """binding.cpp:108-113."""
+    SUM = 0
+    MAX = 1
+    MIN = 2
+    MEAN = 3
+
+
+class COMPUTEOP(enum.IntEnum):
+    """binding.cpp:114-119 (values of the C++ enum, dgsparse.h:15)."""
+    ADD = 0
+    SUB = 1
+    MUL = 2
+    DIV = 3
+
+
+_gspmm = _sig("cxg_gspmm_csr", [_vp, _vp, ctypes.c_int, ctypes.c_int, _vp, _vp, _vp, _i64, ctypes.c_int, ctypes.c_int,
+                                ctypes.c_int, _vp])
+
+
+def _gspmm_call(rowptr, colind, val, b, re_op, comp_op):
+    _cuda(rowptr, "A_rowptr", (torch.int32,))
+    _cuda(colind, "A_colind", (torch.int32,))
+    _cuda(b, "B", (torch.float32,))
+    if val is not None:
+        _cuda(val, "A_csrVal", (torch.float32,))
+    if b.dim() != 2:
+        raise RuntimeError("B must be [n_src, feat]")
+    m = rowptr.shape[0] - 1
+    out = torch.empty((m, b.shape[1]), dtype=torch.float32, device=b.device)
+    with torch.cuda.device(b.device):
+        _check(_gspmm(_p(rowptr), _p(colind), 4, 4, _p(val), _p(b), _p(out), m, b.shape[1], int(re_op), int(comp_op),
+                      _stream()), "cxg_gspmm_csr")
+    return out
+
+
+def GSpMM_u(A_rowptr, A_colind, B, op):
+    """out[r] = REDUCE over row r of B[colind[e]]; int32 CSR, fp32 (binding.cpp:98-104,107)."""
+    return _gspmm_call(A_rowptr, A_colind, None, B, op, COMPUTEOP.MUL)
+
+
+def GSpMM_u_e(A_rowptr, A_colind, A_csrVal, B, re_op, comp_op):
+    """out[r] = REDUCE over row r of COMPUTE(val[e], B[colind[e]]) (binding.cpp:87-96,106)."""
+    return _gspmm_call(A_rowptr, A_colind, A_csrVal, B, re_op, comp_op)
+
+
+_head_sum_c = _sig("cxg_head_sum", [_vp, _vp, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp])
+
+
 def spmm_multihead(ptr, idx, val, vin, num_node, schedule=SPMM_MULTIHEAD_SCHEDULE.Optimal, block_size=256):
     """Multi-head SpMM with per-(edge, head) values (spmm_host.cu:158-196).
     Naive -> [num_node, H, F]; PreReduce / Optimal -> heads summed, [num_node, F]."""
@@ -333,11 +382,12 @@ def spmm_multihead(ptr, idx, val, vin, num_node, schedule=SPMM_MULTIHEAD_SCHEDUL
 
 
 def _head_sum(out):
-    # Heads are added in head order with one fp32 accumulator per column.
-    acc = out[:, 0].float().clone()
-    for h in range(1, out.shape[1]):
-        acc += out[:, h].float()
-    return acc.to(out.dtype)
+    """[n, H, F] -> [n, F]: heads added in head order with one fp32 accumulator per column."""
+    res = torch.empty((out.shape[0], out.shape[2]), dtype=out.dtype, device=out.device)
+    with torch.cuda.device(out.device):
+        _check(_head_sum_c(_p(out), _p(res), out.shape[0], out.shape[1], out.shape[2], _dtype_code(out), _stream()),
+               "cxg_head_sum")
+    return res
 
 
 def spmm_multihead_bwd(ptr, idx, val, grad_output, grad_x, num_node, schedule=SPMM_MULTIHEAD_SCHEDULE.Optimal,
@@ -550,4 +600,8 @@ def gather(x_edge, dest, num_node):
 
 
 from ._rgcn import (pad_rel, pad_rel_idx, typed_linear, typed_linear_s2e, typed_linear_s2d,  # noqa: E402,F401
-                    aggr_rgcn_direct_func, rel_schedule, typed_matmul_raw)
+                    aggr_rgcn_direct_func, rel_schedule, typed_matmul_raw, topo_sort, aggr_rel_direct)
+
+# pybind's export_values(): the enum members are module attributes too
+SUM, MAX, MIN, MEAN = REDUCEOP.SUM, REDUCEOP.MAX, REDUCEOP.MIN, REDUCEOP.MEAN
+ADD, SUB, MUL, DIV = COMPUTEOP.ADD, COMPUTEOP.SUB, COMPUTEOP.MUL, COMPUTEOP.DIV

@@ -114,6 +114,64 @@ def rel_schedule(csr_ptr, csr_idx, rel, num_node_in_layer, num_rel):
     return out
 
 
+_topo = _sig("cxg_topo_sort_host", [_vp, _vp, _vp, _i64, _vp, ctypes.POINTER(_i64)])
+
+
+def topo_sort(csr_ptr, csr_idx, degree):
+    """Release order of the nodes by remaining in-degree (binding.cpp:33, schedule.cu:72-124); CPU int64 tensors."""
+    for t_, name in ((csr_ptr, "csr_ptr"), (csr_idx, "csr_idx"), (degree, "degree")):
+        if t_.is_cuda or t_.dtype != torch.int64 or not t_.is_contiguous():
+            raise RuntimeError(f"topo_sort: {name} must be a contiguous CPU int64 tensor")
+    n = degree.shape[0]
+    out = torch.empty(n, dtype=torch.int64)
+    done = _i64(0)
+    _check(_topo(csr_ptr.data_ptr(), csr_idx.data_ptr(), degree.data_ptr(), n, out.data_ptr(), ctypes.byref(done)),
+           "cxg_topo_sort_host")
+    if done.value != n:
+        print(f"Error: graph is not a DAG, {done.value} {n}")  # the reference prints and returns the buffer
+    return out
+
+
+class _AggrRelDirectFunction(torch.autograd.Function):
+    """AggrRelDirectFunction (rel_spmm.cu:370-432). The reference's backward returns zero gradients; here
+    grad_x[idx[e]] += grad_out[d] @ W[rel[e]]^T and grad_W[r] = sum of x[idx[e]]^T grad_out[d] are computed."""
+
+    @staticmethod
+    def forward(ctx, x, ptr, idx, weights, etype, num_node, num_rel):
+        ctx.save_for_backward(x, ptr, idx, weights, etype)
+        ctx.num_node = num_node
+        return aggr_rgcn_direct_func(x, ptr, idx, weights, etype, num_node)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, ptr, idx, weights, etype = ctx.saved_tensors
+        n = ctx.num_node
+        nnz = int(ptr[n])
+        grad_out = grad_out.contiguous()
+        dst = torch.repeat_interleave(torch.arange(n, device=x.device), (ptr[1:n + 1] - ptr[:n]).long())
+        src = idx[:nnz].long()
+        grad_x = grad_w = None
+        if ctx.needs_input_grad[0]:
+            grad_x = torch.zeros_like(x)
+            typed_linear_s2d(grad_out, weights.transpose(1, 2).contiguous(), grad_x, dst, src, etype[:nnz], 0)
+        if ctx.needs_input_grad[3]:
+            grad_w = torch.zeros_like(weights)
+            order = torch.sort(etype[:nnz].long(), stable=True).indices
+            cnt = torch.bincount(etype[:nnz].long(), minlength=weights.shape[0]).tolist()
+            c = 0
+            for r, n_r in enumerate(cnt):
+                sel = order[c:c + n_r]
+                c += n_r
+                if n_r:
+                    grad_w[r] = torch.mm(x[src[sel]].t(), grad_out[dst[sel]])
+        return grad_x, None, None, grad_w, None, None, None
+
+
+def aggr_rel_direct(x, ptr, idx, weights, etype, num_node, num_rel):
+    """out[d] = sum over row d of x[idx[e]] @ weights[etype[e]] with autograd (binding.cpp:46)."""
+    return _AggrRelDirectFunction.apply(x, ptr, idx, weights, etype, num_node, num_rel)
+
+
 def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None, seq_output=False, exact=False,
                      out_rows=None, atomic_out=None):
     """C = typed matmul through the C ABI. a [*, K], b [R, K, N], rel int64 per position; see cxg_typed_matmul.

@@ -191,6 +191,33 @@ int cxg_spmv_csr(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
                  const float *x, float *y, int64_t n_dst, void *stream);
 
 /*
+ * Generalised SpMM of the dgSPARSE surface, GSpMM_u (val = NULL) and GSpMM_u_e
+ * (src/cpp/include/dgsparse.h:14-131, src/cpp/src/dgsparse.cu:324-475, python_bindings/binding.cpp:87-119):
+ * y[r, c] = REDUCE over the edges e of row r of COMPUTE(val[e], x[idx[e], c]), fp32, edges in CSR order.
+ * The accumulator starts at 0, (float)INT_MIN or (float)INT_MAX; rows without edges give 0; mean divides
+ * by the edge count. compute: add v + x, sub x - v, mul v * x (fused into the sum), div x / v.
+ */
+#define CXG_ROP_SUM 0
+#define CXG_ROP_MAX 1
+#define CXG_ROP_MIN 2
+#define CXG_ROP_MEAN 3
+#define CXG_COP_ADD 0
+#define CXG_COP_SUB 1
+#define CXG_COP_MUL 2
+#define CXG_COP_DIV 3
+int cxg_gspmm_csr(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes, const float *val,
+                  const float *x, float *y, int64_t n_dst, int feat, int reduce_op, int compute_op,
+                  void *stream);
+
+/*
+ * out[r, f] = sum over heads of in[r, h, f] (heads added in order into one fp32 accumulator): the head
+ * reduction of spmm_multihead's PreReduce / Optimal schedules, which return [n, feat]
+ * (src/cpp/src/spmm_host.cu:158-196).
+ */
+int cxg_head_sum(const void *in, void *out, int64_t n_row, int heads, int feat, int dtype,
+                 void *stream);
+
+/*
  * gather / GatherFunction (src/cpp/src/aggr.cu:42-62,395-448). backward = 0:
  * out[dest[e],:] += in[e,:] (out [n_node, feat] zero-filled by the caller, atomic adds);
  * backward = 1: out[e,:] = in[dest[e],:].
@@ -227,6 +254,16 @@ int cxg_typed_linear(const float *x, const float *w, float *out, const int32_t *
 int cxg_rgcn_direct(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
                     const int32_t *rel, const float *x, const float *w, float *y,
                     int64_t n_dst, int k, int n, void *stream);
+
+/*
+ * topo_sort (src/cpp/src/schedule.cu:72-124, python_bindings/binding.cpp:33) on HOST arrays: nodes in
+ * the order a breadth-first release by remaining in-degree gives; ptr/idx list the out-edges, degree
+ * the in-degrees. Cycles are stepped through as the reference does (degree-1 nodes, then the first
+ * node of the smallest remaining degree). order [n_node]; *n_order = nodes released.
+ */
+int cxg_topo_sort_host(const int64_t *ptr_host, const int64_t *idx_host,
+                       const int64_t *degree_host, int64_t n_node, int64_t *order_host,
+                       int64_t *n_order);
 
 /*
  * Per-relation sub-graphs on the host: rel_schedule (src/cpp/src/schedule.cu:5-63).

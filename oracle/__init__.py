@@ -174,6 +174,27 @@ def sddmm(src, dst, src_feat, dst_feat, per_head=False):
     return torch.from_numpy(out)
 
 
+def gspmm(ptr, idx, x, val=None, rop=0, cop=2):
+    """Generalised SpMM per orc_gspmm, fp32. rop: 0 sum 1 max 2 min 3 mean; cop: 0 add 1 sub 2 mul 3 div."""
+    p, i = _np(ptr, np.int64), _np(idx, np.int64)
+    xv = _np(x, np.float32)
+    v = None if val is None else _np(val, np.float32)
+    n, feat = len(p) - 1, xv.shape[1]
+    y = np.zeros((n, feat), dtype=np.float32)
+    lib().orc_gspmm(_ptr(p), _ptr(i), _ptr(v), _ptr(xv), _ptr(y), ctypes.c_int64(n), feat, int(rop), int(cop))
+    return torch.from_numpy(y)
+
+
+def topo_sort(ptr, idx, degree):
+    """Release order per orc_topo_sort; returns (order, number of nodes released)."""
+    p, i, d = _np(ptr, np.int64), _np(idx, np.int64), _np(degree, np.int64)
+    out = np.full(len(d), -1, dtype=np.int64)
+    fn = lib().orc_topo_sort
+    fn.restype = ctypes.c_int64
+    done = fn(_ptr(p), _ptr(i), _ptr(d), ctypes.c_int64(len(d)), _ptr(out))
+    return torch.from_numpy(out), int(done)
+
+
 def pad_rel(rel, count, thres, num_rel, base, idx=None):
     """In-place relation padding on int64 numpy/torch arrays (orc_pad_rel); returns (rel, idx)."""
     rel_n = _np(rel, np.int64).copy()

@@ -392,3 +392,93 @@ ORC_API void orc_typed_linear_f64(const float *a, const float *w, const int64_t 
     }
   }
 }
+
+/*
+ * Generalised SpMM of the dgSPARSE surface, following weightedCacheCoarsenSPMMKernel and init()
+ * (src/cpp/src/dgsparse.cu:324-378, src/cpp/include/dgsparse.h:14-131): per row and column one
+ * accumulator that starts at 0 (sum, mean), (float)INT_MIN (max) or (float)INT_MAX (min) when the row
+ * has edges and at 0 when it has none; edges in CSR order; reduce(acc, compute(val, x)) with
+ * compute add: val + x, sub: x - val, mul: val * x, div: x / val; max/min written as the reference's
+ * macros (a < b ? b : a, a < b ? a : b); mean divides by the edge count. val == NULL: operand x.
+ * acc + val * x is one fused multiply-add, as nvcc contracts it. rop: 0 sum 1 max 2 min 3 mean;
+ * cop: 0 add 1 sub 2 mul 3 div.
+ */
+ORC_API void orc_gspmm(const int64_t *ptr, const int64_t *idx, const float *val, const float *x,
+                       float *y, int64_t n_dst, int feat, int rop, int cop) {
+  for (int64_t r = 0; r < n_dst; ++r) {
+    const int64_t lo = ptr[r], hi = ptr[r + 1];
+    for (int c = 0; c < feat; ++c) {
+      float acc = 0.f;
+      if (hi > lo && rop == 1) acc = (float)INT32_MIN;
+      if (hi > lo && rop == 2) acc = (float)INT32_MAX;
+      for (int64_t e = lo; e < hi; ++e) {
+        const float xv = x[idx[e] * feat + c];
+        float t = xv;
+        if (val != NULL) {
+          const float v = val[e];
+          if ((rop == 0 || rop == 3) && cop == 2) {
+            acc = fmaf(v, xv, acc);
+            continue;
+          }
+          t = cop == 0 ? v + xv : cop == 1 ? xv - v : cop == 2 ? v * xv : xv / v;
+        }
+        if (rop == 1)
+          acc = acc < t ? t : acc;
+        else if (rop == 2)
+          acc = acc < t ? acc : t;
+        else
+          acc = acc + t;
+      }
+      if (rop == 3 && hi > lo) acc = acc / (float)(hi - lo);
+      y[r * feat + c] = acc;
+    }
+  }
+}
+
+/*
+ * topo_sort (src/cpp/src/schedule.cu:72-124): Kahn's algorithm over out-edges ptr/idx with the given
+ * in-degrees; when the queue runs dry before every node is out, every node left with degree 1 is
+ * released and, if some node has degree > 1, the lowest-numbered node of the smallest such degree is
+ * released too (which is how the reference steps through cycles). Returns the number of nodes
+ * written to out.
+ */
+ORC_API int64_t orc_topo_sort(const int64_t *ptr, const int64_t *idx, const int64_t *degree,
+                              int64_t n, int64_t *out) {
+  int64_t *deg = (int64_t *)malloc(sizeof(int64_t) * (size_t)(n > 0 ? n : 1));
+  int64_t *queue = (int64_t *)malloc(sizeof(int64_t) * (size_t)(n > 0 ? n : 1) * 2);
+  int64_t qh = 0, qt = 0, cnt = 0;
+  memcpy(deg, degree, sizeof(int64_t) * (size_t)n);
+  /* a node enters the queue at most twice (once by reaching 0, once released), so 2n slots do */
+  for (int64_t i = 0; i < n; ++i)
+    if (deg[i] == 0) queue[qt++] = i;
+  while (cnt < n) {
+    while (qh < qt && cnt < n) {
+      const int64_t cur = queue[qh++];
+      out[cnt++] = cur;
+      for (int64_t e = ptr[cur]; e < ptr[cur + 1]; ++e) {
+        const int64_t nx = idx[e];
+        if (--deg[nx] == 0 && qt < 2 * n) queue[qt++] = nx;
+      }
+    }
+    if (cnt >= n) break;
+    int64_t min_deg = n, pick = -1;
+    for (int64_t i = 0; i < n; ++i) {
+      if (deg[i] < min_deg && deg[i] > 1) {
+        min_deg = deg[i];
+        pick = i;
+      } else if (deg[i] == 1) {
+        deg[i] = 0;
+        if (qt < 2 * n) queue[qt++] = i;
+      }
+    }
+    if (pick != -1) {
+      if (qt < 2 * n) queue[qt++] = pick;
+      deg[pick] = 0;
+    } else if (qh == qt) {
+      break;
+    }
+  }
+  free(deg);
+  free(queue);
+  return cnt;
+}

@@ -281,3 +281,40 @@ def test_arxiv_shape_config(cuda):
     # cxgnncomp/graph_conv.py:57-77)
     fwd_on_dy = be.run_spmm_configurable(p, i, dy.cuda(), n)
     assert rel_err(xg.grad.cpu(), fwd_on_dy.cpu()) < 1e-4  # same hub-row rounding as above
+
+
+@pytest.mark.parametrize("feat", [128, 36, 7])
+@pytest.mark.parametrize("rop", [0, 1, 2, 3])
+def test_gspmm_bit_exact(cuda, feat, rop):
+    """GSpMM_u / GSpMM_u_e (dgSPARSE surface: int32 CSR, fp32): every reduce op, every compute op, rows without
+    edges, vector and scalar column paths; bit-exact against the C restatement."""
+    import cxgnncomp_backend as be
+    ptr, idx = random_csr(300, 260, 7, seed=50 + feat, hub=900)
+    x = randn((260, feat), 51)
+    val = randn((idx.shape[0],), 52).abs() + 0.5
+    p32, i32 = ptr.int().cuda(), idx.int().cuda()
+    got = be.GSpMM_u(p32, i32, x.cuda(), be.REDUCEOP(rop))
+    assert torch.equal(got.cpu(), oracle.gspmm(ptr, idx, x, None, rop))
+    for cop in range(4):
+        got = be.GSpMM_u_e(p32, i32, val.cuda(), x.cuda(), be.REDUCEOP(rop), be.COMPUTEOP(cop))
+        assert torch.equal(got.cpu(), oracle.gspmm(ptr, idx, x, val, rop, cop)), (rop, cop)
+    if rop == 1:  # max against torch on the rows that have edges
+        dst = oracle.dst_of_edges(ptr)
+        want = torch.full((300, feat), float("-inf")).scatter_reduce_(0, dst[:, None].expand(-1, feat), x[idx], "amax")
+        has = (ptr[1:] - ptr[:-1]) > 0
+        assert torch.equal(be.GSpMM_u(p32, i32, x.cuda(), be.MAX).cpu()[has], want[has])
+
+
+def test_multihead_head_sum(cuda):
+    """spmm_multihead with the PreReduce / Optimal schedules returns the heads summed (spmm_host.cu:158-196)."""
+    import cxgnncomp_backend as be
+    ptr, idx = random_csr(200, 180, 6, seed=60)
+    x = randn((180, 4, 32), 61)
+    val = randn((idx.shape[0], 4), 62)
+    naive = be.spmm_multihead(ptr.cuda(), idx.cuda(), val.cuda(), x.cuda(), 200, be.Naive)
+    opt = be.spmm_multihead(ptr.cuda(), idx.cuda(), val.cuda(), x.cuda(), 200, be.Optimal)
+    assert opt.shape == (200, 32)
+    want = naive[:, 0].clone()
+    for h in range(1, 4):
+        want += naive[:, h]
+    assert torch.equal(opt, want)

@@ -200,3 +200,26 @@ def test_tiled_order_oracle():
         assert rel_err(t_, oracle.spmm_f64(ptr, idx, x)) < 1e-5
     m = oracle.spmm(ptr, idx, x, tile=7, mean=True)
     assert rel_err(m, oracle.spmm_f64(ptr, idx, x, mean=True)) < 1e-5
+
+
+def test_gspmm_oracle_against_torch():
+    """The C restatement of the dgSPARSE GSpMM against torch scatter formulations: max / min are exact, sum and
+    mean agree to rounding, and the four compute ops follow the reference's operand order (x - v, x / v)."""
+    from helpers import random_csr, randn
+    ptr, idx = random_csr(90, 80, 5, seed=1, hub=120)
+    x = randn((80, 12), 2)
+    val = randn((idx.shape[0],), 3).abs() + 0.5
+    dst = oracle.dst_of_edges(ptr)
+    has = (ptr[1:] - ptr[:-1]) > 0
+    ex = dst[:, None].expand(-1, 12)
+    for cop, fn in enumerate((lambda v, t: v + t, lambda v, t: t - v, lambda v, t: v * t, lambda v, t: t / v)):
+        e = fn(val[:, None], x[idx])
+        mx = torch.full((90, 12), float("-inf")).scatter_reduce_(0, ex, e, "amax")
+        mn = torch.full((90, 12), float("inf")).scatter_reduce_(0, ex, e, "amin")
+        sm = torch.zeros(90, 12, dtype=torch.float64).index_add_(0, dst, e.double())
+        assert torch.equal(oracle.gspmm(ptr, idx, x, val, 1, cop)[has], mx[has])
+        assert torch.equal(oracle.gspmm(ptr, idx, x, val, 2, cop)[has], mn[has])
+        assert float((oracle.gspmm(ptr, idx, x, val, 0, cop).double() - sm).abs().max()) < 1e-4
+        mean = sm / (ptr[1:] - ptr[:-1]).clamp(min=1)[:, None]
+        assert float((oracle.gspmm(ptr, idx, x, val, 3, cop).double() - mean).abs().max()) < 1e-5
+        assert bool((oracle.gspmm(ptr, idx, x, val, 1, cop)[~has] == 0).all())  # rows without edges give 0
