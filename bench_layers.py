@@ -75,11 +75,21 @@ def config1(steps, flush):
     p, i, xg, dyg = ptr.cuda(), idx.cuda(), x.cuda(), dy.cuda()
     nnz = idx.shape[0]
     fwd = gpu_ms(lambda: be.run_spmm_configurable(p, i, xg, n), steps, flush)
+    be.BACKWARD_MODE = "scatter"
     bwd = gpu_ms(lambda: be.run_spmm_configurable_bwd(p, i, xg, dyg, n), steps, flush)
+    err_b = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0])
+    be.BACKWARD_MODE = "transpose"  # the transposed graph is built on the first call and cached
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    be.run_spmm_configurable_bwd(p, i, xg, dyg, n)
+    torch.cuda.synchronize()
+    transpose_build_ms = (time.perf_counter() - t0) * 1e3
+    bwd_t = gpu_ms(lambda: be.run_spmm_configurable_bwd(p, i, xg, dyg, n), steps, flush)
+    err_bt = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0])
+    be.BACKWARD_MODE = "auto"
     bwd_sym = gpu_ms(lambda: be.run_spmm_configurable(p, i, dyg, n), steps, flush)  # AggrOP.backward on a symmetric graph
     y = be.run_spmm_configurable(p, i, xg, n).cpu()
     err_f = rel(y, oracle.spmm_f64(ptr, idx, x))
-    err_b = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0])
     xr = x.clone().requires_grad_(True)
     dst = oracle.dst_of_edges(ptr)
 
@@ -93,7 +103,8 @@ def config1(steps, flush):
     c_fb = cpu_ms(cpu_fb)
     b_alg = 2 * n * 128 * 4 + nnz * 8 + (n + 1) * 8
     return {"config": "c1 GCN SpMM fwd/bwd", "nodes": n, "nnz": nnz, "gpu_fwd_ms": fwd, "gpu_bwd_scatter_ms": bwd,
-            "gpu_bwd_symmetric_ms": bwd_sym, "b_alg_bytes": b_alg, "fwd_GBps": b_alg / fwd / 1e6,
+            "gpu_bwd_transposed_ms": bwd_t, "transpose_build_first_call_ms": transpose_build_ms,
+            "max_rel_err_bwd_transposed": err_bt, "gpu_bwd_symmetric_ms": bwd_sym, "b_alg_bytes": b_alg, "fwd_GBps": b_alg / fwd / 1e6,
             "fwd_gflops": 2 * nnz * 128 / fwd / 1e6, "cpu_fwd_sparse_mm_ms": c_fwd, "cpu_fwd_bwd_index_add_ms": c_fb,
             "cpu_cores": torch.get_num_threads(), "max_rel_err_fwd": err_f, "max_rel_err_bwd": err_b}
 
@@ -146,6 +157,105 @@ def config2(steps, flush):
     return {"config": "c2 GAT layer fwd+bwd (4 heads x 32)", "nodes": n, "nnz": nnz, "gpu_fwd_ms": t_f,
             "gpu_fwd_bwd_ms": t_fb, "aggregate_b_alg_bytes": b_alg, "cpu_fwd_bwd_ms": c_fb,
             "cpu_cores": torch.get_num_threads(), "max_rel_err_fwd": err, "max_rel_err_grad_x": err_g}
+
+
+def config3(steps, flush, scale=1.0):
+    """GraphSAGE (mean) mini-batch training, 2.449 M nodes / ~126 M edges, F 100 -> 256 -> 256 -> 47, 1024 seeds,
+    fanouts 15 / 10 / 5 counted from the seeds, 8 % of the nodes as training set: epoch time with the stages of a
+    step (sample, feature gather, forward + backward + Adam) timed apart, and the same step in the torch index_add
+    formulation on the host cores."""
+    import cxgnncomp
+    import oracle
+    from cxgnncomp import synthetic
+    n, e_und = synthetic.CONFIG_SHAPES["products_like"]
+    n, e_und = int(n * scale), int(e_und * scale)
+    dev = torch.device("cuda")
+    ptr, idx = synthetic.powerlaw_graph(n, e_und, seed=0, device=dev)
+    x = synthetic.node_features(n, 100, seed=0, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    y = torch.randint(0, 47, (n,), device=dev, generator=g)
+    train = torch.randperm(n, device=dev, generator=g)[:int(0.08 * n)]
+    fanouts, bs = [15, 10, 5], 1024
+    torch.manual_seed(0)
+    model = cxgnncomp.SAGE(100, 256, 47, 3).cuda()
+    opt = torch.optim.Adam(model.parameters(), lr=0.003)
+    sampler = cxgnncomp.NeighborSampler(ptr, idx, fanouts)
+    nb = cxgnncomp.num_batches(train.shape[0], bs)
+    cxgnncomp.train_epoch(model, opt, sampler, x, y, train, bs, epoch=0, max_batches=10)  # warm-up
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    losses = cxgnncomp.train_epoch(model, opt, sampler, x, y, train, bs, epoch=1)
+    b.record()
+    b.synchronize()
+    epoch_ms, wall_ms = a.elapsed_time(b), (time.perf_counter() - t0) * 1e3
+    # stages of a step over 20 batches
+    seeds_list = [train[i * bs:(i + 1) * bs] for i in range(20)]
+    batches = []
+
+    def stage(fn):
+        torch.cuda.synchronize()
+        t = time.perf_counter()
+        for i, s_ in enumerate(seeds_list):
+            fn(i, s_)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t) * 1e3 / len(seeds_list)
+
+    samples = []
+    t_sample = stage(lambda i, s_: samples.append(sampler.sample(s_, seed=i)))
+    t_gather = stage(lambda i, s_: batches.append(cxgnncomp.Batch(x[samples[i][0]], samples[i][1], samples[i][2],
+                                                                  samples[i][3], samples[i][4], y=y[s_])))
+
+    def step(i, s_):
+        opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.nll_loss(model(batches[i]), batches[i].y)
+        loss.backward()
+        opt.step()
+
+    t_step = stage(step)
+    nodes_per_batch = sum(int(s_[3][-1]) for s_ in samples) / len(samples)
+    edges_per_batch = sum(int(s_[4][-1]) for s_ in samples) / len(samples)
+
+    # the same step on the host cores: aggregation as index_add (the reference's CPU formulation), autograd
+    torch.set_num_threads(os.cpu_count() or 1)
+    params = {k: v.detach().cpu().clone().requires_grad_(True) for k, v in model.named_parameters()}
+    cpu_opt = torch.optim.Adam(list(params.values()), lr=0.003)
+
+    def cpu_step(bt):
+        h, pc, ic = bt.x.cpu(), bt.ptr.cpu(), bt.idx.cpu()
+        for i in range(3):
+            nn_, ne_ = bt.num_node_in_layer[2 - i], bt.num_edge_in_layer[2 - i]
+            wl, bl = params[f"convs.{i}.lin_l.weight"], params[f"convs.{i}.lin_l.bias"]
+            if wl.shape[1] > wl.shape[0]:  # wide input: transform, then aggregate (graph_conv.py:142-152)
+                agg = oracle.torch_spmm_index_add(h @ wl.t() + bl, pc[:nn_ + 1], ic[:ne_], nn_, mean=True)
+            else:
+                agg = oracle.torch_spmm_index_add(h, pc[:nn_ + 1], ic[:ne_], nn_, mean=True) @ wl.t() + bl
+            h = agg + h[:nn_] @ params[f"convs.{i}.lin_r.weight"].t()
+            if i != 2:
+                h = torch.relu(torch.nn.functional.batch_norm(h, None, None, params[f"bns.{i}.weight"],
+                                                              params[f"bns.{i}.bias"], training=True))
+                h = torch.nn.functional.dropout(h, 0.5)
+        cpu_opt.zero_grad()
+        torch.nn.functional.nll_loss(h.log_softmax(-1), bt.y.cpu()).backward()
+        cpu_opt.step()
+
+    cpu_step(batches[0])
+    ts = []
+    for bt in batches[1:4]:
+        t = time.perf_counter()
+        cpu_step(bt)
+        ts.append((time.perf_counter() - t) * 1e3)
+    cpu_step_ms = sorted(ts)[1]
+    return {"config": "c3 GraphSAGE mini-batch training (100 -> 256 -> 256 -> 47)", "nodes": n, "nnz": int(idx.shape[0]),
+            "fanouts_from_seeds": fanouts, "batch_size": bs, "train_fraction": 0.08, "batches_per_epoch": nb,
+            "epoch_ms": epoch_ms, "epoch_wall_ms": wall_ms, "ms_per_batch": epoch_ms / nb,
+            "stage_ms_per_batch": {"sample": t_sample, "feature_gather": t_gather, "forward_backward_adam": t_step},
+            "nodes_per_batch": nodes_per_batch, "edges_per_batch": edges_per_batch,
+            "loss_first_last": [float(losses[0]), float(losses[-1])],
+            "cpu_step_ms_index_add_formulation": cpu_step_ms, "cpu_epoch_ms_extrapolated": cpu_step_ms * nb,
+            "cpu_cores": torch.get_num_threads(),
+            "note": "CPU step excludes sampling and feature gather (batches taken from the GPU sampler)"}
 
 
 def config4(steps, flush, scale=1.0):
@@ -217,12 +327,16 @@ def main():
     ap.add_argument("--configs", default="c1,c2,c4")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--c4-scale", type=float, default=1.0, help="shrink configuration 4 (nodes and edges) by this factor")
+    ap.add_argument("--c3-scale", type=float, default=1.0, help="shrink configuration 3 (nodes and edges) by this factor")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "needs a CUDA device"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    table = {"c1": config1, "c2": config2, "c4": config4}
+    table = {"c1": config1, "c2": config2, "c3": config3, "c4": config4}
     for c in args.configs.split(","):
-        res = table[c](args.steps, flush, args.c4_scale) if c == "c4" else table[c](args.steps, flush)
+        if c in ("c3", "c4"):
+            res = table[c](args.steps, flush, args.c4_scale if c == "c4" else args.c3_scale)
+        else:
+            res = table[c](args.steps, flush)
         print(json.dumps(res), flush=True)
 
 

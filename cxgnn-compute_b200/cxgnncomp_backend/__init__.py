@@ -193,6 +193,46 @@ def _spmm_forward(x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, out=N
     return out
 
 
+# dX = A^T dY is a forward aggregation over the transposed graph: deterministic and on the fast forward
+# kernel, where the scatter kernel adds with atomics in no fixed order (like the reference's backward,
+# aggr_kernel.cu:188-273). Transposing costs a sort of the edges, so it is done for a graph whose backward is
+# asked for the second time (full-graph training) and kept in a small cache; sampled batches, whose graphs are
+# seen once, stay on the scatter kernel. BACKWARD_MODE: "auto" | "scatter" | "transpose".
+BACKWARD_MODE = os.environ.get("CXG_BACKWARD_MODE", "auto")
+_TRANSPOSE_CACHE = {}
+_TRANSPOSE_SEEN = {}
+_TRANSPOSE_CACHE_MAX = 4
+
+
+def _transposed_graph(ptr, idx, n, n_src):
+    """(t_ptr [n_src + 1], t_idx = destination of every transposed edge, t_eid = its edge id in the forward
+    graph, 1 / in-degree per destination) for the first n rows, or None while the graph has been seen once."""
+    key = (ptr.data_ptr(), idx.data_ptr(), n, n_src, ptr._version, idx._version, str(ptr.device))
+    hit = _TRANSPOSE_CACHE.get(key)
+    if hit is not None:
+        return hit[:4]
+    if BACKWARD_MODE == "auto":
+        seen = _TRANSPOSE_SEEN.get(key, 0)
+        if len(_TRANSPOSE_SEEN) > 64:
+            _TRANSPOSE_SEEN.clear()
+        _TRANSPOSE_SEEN[key] = seen + 1
+        if seen == 0:
+            return None
+    deg = (ptr[1:n + 1] - ptr[:n]).long()
+    nnz = int(ptr[n])
+    dst = torch.repeat_interleave(torch.arange(n, device=ptr.device, dtype=idx.dtype), deg)
+    src = idx[:nnz]
+    order = torch.sort(src, stable=True).indices  # stable: destinations ascending within a source row
+    t_ptr = torch.zeros(n_src + 1, dtype=torch.int64, device=ptr.device)
+    torch.cumsum(torch.bincount(src, minlength=n_src), 0, out=t_ptr[1:])
+    entry = (t_ptr, dst[order].contiguous(), order, 1.0 / deg.clamp(min=1).float())
+    while len(_TRANSPOSE_CACHE) >= _TRANSPOSE_CACHE_MAX:
+        _TRANSPOSE_CACHE.pop(next(iter(_TRANSPOSE_CACHE)))
+    # ptr and idx are kept alive with the entry, so their addresses cannot be handed to another graph
+    _TRANSPOSE_CACHE[key] = entry + (ptr, idx)
+    return entry
+
+
 def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, need_dx=True,
                    need_dval=False, grad_x=None, edge_mask=None, edge_rel=None, rel_stride=0, targets=None,
                    x_shape=None):
@@ -203,6 +243,20 @@ def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG
     feat = grad_out.shape[-1]
     if x_shape is None:
         x_shape = x.shape
+    dx_t = None
+    if (need_dx and BACKWARD_MODE != "scatter" and grad_x is None and edge_mask is None and edge_rel is None
+            and targets is None and n > 0):
+        tg = _transposed_graph(ptr, idx, n, x_shape[0])
+        if tg is not None:
+            t_ptr, t_idx, t_eid, inv_deg = tg
+            dy = grad_out
+            if reduce == CXG_MEAN:
+                dy = (grad_out.float() * inv_deg.view(-1, *([1] * (grad_out.dim() - 1)))).to(grad_out.dtype)
+            t_val = None if edge_val is None else edge_val[t_eid].contiguous()
+            dx_t = _spmm_forward(dy, t_ptr, t_idx, x_shape[0], edge_val=t_val)
+            need_dx = False
+            if not need_dval:
+                return dx_t, None
     dx = None
     if need_dx:
         dx = grad_x if grad_x is not None else torch.zeros(x_shape, dtype=torch.float32, device=grad_out.device)
@@ -219,7 +273,7 @@ def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG
     with torch.cuda.device(grad_out.device):
         _check(_spmm_bwd(ctypes.byref(desc), _p(grad_out), _p(dx), _p(dval), _stream()),
                "cxg_spmm_csr_backward")
-    return dx, dval
+    return (dx_t if dx_t is not None else dx), dval
 
 
 # --------------------------------------------------------------------------------------
@@ -315,6 +369,29 @@ class SPMM_MULTIHEAD_SCHEDULE(enum.IntEnum):
 Naive = SPMM_MULTIHEAD_SCHEDULE.Naive
 PreReduce = SPMM_MULTIHEAD_SCHEDULE.PreReduce
 Optimal = SPMM_MULTIHEAD_SCHEDULE.Optimal
+
+
+_sample = _sig("cxg_sample_neighbors", [_vp, _vp, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.c_int, _vp, _vp,
+                                        ctypes.c_uint64, _vp])
+
+
+def sample_neighbors(graph_ptr, graph_idx, frontier, fanout, seed):
+    """min(degree, fanout) distinct in-neighbours of every frontier node, uniformly without replacement, as a CSR
+    (out_ptr int64 [n + 1], out int64 global ids). Deterministic in (seed, node id). This is the step the reference
+    takes from its external loader (neighbor_sample, cxgnncomp/data_preparation.py:214-215)."""
+    _cuda(graph_ptr, "graph_ptr", _INDEX_DTYPES)
+    _cuda(graph_idx, "graph_idx", _INDEX_DTYPES)
+    _cuda(frontier, "frontier", (torch.int64,))
+    n = frontier.shape[0]
+    deg = (graph_ptr[frontier + 1] - graph_ptr[frontier]).long()
+    out_ptr = torch.zeros(n + 1, dtype=torch.int64, device=frontier.device)
+    torch.cumsum(deg.clamp(max=int(fanout)), 0, out=out_ptr[1:])
+    out = torch.empty(int(out_ptr[-1]), dtype=torch.int64, device=frontier.device)
+    with torch.cuda.device(frontier.device):
+        _check(_sample(_p(graph_ptr), _p(graph_idx), graph_ptr.element_size(), graph_idx.element_size(), _p(frontier), n,
+                       int(fanout), _p(out_ptr), _p(out), int(seed) & 0xFFFFFFFFFFFFFFFF, _stream()),
+               "cxg_sample_neighbors")
+    return out_ptr, out
 
 
 class REDUCEOP(enum.IntEnum):

@@ -256,6 +256,18 @@ int cxg_rgcn_direct(const void *ptr, const void *idx, int ptr_bytes, int idx_byt
                     int64_t n_dst, int k, int n, void *stream);
 
 /*
+ * Neighbour sampling for mini-batches in the CSR_Layer format (the step the reference takes from its
+ * external loader: neighbor_sample at cxgnncomp/data_preparation.py:214-215, test/ae/E2_spmm/perf-spmm.py:45-46).
+ * For frontier node v = frontier[i] with in-degree d: out[out_ptr[i] .. out_ptr[i] + min(d, fanout)) receives
+ * min(d, fanout) distinct in-neighbours of v (global ids), in the order of v's CSR row; all of them when
+ * d <= fanout, else a uniform subset drawn by Floyd's algorithm from a counter-based generator keyed by
+ * (seed, v). out_ptr is the caller's exclusive prefix sum of min(d, fanout). fanout <= 64.
+ */
+int cxg_sample_neighbors(const void *graph_ptr, const void *graph_idx, int ptr_bytes, int idx_bytes,
+                         const int64_t *frontier, int64_t n_front, int fanout,
+                         const int64_t *out_ptr, int64_t *out, uint64_t seed, void *stream);
+
+/*
  * topo_sort (src/cpp/src/schedule.cu:72-124, python_bindings/binding.cpp:33) on HOST arrays: nodes in
  * the order a breadth-first release by remaining in-degree gives; ptr/idx list the out-edges, degree
  * the in-degrees. Cycles are stepped through as the reference does (degree-1 nodes, then the first

@@ -185,6 +185,18 @@ def gspmm(ptr, idx, x, val=None, rop=0, cop=2):
     return torch.from_numpy(y)
 
 
+def sample_neighbors(gptr, gidx, frontier, fanout, seed):
+    """(out_ptr, out) per orc_sample_neighbors."""
+    p, i, f = _np(gptr, np.int64), _np(gidx, np.int64), _np(frontier, np.int64)
+    cnt = np.minimum(p[f + 1] - p[f], fanout)
+    out_ptr = np.zeros(len(f) + 1, dtype=np.int64)
+    out_ptr[1:] = np.cumsum(cnt)
+    out = np.full(int(out_ptr[-1]), -1, dtype=np.int64)
+    lib().orc_sample_neighbors(_ptr(p), _ptr(i), _ptr(f), ctypes.c_int64(len(f)), int(fanout), _ptr(out_ptr), _ptr(out),
+                               ctypes.c_uint64(seed))
+    return torch.from_numpy(out_ptr), torch.from_numpy(out)
+
+
 def topo_sort(ptr, idx, degree):
     """Release order per orc_topo_sort; returns (order, number of nodes released)."""
     p, i, d = _np(ptr, np.int64), _np(idx, np.int64), _np(degree, np.int64)

@@ -482,3 +482,45 @@ ORC_API int64_t orc_topo_sort(const int64_t *ptr, const int64_t *idx, const int6
   free(queue);
   return cnt;
 }
+
+/*
+ * Neighbour sampling restated from the library's definition (the reference takes this step from its
+ * external loader, cxgnncomp/data_preparation.py:214-215): per frontier node v of in-degree d, all
+ * neighbours when d <= fanout, else Floyd's subset algorithm over positions 0 .. d-1 with draw number k
+ * taken from splitmix64(splitmix64(seed ^ v * 0xD1B54A32D192ED03) + k) by multiply-shift, positions
+ * sorted ascending. out_ptr = exclusive prefix sum of min(d, fanout).
+ */
+static uint64_t orc_splitmix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+ORC_API void orc_sample_neighbors(const int64_t *gptr, const int64_t *gidx, const int64_t *frontier,
+                                  int64_t n_front, int fanout, const int64_t *out_ptr, int64_t *out,
+                                  uint64_t seed) {
+  for (int64_t i = 0; i < n_front; ++i) {
+    const int64_t v = frontier[i], lo = gptr[v], deg = gptr[v + 1] - lo;
+    int64_t *o = out + out_ptr[i];
+    if (deg <= fanout) {
+      for (int64_t j = 0; j < deg; ++j) o[j] = gidx[lo + j];
+      continue;
+    }
+    int64_t pick[64];
+    int k = 0;
+    const uint64_t base = orc_splitmix64(seed ^ ((uint64_t)v * 0xD1B54A32D192ED03ull));
+    for (int64_t j = deg - fanout; j < deg; ++j) {
+      const uint64_t h = orc_splitmix64(base + (uint64_t)k);
+      int64_t t = (int64_t)(((h >> 32) * (uint64_t)(j + 1)) >> 32);
+      int seen = 0;
+      for (int q = 0; q < k; ++q) seen |= pick[q] == t;
+      if (seen) t = j;
+      int q = k;
+      for (; q > 0 && pick[q - 1] > t; --q) pick[q] = pick[q - 1];
+      pick[q] = t;
+      ++k;
+    }
+    for (int q = 0; q < fanout; ++q) o[q] = gidx[lo + pick[q]];
+  }
+}

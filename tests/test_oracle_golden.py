@@ -223,3 +223,26 @@ def test_gspmm_oracle_against_torch():
         mean = sm / (ptr[1:] - ptr[:-1]).clamp(min=1)[:, None]
         assert float((oracle.gspmm(ptr, idx, x, val, 3, cop).double() - mean).abs().max()) < 1e-5
         assert bool((oracle.gspmm(ptr, idx, x, val, 1, cop)[~has] == 0).all())  # rows without edges give 0
+
+
+def test_sampler_oracle_properties():
+    """The C restatement of the neighbour sampler: counts, membership, no position drawn twice, rows kept in CSR
+    order, and uniform frequencies (degree 40, 5 draws, 4000 seeds: 1/8 each within 4 standard deviations)."""
+    from helpers import random_csr
+    ptr, idx = random_csr(200, 5000, 20, seed=4, hub=700)  # 5000 sources: duplicates within a row are rare
+    frontier = torch.arange(200)
+    out_ptr, out = oracle.sample_neighbors(ptr, idx, frontier, 8, 11)
+    deg = ptr[1:] - ptr[:-1]
+    assert torch.equal(out_ptr[1:] - out_ptr[:-1], deg.clamp(max=8))
+    for r in range(200):
+        row = idx[ptr[r]:ptr[r + 1]].tolist()
+        got = out[out_ptr[r]:out_ptr[r + 1]].tolist()
+        it = iter(row)
+        assert all(any(g == v for v in it) for g in got)  # an ordered sub-sequence of the row
+    ptr2, idx2 = torch.tensor([0, 40]), torch.arange(40)
+    counts = torch.zeros(40)
+    for s in range(4000):
+        _, o = oracle.sample_neighbors(ptr2, idx2, torch.zeros(1, dtype=torch.int64), 5, s)
+        assert o.unique().shape[0] == 5
+        counts[o] += 1
+    assert float((counts - 500).abs().max()) < 4 * (4000 * 0.125 * 0.875) ** 0.5
