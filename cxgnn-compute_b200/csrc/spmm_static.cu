@@ -20,8 +20,8 @@
 //
 // In host code the array's name is only a host-side handle, not a device address. The
 // address is looked up with cudaGetSymbolAddress, once per device with that device current,
-// by the first call made on that device; that first call should therefore happen before any
-// stream capture is started. No cudaMalloc, cudaFree or other allocating routine is called.
+// by the first call made on that device. No cudaMalloc, cudaFree or other allocating routine is
+// called.
 #include <mutex>
 
 #include "common.cuh"

@@ -331,7 +331,7 @@ int cxg_typed_matmul(const void *a, const void *w, void *c, const int64_t *rel,
  *     that overlap on the GPU (other streams, other host threads) corrupt each
  *     other: order them on the device.
  *   - The first call on each device looks the array's device address up
- *     (cudaGetSymbolAddress); make that call before starting any stream capture.
+ *     (cudaGetSymbolAddress).
  *   - It never calls cudaMalloc, cudaFree or any other allocating routine.
  * Results are those of cxg_spmm_csr, bit for bit.
  */
