@@ -183,6 +183,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("CXG_BENCH_WORKLOAD", "papers_like"),
                     choices=sorted(WORKLOADS))
+    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "needed"],
+                    help="multi-GPU feature exchange: one padded all-gather, or an all-to-all of only the rows each "
+                         "rank's edges name; auto takes the second when it moves under 80 %% of the rows")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -204,7 +207,7 @@ def main():
     import torch.distributed as dist
     import cxgnncomp_backend as be
     from cxgnncomp import synthetic
-    from cxgnncomp.distributed import RowPartition, exchange_features
+    from cxgnncomp.distributed import NeededRowsExchange, RowPartition, exchange_features
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local_rank)
@@ -223,34 +226,67 @@ def main():
     idx_bytes = idx.element_size()
     part = RowPartition(ptr, world)
     r0, r1 = part.rows(rank)
+    ex, exchange_mode, remote_rows = None, "none", 0
     if world > 1:
-        lptr, lidx = part.local_graph(ptr, idx, rank)
+        lptr, lidx = part.local_graph(ptr, idx, rank, gather_ids=False)
         full_ptr = ptr
         del idx
+        torch.cuda.empty_cache()
+        exchange_mode = args.exchange
+        remote_all = (world - 1) * part.shard_rows
+        if exchange_mode in ("auto", "needed"):
+            ex = NeededRowsExchange(part, lptr, lidx, rank, n)
+            frac = torch.tensor([ex.remote_rows() / max(remote_all, 1)], dtype=torch.float64, device=dev)
+            dist.all_reduce(frac, op=dist.ReduceOp.MAX)
+            if exchange_mode == "auto":
+                exchange_mode = "needed" if float(frac[0]) < 0.8 else "allgather"
+        if exchange_mode == "needed":
+            lidx = ex.lidx
+            remote_rows = ex.remote_rows()
+        else:
+            ex = None
+            lidx = part.to_gather_ids(lidx)
+            remote_rows = remote_all
     else:
         lptr, lidx, full_ptr = ptr, idx, ptr
     torch.cuda.empty_cache()
     n_local = r1 - r0
 
-    # features: every rank draws the same stream; with several ranks the matrix is re-laid out as the
-    # [world, shard_rows, F] gather buffer that the all-gather fills
+    # features: every rank draws the same stream. All-gather mode re-lays the matrix out as the
+    # [world, shard_rows, F] gather buffer; needed-rows mode keeps this rank's shard followed by the remote
+    # rows its edges name.
     x_full = synthetic.node_features(n, feat, seed=0, device=dev, dtype=dtype)
-    if world > 1:
+    send_buf = None
+    if world > 1 and ex is None:
         xg = torch.zeros((part.gather_rows(), feat), dtype=dtype, device=dev)
         for j in range(world):
             b0, b1 = part.rows(j)
             part.shard(xg, j).copy_(x_full[b0:b1])
         x_full = xg
         del xg
-    x_own = part.shard(x_full, rank) if world > 1 else x_full
+        x_own = part.shard(x_full, rank)
+    elif world > 1:
+        xb = torch.empty((ex.buffer_rows(), feat), dtype=dtype, device=dev)  # [own shard | remote rows]
+        ex.own(xb).copy_(x_full[r0:r1])
+        x_full = xb
+        del xb
+        torch.cuda.empty_cache()
+        x_own = ex.own(x_full)
+        send_buf = torch.empty((ex.send_rows.shape[0], feat), dtype=dtype, device=dev)
+    else:
+        x_own = x_full
     y = torch.empty((n_local, feat), dtype=dtype, device=dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     b_alg_total = algorithmic_bytes(n, n, nnz, feat, elem, idx_bytes)
     b_alg_local = algorithmic_bytes(n_local, n, int(lptr[n_local]), feat, elem, idx_bytes)
 
     def exchange():
-        """All ranks end up with every shard of x in x_full (one NCCL all-gather)."""
-        exchange_features(x_full, part, rank)
+        """x_full receives what this rank's aggregation reads: every shard (one NCCL all-gather) or the rows its
+        edges name (pack + one NCCL all-to-all)."""
+        if ex is not None:
+            ex.exchange(x_full, send_buf)
+        else:
+            exchange_features(x_full, part, rank)
 
     def step():
         if world > 1:
@@ -281,13 +317,16 @@ def main():
     # kernel-only time of the SpMM call (no exchange), for the roofline
     spmm_ms = timed(lambda: be._spmm_forward(x_full, lptr, lidx, n_local, out=y), args.steps) / args.steps
     barrier()
+    exch_ms = timed(exchange, args.steps) / args.steps if world > 1 else 0.0
+    barrier()
     clocks = sampler.stop() if sampler else None
 
-    t = torch.tensor([ms_total, spmm_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, spmm_ms, exch_ms, float(remote_rows)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t[0]) / args.steps
     spmm_ms = float(t[1])
+    exch_ms, remote_rows_max = float(t[2]), int(t[3])
     value = b_alg_total / (ms_step * 1e-3) / 1e9
 
     # end to end: inputs from pinned host memory, result back to the host, every step
@@ -336,6 +375,14 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline_sample(full_ptr, lidx, feat, dtype)
 
+    exchange_info = None
+    if world > 1:
+        # the exchange against the measured peer-copy rate of this pool (770 GB/s into each GPU)
+        bytes_in = remote_rows_max * feat * elem
+        exchange_info = {"mode": exchange_mode, "ms": exch_ms, "rows_into_busiest_gpu": remote_rows_max,
+                         "bytes_into_busiest_gpu": bytes_in, "achieved_GBps": bytes_in / (exch_ms * 1e-3) / 1e9,
+                         "nvlink_peak_GBps": 770.0, "frac": bytes_in / (exch_ms * 1e-3) / 1e9 / 770.0,
+                         "allgather_rows_per_gpu": (world - 1) * part.shard_rows}
     if rank == 0:
         line = {"metric": "spmm_algorithmic_hbm_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -343,9 +390,10 @@ def main():
                 "data": "synthetic",
                 "config": {"workload": args.workload, "description": desc, "nodes": n, "nnz": nnz, "feat": feat,
                            "idx_bytes": idx_bytes, "partition": f"rows by edge count over {world} GPU(s)",
+                           "exchange": exchange_mode,
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
-                "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
+                "gpu_launches": int(launches), "roofline": roofline, "exchange": exchange_info, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:

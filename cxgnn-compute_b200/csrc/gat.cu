@@ -20,7 +20,9 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kHeavyRow = 4096;
+constexpr int kHeavyRow = 1024;      // rows above this many edges get a whole CTA
+constexpr int kHeavyThreads = 1024;  // threads of that CTA
+constexpr int kHeavyWarps = kHeavyThreads / 32;
 constexpr int kHC = 4;  // heads carried together
 
 struct SoftmaxArgs {
@@ -53,7 +55,7 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// Block-wide sum / max of one value per thread (kThreads threads), result to all.
+// Block-wide sum / max of one value per thread (kHeavyThreads threads), result to all.
 __device__ __forceinline__ float block_sum(float v, float *sh) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -62,7 +64,7 @@ __device__ __forceinline__ float block_sum(float v, float *sh) {
   __syncthreads();
   float r = 0.f;
 #pragma unroll
-  for (int w = 0; w < kWarps; ++w) r += sh[w];
+  for (int w = 0; w < kHeavyWarps; ++w) r += sh[w];
   return r;
 }
 __device__ __forceinline__ float block_max(float v, float *sh) {
@@ -72,7 +74,7 @@ __device__ __forceinline__ float block_max(float v, float *sh) {
   __syncthreads();
   float r = sh[0];
 #pragma unroll
-  for (int w = 1; w < kWarps; ++w) r = fmaxf(r, sh[w]);
+  for (int w = 1; w < kHeavyWarps; ++w) r = fmaxf(r, sh[w]);
   return r;
 }
 
@@ -80,7 +82,7 @@ __device__ __forceinline__ float block_max(float v, float *sh) {
 // HEAVY = false: one warp, reference summation order. HEAVY = true: one CTA.
 template <typename IdxT, bool HEAVY>
 __device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh) {
-  constexpr int STEP = HEAVY ? kThreads : 32;
+  constexpr int STEP = HEAVY ? kHeavyThreads : 32;
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const int H = a.heads;
   const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
@@ -130,7 +132,7 @@ __device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d,
 // grad_dst = sum tmp, written only when the row has both signs (it is 0 otherwise).
 template <typename IdxT, bool HEAVY>
 __device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh) {
-  constexpr int STEP = HEAVY ? kThreads : 32;
+  constexpr int STEP = HEAVY ? kHeavyThreads : 32;
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const int H = a.heads;
   const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
@@ -190,8 +192,8 @@ __global__ void __launch_bounds__(kThreads) edge_softmax_rows(SoftmaxArgs a) {
 }
 
 template <typename IdxT, bool BWD>
-__global__ void __launch_bounds__(kThreads) edge_softmax_heavy(SoftmaxArgs a) {
-  __shared__ float sh[kWarps];
+__global__ void __launch_bounds__(kHeavyThreads) edge_softmax_heavy(SoftmaxArgs a) {
+  __shared__ float sh[kHeavyWarps];
   const int n = min(a.hdr[0], a.max_heavy);
   for (int i = blockIdx.x; i < n; i += gridDim.x) {
     if (BWD)
@@ -305,10 +307,10 @@ extern "C" int cxg_edge_softmax_forward(const void *ptr, const void *idx, int pt
   const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
   if (idx_bytes == 8) {
     edge_softmax_rows<int64_t, false><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int64_t, false><<<kNumSM, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int64_t, false><<<kNumSM, kHeavyThreads, 0, st>>>(a);
   } else {
     edge_softmax_rows<int32_t, false><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int32_t, false><<<kNumSM, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int32_t, false><<<kNumSM, kHeavyThreads, 0, st>>>(a);
   }
   count_launches(2);
   return check_launch("cxg_edge_softmax_forward");
@@ -332,10 +334,10 @@ extern "C" int cxg_edge_softmax_backward(const void *ptr, const void *idx, int p
   const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
   if (idx_bytes == 8) {
     edge_softmax_rows<int64_t, true><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int64_t, true><<<kNumSM, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int64_t, true><<<kNumSM, kHeavyThreads, 0, st>>>(a);
   } else {
     edge_softmax_rows<int32_t, true><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int32_t, true><<<kNumSM, kThreads, 0, st>>>(a);
+    edge_softmax_heavy<int32_t, true><<<kNumSM, kHeavyThreads, 0, st>>>(a);
   }
   count_launches(2);
   return check_launch("cxg_edge_softmax_backward");

@@ -9,10 +9,10 @@
 // Like the reference this is a scatter: the gradient row of a destination is held
 // in registers and pushed to every source of the row. The push is one 128-bit
 // vector reduction (`red.global.add.v4.f32`) per lane instead of four scalar
-// atomicAdds, and long rows are walked by many groups at once (a grid-stride loop
-// over fixed segments), so a hub row does not serialise on one warp. The order of
-// the additions into dX is not fixed (it is not in the reference either), so dX is
-// reproducible only up to fp32 rounding; dV has a fixed order.
+// atomicAdds, and the work is cut into tiles of consecutive edges rather than rows,
+// so a hub row does not serialise on one warp. The order of the additions into dX
+// is not fixed (it is not in the reference either), so dX is reproducible only up
+// to fp32 rounding; dV has a fixed order.
 #include "common.cuh"
 
 namespace cxg {
@@ -43,10 +43,14 @@ __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float 
                : "memory");
 }
 
-// One group of G lanes per (row, segment of kSegment edges). E = elements per lane
-// and vector (4 for fp32, 8 for bf16 gradients, 1 for the scalar path).
+// One group of G lanes per tile of kSegment consecutive edges, whatever rows they belong to: the
+// work is balanced by edges, so a hub row is spread over as many groups as it has tiles. The group
+// finds the row of its first edge by binary search in ptr, then walks its edges in CSR order and
+// reloads the gradient row whenever the walk enters a new row (the row ends of the next G rows
+// are kept one per lane). E = elements per lane and vector (4 for fp32, 8 for bf16 gradients, 1
+// for the scalar path).
 template <typename VT, typename T, typename IdxT, int G, int VALMODE, bool EDGE_GRAD>
-__global__ void __launch_bounds__(kThreads) spmm_bwd_rows(BwdArgs a) {
+__global__ void __launch_bounds__(kThreads) spmm_bwd_tiles(BwdArgs a) {
   constexpr int E = VT::kElems;
   constexpr int kGroupsPerBlock = kThreads / G;
   const int lane = threadIdx.x & 31;
@@ -56,84 +60,101 @@ __global__ void __launch_bounds__(kThreads) spmm_bwd_rows(BwdArgs a) {
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const T *dy = reinterpret_cast<const T *>(a.dy);
   const T *x = reinterpret_cast<const T *>(a.x);
-  int64_t row = static_cast<int64_t>(blockIdx.x) * kGroupsPerBlock + threadIdx.x / G;
-  if (row >= a.n_dst) return;
-  const int64_t rb = load_ptr(a.ptr, row, a.ptr_bytes);
-  const int64_t re = load_ptr(a.ptr, row + 1, a.ptr_bytes);
-  if (re <= rb) return;
-  const int64_t g_row = a.targets != nullptr ? __ldg(a.targets + row) : row;
-  const float inv = a.reduce == CXG_MEAN ? 1.f / static_cast<float>(re - rb) : 1.f;
-  // Segments of this row are dealt to gridDim.y groups.
-  for (int64_t sb = rb + static_cast<int64_t>(blockIdx.y) * kSegment; sb < re;
-       sb += static_cast<int64_t>(gridDim.y) * kSegment) {
-    const int64_t se = min(re, sb + kSegment);
-    for (int v0 = 0; v0 < nvec; v0 += G) {
-      const int v = v0 + lg;
-      const bool on = v < nvec;
-      const int col = v * E;
-      const int head = on ? col / a.feat : 0;
-      // Lanes that share a head: a power of two when dV is asked for.
-      const int lanes_per_head = a.feat / E;
-      float g[E];
-#pragma unroll
-      for (int i = 0; i < E; ++i) g[i] = 0.f;
-      if (on) {
-        VT::to_float(g, VT::load(dy + g_row * a.width + col));
-        if (a.reduce == CXG_MEAN) {
-#pragma unroll
-          for (int i = 0; i < E; ++i) g[i] *= inv;
+  const int64_t e_first = load_ptr(a.ptr, 0, a.ptr_bytes), e_last = load_ptr(a.ptr, a.n_dst, a.ptr_bytes);
+  const int64_t tile = static_cast<int64_t>(blockIdx.x) * kGroupsPerBlock + threadIdx.x / G;
+  const int64_t sb = e_first + tile * kSegment;
+  if (sb >= e_last) return;
+  const int64_t se = min(e_last, sb + static_cast<int64_t>(kSegment));
+  // row0 = last row whose first edge is <= sb (rows without edges in front of it are skipped)
+  int64_t lo = 0, hi = a.n_dst;  // invariant: ptr[lo] <= sb < ptr[hi]
+  while (hi - lo > 1) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (load_ptr(a.ptr, mid, a.ptr_bytes) <= sb)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  const int64_t row0 = lo;
+  const int lanes_per_head = a.feat / E;  // a power of two when dV is asked for
+
+  for (int v0 = 0; v0 < nvec; v0 += G) {
+    const int v = v0 + lg;
+    const bool on = v < nvec;
+    const int col = v * E;
+    const int head = on ? col / a.feat : 0;
+    // walk state: `row` owns the edges up to row_end; lane l keeps the end of row cache_base + l
+    int64_t row = row0, cache_base = row0;
+    int64_t my_end = load_ptr(a.ptr, min(cache_base + lg, a.n_dst - 1) + 1, a.ptr_bytes);
+    int64_t row_end = __shfl_sync(gmask, my_end, 0, G);
+    bool fresh = true;  // the gradient row of `row` is not loaded yet
+    float g[E];
+    for (int64_t e0 = sb; e0 < se; e0 += G) {
+      int64_t my_nid = -1;
+      float my_val = 1.f;
+      const int64_t e = e0 + lg;
+      if (e < se) {
+        const bool keep = a.edge_mask == nullptr || a.edge_mask[e] != 0;
+        if (keep) {
+          my_nid = static_cast<int64_t>(__ldg(idx + e));
+          if (a.edge_rel != nullptr) my_nid += static_cast<int64_t>(__ldg(a.edge_rel + e)) * a.rel_stride;
         }
+        if (VALMODE == 1) my_val = __ldg(a.edge_val + e);
       }
-      for (int64_t e0 = sb; e0 < se; e0 += G) {
-        int64_t my_nid = -1;
-        float my_val = 1.f;
-        int64_t e = e0 + lg;
-        if (e < se) {
-          bool keep = a.edge_mask == nullptr || a.edge_mask[e] != 0;
-          if (keep) {
-            my_nid = static_cast<int64_t>(__ldg(idx + e));
-            if (a.edge_rel != nullptr)
-              my_nid += static_cast<int64_t>(__ldg(a.edge_rel + e)) * a.rel_stride;
+      const int64_t left = se - e0;
+      const int cnt = left < G ? static_cast<int>(left) : G;
+      for (int j = 0; j < cnt; ++j) {
+        const int64_t ej = e0 + j;
+        while (ej >= row_end) {  // uniform over the group
+          ++row;
+          if (row - cache_base == G) {
+            cache_base = row;
+            my_end = load_ptr(a.ptr, min(cache_base + lg, a.n_dst - 1) + 1, a.ptr_bytes);
           }
-          if (VALMODE == 1) my_val = __ldg(a.edge_val + e);
+          row_end = __shfl_sync(gmask, my_end, static_cast<int>(row - cache_base), G);
+          fresh = true;
         }
-        int64_t left = se - e0;
-        int cnt = left < G ? static_cast<int>(left) : G;
-        for (int j = 0; j < cnt; ++j) {
-          int64_t nid = __shfl_sync(gmask, my_nid, j, G);
-          float val = 1.f;
-          if (VALMODE == 1) val = __shfl_sync(gmask, my_val, j, G);
-          if (VALMODE == 2 && on) val = __ldg(a.edge_val + (e0 + j) * a.heads + head);
-          if (nid < 0) continue;
-          if (a.dx != nullptr && on) {
-            float *dst = a.dx + nid * a.width + col;
-            if (E % 4 == 0) {
+        if (fresh) {
+          fresh = false;
+          const int64_t g_row = a.targets != nullptr ? __ldg(a.targets + row) : row;
 #pragma unroll
-              for (int i = 0; i < E; i += 4)
-                red_add_v4(dst + i, g[i] * val, g[(i + 1) % E] * val, g[(i + 2) % E] * val,
-                           g[(i + 3) % E] * val);
-            } else {
+          for (int i = 0; i < E; ++i) g[i] = 0.f;
+          if (on) {
+            VT::to_float(g, VT::load(dy + g_row * a.width + col));
+            if (a.reduce == CXG_MEAN) {
+              const float inv = 1.f / static_cast<float>(row_end - load_ptr(a.ptr, row, a.ptr_bytes));
 #pragma unroll
-              for (int i = 0; i < E; ++i) atomicAdd(dst + i, g[i] * val);
+              for (int i = 0; i < E; ++i) g[i] *= inv;
             }
           }
-          if (EDGE_GRAD) {
-            float dot = 0.f;
-            if (on) {
-              float xv[E];
-              VT::to_float(xv, VT::load(x + nid * a.width + col));
+        }
+        const int64_t nid = __shfl_sync(gmask, my_nid, j, G);
+        float val = 1.f;
+        if (VALMODE == 1) val = __shfl_sync(gmask, my_val, j, G);
+        if (VALMODE == 2 && on) val = __ldg(a.edge_val + ej * a.heads + head);
+        if (nid < 0) continue;
+        if (a.dx != nullptr && on) {
+          float *dst = a.dx + nid * a.width + col;
+          if (E % 4 == 0) {
 #pragma unroll
-              for (int i = 0; i < E; ++i) dot = fmaf(g[i], xv[i], dot);
-            }
-            // Tree over the lanes of one head (xor butterflies stay inside the
-            // aligned block of lanes_per_head lanes).
-            for (int o = lanes_per_head >> 1; o > 0; o >>= 1)
-              dot += __shfl_xor_sync(gmask, dot, o, G);
-            if (on && (lg % lanes_per_head) == 0) {
-              float *dv = a.dval + (e0 + j) * a.heads + head;
-              *dv = dot;  // a head never straddles two column passes
-            }
+            for (int i = 0; i < E; i += 4)
+              red_add_v4(dst + i, g[i] * val, g[(i + 1) % E] * val, g[(i + 2) % E] * val, g[(i + 3) % E] * val);
+          } else {
+#pragma unroll
+            for (int i = 0; i < E; ++i) atomicAdd(dst + i, g[i] * val);
           }
+        }
+        if (EDGE_GRAD) {
+          float dot = 0.f;
+          if (on) {
+            float xv[E];
+            VT::to_float(xv, VT::load(x + nid * a.width + col));
+#pragma unroll
+            for (int i = 0; i < E; ++i) dot = fmaf(g[i], xv[i], dot);
+          }
+          // tree over the lanes of one head (xor butterflies stay inside the aligned block of
+          // lanes_per_head lanes)
+          for (int o = lanes_per_head >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o, G);
+          if (on && (lg % lanes_per_head) == 0) a.dval[ej * a.heads + head] = dot;  // a head never straddles two passes
         }
       }
     }
@@ -142,7 +163,7 @@ __global__ void __launch_bounds__(kThreads) spmm_bwd_rows(BwdArgs a) {
 
 template <typename VT, typename T, typename IdxT, int G>
 void launch_bwd2(const BwdArgs &a, int valmode, bool edge_grad, dim3 grid, cudaStream_t st) {
-#define CXG_BWD(VM, EG) spmm_bwd_rows<VT, T, IdxT, G, VM, EG><<<grid, kThreads, 0, st>>>(a)
+#define CXG_BWD(VM, EG) spmm_bwd_tiles<VT, T, IdxT, G, VM, EG><<<grid, kThreads, 0, st>>>(a)
   if (!edge_grad) {
     if (valmode == 0)
       CXG_BWD(0, false);
@@ -186,13 +207,10 @@ int launch_bwd(const BwdArgs &a, int valmode, bool edge_grad, int64_t nnz, cudaS
     else if (nvec <= 16)
       G = 16;
   }
-  int64_t groups_per_block = kThreads / G;
-  int64_t row_blocks = (a.n_dst + groups_per_block - 1) / groups_per_block;
-  // Enough y-slices that the longest rows are shared by many groups, bounded so
-  // that short rows do not pay for idle groups.
-  int64_t avg = a.n_dst > 0 ? nnz / a.n_dst : 0;
-  int slices = avg > 4 * kSegment ? 64 : 16;
-  dim3 grid(static_cast<unsigned>(row_blocks), slices);
+  // one group per tile of kSegment edges; nnz bounds the edge count (tiles past ptr[n_dst] return)
+  const int64_t groups_per_block = kThreads / G;
+  const int64_t tiles = (nnz + kSegment - 1) / kSegment;
+  dim3 grid(static_cast<unsigned>((tiles + groups_per_block - 1) / groups_per_block));
   if (!vector_ok)
     launch_bwd2<Scalar<T>, T, IdxT, 32>(a, valmode, edge_grad, grid, st);
   else if (G == 8)

@@ -9,6 +9,12 @@ own rows. The feature shards are exchanged with ONE NCCL all-gather into a local
 column ids of the local CSR are renumbered once into that layout, so the exchange needs no repacking and
 one aggregation over the local rows follows it. Remote features are in local HBM before any kernel reads
 them: no peer-memory loads.
+
+`NeededRowsExchange` is the volume-reducing alternative (the reference's "densify" step,
+test/1-kernels/test_mgpu_model.py:227-331,447-454): every rank asks each owner only for the feature rows its
+own edges name. Requests are exchanged once per graph; every step the owners pack the requested rows and one
+variable-size all-to-all delivers them into a compact local buffer, into whose numbering the column ids were
+renumbered. It moves (rows needed from other ranks) x F instead of (world - 1) / world x N x F per rank.
 """
 import torch
 import torch.distributed as dist
@@ -67,3 +73,71 @@ def dist_aggregate(x_gather, lptr, lidx, part, rank, aggregate, out=None, group=
     exchange_features(x_gather, part, rank, group)
     r0, r1 = part.rows(rank)
     return aggregate(x_gather, lptr, lidx, r1 - r0, out)
+
+
+class NeededRowsExchange:
+    """Per-graph state of the needed-rows exchange for one rank.
+
+    The local feature buffer is [own shard | remote rows this rank's edges name, ordered by global id]; the
+    rank's own rows are used in place (no copy), only remote rows travel.
+
+    remote        sorted global ids of the remote feature rows this rank's edges read
+    recv_counts   how many of them each owner holds (0 for this rank itself)
+    send_rows     local row numbers (inside this rank's shard) that the other ranks asked for, grouped by asker
+    send_counts   rows per asker
+    lidx          the local column ids renumbered into rows of the local feature buffer
+    """
+
+    def __init__(self, part, lptr, lidx_global, rank, num_nodes, group=None):
+        self.part, self.rank, self.group = part, rank, group
+        world = part.world
+        dev = lidx_global.device
+        nnz = int(lptr[-1])
+        r0, r1 = part.rows(rank)
+        self.n_own = r1 - r0
+        cols = lidx_global[:nnz].long()
+        used = torch.zeros(num_nodes, dtype=torch.bool, device=dev)
+        used[cols] = True
+        used[r0:r1] = False  # own rows are addressed in place
+        self.remote = torch.nonzero(used).squeeze(1)  # ascending, hence grouped by owner
+        pos = torch.cumsum(used, 0, dtype=torch.int64) - 1 + self.n_own
+        pos[r0:r1] = torch.arange(self.n_own, device=dev)
+        self.lidx = pos[cols].to(lidx_global.dtype)
+        del pos, used, cols
+        bounds = torch.tensor(part.bounds, dtype=torch.int64, device=dev)
+        cut = torch.searchsorted(self.remote, bounds)
+        self.recv_counts = (cut[1:] - cut[:-1]).tolist()
+        # tell every owner which of its rows (shard-local numbers) this rank needs
+        owner = torch.repeat_interleave(torch.arange(world, device=dev), cut[1:] - cut[:-1])
+        want_local = self.remote - bounds[owner]
+        counts_out = torch.tensor(self.recv_counts, dtype=torch.int64, device=dev)
+        counts_in = torch.empty_like(counts_out)
+        dist.all_to_all_single(counts_in, counts_out, group=group)
+        self.send_counts = counts_in.tolist()
+        self.send_rows = torch.empty(sum(self.send_counts), dtype=torch.int64, device=dev)
+        dist.all_to_all_single(self.send_rows, want_local, self.send_counts, self.recv_counts, group=group)
+
+    def buffer_rows(self):
+        """Rows of the local feature buffer: own shard + remote rows."""
+        return self.n_own + self.remote.shape[0]
+
+    def remote_rows(self):
+        """Rows that cross the interconnect into this rank per step."""
+        return self.remote.shape[0]
+
+    def own(self, x_buf):
+        """View of this rank's own rows at the head of the buffer."""
+        return x_buf[:self.n_own]
+
+    def exchange(self, x_buf, send_buf=None, pack=None):
+        """x_buf [buffer_rows, F] with this rank's shard already in x_buf[:n_own]; fills the remote part.
+        `pack(x_own, rows, out)` gathers the rows the peers asked for (default: the CUDA row-gather kernel)."""
+        x_own = x_buf[:self.n_own]
+        if send_buf is None:
+            send_buf = torch.empty((self.send_rows.shape[0], x_buf.shape[1]), dtype=x_buf.dtype, device=x_buf.device)
+        if pack is None:
+            import cxgnncomp_backend
+            pack = cxgnncomp_backend.gather_rows
+        pack(x_own, self.send_rows, send_buf)
+        dist.all_to_all_single(x_buf[self.n_own:], send_buf, self.recv_counts, self.send_counts, group=self.group)
+        return x_buf

@@ -244,15 +244,23 @@ def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG
     if x_shape is None:
         x_shape = x.shape
     dx_t = None
-    if (need_dx and BACKWARD_MODE != "scatter" and grad_x is None and edge_mask is None and edge_rel is None
-            and targets is None and n > 0):
+    # with edge-value gradients asked for, the scatter kernel yields dx and dval in one pass over the edges:
+    # "auto" keeps it; the transposed graph is used for the plain dx = A^T dy
+    if (need_dx and BACKWARD_MODE != "scatter" and not (need_dval and BACKWARD_MODE == "auto") and grad_x is None
+            and edge_mask is None and edge_rel is None and targets is None and n > 0):
         tg = _transposed_graph(ptr, idx, n, x_shape[0])
         if tg is not None:
             t_ptr, t_idx, t_eid, inv_deg = tg
             dy = grad_out
             if reduce == CXG_MEAN:
                 dy = (grad_out.float() * inv_deg.view(-1, *([1] * (grad_out.dim() - 1)))).to(grad_out.dtype)
-            t_val = None if edge_val is None else edge_val[t_eid].contiguous()
+            t_val = None
+            if edge_val is not None:  # the edge values in transposed order
+                ev = edge_val.contiguous()
+                t_val = torch.empty_like(ev)
+                with torch.cuda.device(ev.device):
+                    _check(_gather(_p(ev), _p(t_eid), t_eid.element_size(), _p(t_val), t_eid.shape[0],
+                                   ev.shape[1] if ev.dim() == 2 else 1, 1, _stream()), "cxg_gather_edges")
             dx_t = _spmm_forward(dy, t_ptr, t_idx, x_shape[0], edge_val=t_val)
             need_dx = False
             if not need_dval:
@@ -369,6 +377,26 @@ class SPMM_MULTIHEAD_SCHEDULE(enum.IntEnum):
 Naive = SPMM_MULTIHEAD_SCHEDULE.Naive
 PreReduce = SPMM_MULTIHEAD_SCHEDULE.PreReduce
 Optimal = SPMM_MULTIHEAD_SCHEDULE.Optimal
+
+
+_gather_rows = _sig("cxg_gather_rows", [_vp, _vp, _vp, _i64, _i64, _vp])
+
+
+def gather_rows(x, rows, out=None):
+    """out[i] = x[rows[i]] for a contiguous 2-D x and int64 rows (any element type of even size)."""
+    _cuda(x, "x")
+    _cuda(rows, "rows", (torch.int64,))
+    if x.dim() != 2:
+        raise RuntimeError("x must be 2-D")
+    if out is None:
+        out = torch.empty((rows.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    _cuda(out, "out", (x.dtype,))
+    if out.shape[0] < rows.shape[0] or out.shape[1] != x.shape[1]:
+        raise RuntimeError("out must be [len(rows), x.shape[1]]")
+    with torch.cuda.device(x.device):
+        _check(_gather_rows(_p(x), _p(rows), _p(out), rows.shape[0], x.shape[1] * x.element_size(), _stream()),
+               "cxg_gather_rows")
+    return out
 
 
 _sample = _sig("cxg_sample_neighbors", [_vp, _vp, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.c_int, _vp, _vp,

@@ -147,7 +147,7 @@ int cxg_spmm_csr_backward(const cxg_spmm_desc *desc, const void *dy, float *dx,
  * att_dst [n_dst, heads], att_src [n_src, heads], out [nnz, heads] float32, mask
  * [nnz, heads] bytes. Replaces edge_attention / EdgeSoftMaxFunction::forward and
  * edge_softmax_fwd (src/cpp/src/edge_softmax.cu:3-42,97-132). Same summation order per
- * row as the reference for rows of up to 4096 edges; exp is the accurate expf where the
+ * row as the reference for rows of up to 1024 edges; exp is the accurate expf where the
  * reference uses the fast __expf. Workspace: cxg_edge_softmax_workspace_size bytes.
  */
 int cxg_edge_softmax_workspace_size(int64_t n_dst, int64_t nnz, size_t *bytes);
@@ -254,6 +254,14 @@ int cxg_typed_linear(const float *x, const float *w, float *out, const int32_t *
 int cxg_rgcn_direct(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
                     const int32_t *rel, const float *x, const float *w, float *y,
                     int64_t n_dst, int k, int n, void *stream);
+
+/*
+ * out[i, :] = in[rows[i], :] for rows of row_bytes bytes (even; 16-byte accesses when pointers and
+ * row size allow): the pack step of the needed-rows feature exchange between GPUs, the reference's
+ * "densify" (test/1-kernels/test_mgpu_model.py:227-331). rows int64 [n_rows].
+ */
+int cxg_gather_rows(const void *in, const int64_t *rows, void *out, int64_t n_rows,
+                    int64_t row_bytes, void *stream);
 
 /*
  * Neighbour sampling for mini-batches in the CSR_Layer format (the step the reference takes from its

@@ -38,6 +38,19 @@ def _worker(rank, world, port, out_dir):
     # column ids were renumbered into the gather layout: they address the same feature rows
     _, gidx = part.local_graph(ptr, idx, rank, gather_ids=False)
     assert torch.equal(x_gather[lidx], x[gidx])
+    # needed-rows exchange: only the rows this rank's edges name arrive, in the renumbered order
+    from cxgnncomp.distributed import NeededRowsExchange
+    ex = NeededRowsExchange(part, lptr, gidx, rank, 3000)
+    x_buf = torch.zeros(ex.buffer_rows(), x.shape[1])
+    ex.own(x_buf).copy_(x[r0:r1])
+    ex.exchange(x_buf, pack=lambda src, rows, out: torch.index_select(src, 0, rows, out=out))
+    remote_ids = torch.unique(gidx[(gidx < r0) | (gidx >= r1)])
+    assert torch.equal(ex.remote, remote_ids) and ex.recv_counts[rank] == 0 and ex.send_counts[rank] == 0
+    assert torch.equal(x_buf[ex.n_own:], x[remote_ids])
+    assert torch.equal(x_buf[ex.lidx.long()], x[gidx])
+    assert 0 < ex.remote_rows() <= 3000 - (r1 - r0)
+    y_need = oracle.spmm(lptr, ex.lidx, x_buf)
+    assert torch.equal(y_need, y_local)
     torch.save({"bounds": part.bounds, "y": y_local, "nnz": int(lptr[-1])}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()

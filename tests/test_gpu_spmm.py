@@ -357,3 +357,16 @@ def test_backward_over_transposed_graph(cuda, mean, with_val, monkeypatch):
         xg = x.cuda().requires_grad_(True)
         be.sage_sum_forward(xg, p, i, 500).backward(dy.cuda())
         assert len(be._TRANSPOSE_CACHE) == (0 if k == 0 else 1)
+
+
+@pytest.mark.parametrize("dtype,width", [(torch.bfloat16, 128), (torch.float32, 128), (torch.float32, 5),
+                                         (torch.bfloat16, 7), (torch.int64, 3)])
+def test_gather_rows(cuda, dtype, width):
+    """The pack kernel of the needed-rows exchange: out[i] = x[rows[i]], any even row size."""
+    import cxgnncomp_backend as be
+    g = torch.Generator().manual_seed(width)
+    x = (torch.randn(1000, width, generator=g) * 100).to(dtype)
+    rows = torch.randint(0, 1000, (2500,), generator=g)
+    got = be.gather_rows(x.cuda(), rows.cuda())
+    assert torch.equal(got.cpu(), x[rows])
+    assert be.gather_rows(x.cuda(), rows[:0].cuda()).shape == (0, width)
