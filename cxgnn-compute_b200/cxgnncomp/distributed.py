@@ -129,9 +129,22 @@ class NeededRowsExchange:
         """View of this rank's own rows at the head of the buffer."""
         return x_buf[:self.n_own]
 
-    def exchange(self, x_buf, send_buf=None, pack=None):
+    def split_graph(self, lptr):
+        """The local CSR cut by where the source lives: ((ptr, idx) of the edges whose source is one of this rank's
+        own rows, (ptr, idx) of the edges that read remote rows). Both keep every local row, so the second can be
+        accumulated onto the result of the first while nothing else changes; the first needs no exchange."""
+        nnz = int(lptr[-1])
+        own = self.lidx[:nnz] < self.n_own
+        run = torch.zeros(nnz + 1, dtype=torch.int64, device=lptr.device)
+        torch.cumsum(own, 0, out=run[1:])
+        ptr_own = run[lptr.long()]
+        ptr_rem = lptr.long() - ptr_own
+        return (ptr_own, self.lidx[:nnz][own].contiguous()), (ptr_rem, self.lidx[:nnz][~own].contiguous())
+
+    def exchange(self, x_buf, send_buf=None, pack=None, async_op=False):
         """x_buf [buffer_rows, F] with this rank's shard already in x_buf[:n_own]; fills the remote part.
-        `pack(x_own, rows, out)` gathers the rows the peers asked for (default: the CUDA row-gather kernel)."""
+        `pack(x_own, rows, out)` gathers the rows the peers asked for (default: the CUDA row-gather kernel).
+        async_op=True returns the collective's work handle instead of waiting for it on the current stream."""
         x_own = x_buf[:self.n_own]
         if send_buf is None:
             send_buf = torch.empty((self.send_rows.shape[0], x_buf.shape[1]), dtype=x_buf.dtype, device=x_buf.device)
@@ -139,5 +152,6 @@ class NeededRowsExchange:
             import cxgnncomp_backend
             pack = cxgnncomp_backend.gather_rows
         pack(x_own, self.send_rows, send_buf)
-        dist.all_to_all_single(x_buf[self.n_own:], send_buf, self.recv_counts, self.send_counts, group=self.group)
-        return x_buf
+        work = dist.all_to_all_single(x_buf[self.n_own:], send_buf, self.recv_counts, self.send_counts,
+                                      group=self.group, async_op=async_op)
+        return work if async_op else x_buf

@@ -51,6 +51,12 @@ def _worker(rank, world, port, out_dir):
     assert 0 < ex.remote_rows() <= 3000 - (r1 - r0)
     y_need = oracle.spmm(lptr, ex.lidx, x_buf)
     assert torch.equal(y_need, y_local)
+    # the two-phase form: own-source edges (no exchange needed) + remote-source edges
+    (p_own, i_own), (p_rem, i_rem) = ex.split_graph(lptr)
+    assert int(p_own[-1]) + int(p_rem[-1]) == int(lptr[-1]) and torch.equal(p_own + p_rem, lptr)
+    assert bool((i_own < ex.n_own).all()) and bool((i_rem >= ex.n_own).all())
+    y_two = oracle.spmm_f64(p_own, i_own, x_buf) + oracle.spmm_f64(p_rem, i_rem, x_buf)
+    assert float((y_two - oracle.spmm_f64(lptr, ex.lidx, x_buf)).abs().max()) < 1e-12
     torch.save({"bounds": part.bounds, "y": y_local, "nnz": int(lptr[-1])}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
