@@ -138,10 +138,19 @@ def cpu_baseline_sample(ptr, idx, feat, dtype, budget_s=20.0):
         if ts:
             best[name] = sorted(ts)[len(ts) // 2]
     form = min(best, key=best.get)
-    return {"value": b_alg / best[form] / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+    # The metric is the algorithmic bytes of the WHOLE workload over the time of one pass. The CPU pass is
+    # extrapolated from the sample by edge count (its time is per-edge gather work); the sample's own
+    # algorithmic bytes per edge are several times the full graph's (few edges per distinct source), so its
+    # own GB/s is reported separately and is not comparable with the GPU figure.
+    elem = 2 if dtype == torch.bfloat16 else 4
+    b_alg_full = algorithmic_bytes(n, n, nnz, feat, elem, idx.element_size())
+    full_s = best[form] * (nnz / max(1, e1 - e0))
+    return {"value": b_alg_full / full_s / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"rows [{r0},{r1}) of the workload = {rows} rows / {e1 - e0} edges / {n_src} distinct sources, "
-                      f"fp32 int64, torch {form} (median of {len(ts)}), {best[form] * 1e3:.1f} ms",
-            "formulation": form, "ms": best[form] * 1e3}
+                      f"fp32 int64, torch {form} (median of {len(ts)}), {best[form] * 1e3:.1f} ms; whole pass "
+                      f"extrapolated by edge count ({nnz} edges): {full_s:.2f} s",
+            "formulation": form, "ms": best[form] * 1e3, "extrapolated_pass_s": full_s,
+            "sample_own_GBps": b_alg / best[form] / 1e9}
 
 
 def build_workload(name, device, seed=0):
@@ -166,6 +175,7 @@ def run_reference(args, rank):
         base = cpu_baseline_sample(ptr, idx, feat, dtype, budget_s=max(5.0, 60.0 / (args.warmup + args.steps)))
         ts.append(base["ms"])
     ms = sum(ts[args.warmup:]) / max(1, args.steps)
+    base["value"] = base["value"] * base["ms"] / ms  # mean over the timed steps instead of the last one
     line = {"impl": "reference", "metric": "spmm_algorithmic_hbm_throughput", "value": base["value"], "unit": "GB/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
