@@ -154,8 +154,28 @@ def config2(steps, flush):
     err_g = rel(xg.grad.cpu(), xr.grad)
     # fused aggregate bytes: x_src rows + scores in, out rows + values out, idx, ptr
     b_alg = 2 * n * 4 * (32 * 4 + 4) + nnz * (8 + 4 * 4) + (n + 1) * 8
+    # the library's kernels of the layer, each against the HBM roofline with its own algorithmic bytes
+    import cxgnncomp_backend as be
+    hbm = peaks()[0]
+    H = 4
+    with torch.no_grad():
+        h3 = F.linear(xg, conv.lin_src).view(-1, H, 32).contiguous()
+        sc_s, sc_d = (h3 * conv.att_src).sum(-1).contiguous(), (h3 * conv.att_dst).sum(-1).contiguous()
+        val = be.edge_attention(p, i, sc_d, sc_s, nnz, 0.2)
+        dyh = go.view(-1, H, 32).contiguous()
+        kern = {
+            "edge_softmax_fwd": (gpu_ms(lambda: be.edge_attention(p, i, sc_d, sc_s, nnz, 0.2), steps, flush),
+                                 2 * n * H * 4 + nnz * (8 + 5 * H) + (n + 1) * 8),
+            "spmm_multihead_fwd": (gpu_ms(lambda: be.spmm_multihead(p, i, val, h3, n, be.Naive), steps, flush),
+                                   2 * n * 128 * 4 + nnz * (8 + 4 * H) + (n + 1) * 8),
+            "spmm_multihead_bwd_dx_dval": (gpu_ms(lambda: be._spmm_backward(dyh, h3, p, i, n, edge_val=val, need_dx=True,
+                                                                           need_dval=True), steps, flush),
+                                           3 * n * 128 * 4 + nnz * (8 + 8 * H) + (n + 1) * 8),
+        }
+    kernels = {k: {"ms": t, "b_alg_bytes": b, "GBps": b / t / 1e6, "frac_hbm_peak": b / t / 1e6 / hbm}
+               for k, (t, b) in kern.items()}
     return {"config": "c2 GAT layer fwd+bwd (4 heads x 32)", "nodes": n, "nnz": nnz, "gpu_fwd_ms": t_f,
-            "gpu_fwd_bwd_ms": t_fb, "aggregate_b_alg_bytes": b_alg, "cpu_fwd_bwd_ms": c_fb,
+            "gpu_fwd_bwd_ms": t_fb, "aggregate_b_alg_bytes": b_alg, "kernels": kernels, "cpu_fwd_bwd_ms": c_fb,
             "cpu_cores": torch.get_num_threads(), "max_rel_err_fwd": err, "max_rel_err_grad_x": err_g}
 
 

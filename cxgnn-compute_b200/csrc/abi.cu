@@ -35,3 +35,25 @@ extern "C" int cxg_abi_version(void) { return 1; }
 extern "C" long long cxg_kernel_launch_count(void) {
   return __atomic_load_n(&cxg::g_launches, __ATOMIC_RELAXED);
 }
+
+namespace {
+// Reads one 32-bit word of a device workspace after everything queued on `stream` has run.
+int read_status_word(const void *workspace, size_t word, void *stream, const char *who) {
+  if (workspace == nullptr) return cxg::set_error(CXG_ENULL, "%s: workspace is NULL", who);
+  int32_t v = 0;
+  cudaStream_t st = cxg::as_stream(stream);
+  cudaError_t e = cudaMemcpyAsync(&v, static_cast<const int32_t *>(workspace) + word, sizeof(v), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cxg::set_error(CXG_ECUDA, "%s: %s", who, cudaGetErrorString(e));
+  if (v != 0) return cxg::set_error(CXG_ETIMEOUT, "%s: a bounded device-side wait ran out; the result is incomplete", who);
+  return CXG_OK;
+}
+}  // namespace
+
+extern "C" int cxg_spmm_csr_status(const void *workspace, void *stream) {
+  return read_status_word(workspace, 63, stream, "cxg_spmm_csr_status");
+}
+
+extern "C" int cxg_typed_matmul_status(const void *workspace, void *stream) {
+  return read_status_word(workspace, 0, stream, "cxg_typed_matmul_status");
+}

@@ -5,7 +5,7 @@
 namespace cxg {
 
 // Header words of the streaming workspace.
-enum { kSHdrNumLong = 0, kSHdrError = 1 };
+enum { kSHdrNumLong = 0, kSHdrError = 63 };  // word 63 is the error word of every SpMM workspace header
 // Row fetch variants: 16-byte async copies into shared memory (default), one bulk
 // async copy per row into shared memory.
 enum { kModeCpAsync = 0, kModeBulk = 1 };

@@ -68,6 +68,18 @@ def exchange_features(x_gather, part, rank, group=None):
     return x_gather
 
 
+def reduce_gradients(dx_gather, part, rank, group=None):
+    """Backward of `exchange_features` (DistAggrOP.backward, test_mgpu_model.py:185-224): every rank holds partial
+    gradients for ALL feature rows in the gather layout; the shards are summed across ranks and each rank
+    receives its own (one reduce-scatter). Returns the [rows of this rank, F] gradient."""
+    r0, r1 = part.rows(rank)
+    if part.world == 1:
+        return dx_gather[:r1 - r0]
+    out = torch.empty((part.shard_rows, dx_gather.shape[1]), dtype=dx_gather.dtype, device=dx_gather.device)
+    dist.reduce_scatter_tensor(out, dx_gather, group=group)
+    return out[:r1 - r0]
+
+
 def dist_aggregate(x_gather, lptr, lidx, part, rank, aggregate, out=None, group=None):
     """One full-graph aggregation step for this rank: exchange, then aggregate(x_gather, lptr, lidx, n_local, out)."""
     exchange_features(x_gather, part, rank, group)
@@ -140,6 +152,23 @@ class NeededRowsExchange:
         ptr_own = run[lptr.long()]
         ptr_rem = lptr.long() - ptr_own
         return (ptr_own, self.lidx[:nnz][own].contiguous()), (ptr_rem, self.lidx[:nnz][~own].contiguous())
+
+    def exchange_backward(self, dx_buf, recv_buf=None, unpack=None):
+        """Backward of `exchange`: dx_buf [buffer_rows, F] holds this rank's partial gradients for its own rows and
+        for the remote rows it read. The remote part travels back to the owners (the forward all-to-all with the
+        counts swapped) and every owner adds what it receives into its own rows. Returns the gradient of this
+        rank's shard (a view of dx_buf[:n_own], updated in place).
+        `unpack(dx_own, rows, recv)` adds recv[i] into dx_own[rows[i]] (default: index_add_)."""
+        dx_own = dx_buf[:self.n_own]
+        if recv_buf is None:
+            recv_buf = torch.empty((self.send_rows.shape[0], dx_buf.shape[1]), dtype=dx_buf.dtype, device=dx_buf.device)
+        dist.all_to_all_single(recv_buf, dx_buf[self.n_own:].contiguous(), self.send_counts, self.recv_counts,
+                               group=self.group)
+        if unpack is None:
+            dx_own.index_add_(0, self.send_rows, recv_buf)
+        else:
+            unpack(dx_own, self.send_rows, recv_buf)
+        return dx_own
 
     def exchange(self, x_buf, send_buf=None, pack=None, async_op=False):
         """x_buf [buffer_rows, F] with this rank's shard already in x_buf[:n_own]; fills the remote part.

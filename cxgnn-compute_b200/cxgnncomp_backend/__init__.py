@@ -158,6 +158,23 @@ def _num_rows(ptr, num_node):
     return n
 
 
+_spmm_status = _sig("cxg_spmm_csr_status", [_vp, _vp])
+_tmm_status = _sig("cxg_typed_matmul_status", [_vp, _vp])
+
+
+def check_device_status(kind="spmm", device=None):
+    """Synchronises the current stream and raises if a bounded device-side wait of the LAST call of that kind
+    ("spmm" or "typed_matmul") on this stream ran out (the kernels give up after about a second instead of
+    spinning forever). The calls of one stream share a scratch buffer, so ask right after the call in question."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspaces.get((device.index, torch.cuda.current_stream(device).cuda_stream))
+    if ws is None:
+        return
+    fn, name = (_spmm_status, "cxg_spmm_csr_status") if kind == "spmm" else (_tmm_status, "cxg_typed_matmul_status")
+    with torch.cuda.device(device):
+        _check(fn(_p(ws), _stream()), name)
+
+
 def _run_spmm(desc, device):
     need = _sz(0)
     _check(_spmm_ws(desc.n_dst, desc.nnz, desc.feat, desc.heads, desc.split_edges, ctypes.byref(need)),

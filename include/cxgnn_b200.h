@@ -100,6 +100,16 @@ typedef struct cxg_spmm_desc {
 } cxg_spmm_desc;
 
 /*
+ * The kernels never spin without a limit: a wait on an mbarrier (the bulk-copy variant of cxg_spmm_csr,
+ * the pipeline of cxg_typed_matmul) gives up after about a second, records that in the call's workspace
+ * and returns. These two read the record: they WAIT for everything queued on `stream`, then return CXG_OK
+ * or CXG_ETIMEOUT (the result of the call that used `workspace` last is then incomplete). Optional: nothing
+ * else in the library synchronises.
+ */
+int cxg_spmm_csr_status(const void *workspace, void *stream);
+int cxg_typed_matmul_status(const void *workspace, void *stream);
+
+/*
  * Scratch bytes needed by cxg_spmm_csr for a graph with n_dst rows and nnz
  * edges at row width heads*feat (split_edges as in the descriptor). Upper bound;
  * depends on sizes only.

@@ -57,7 +57,16 @@ def _worker(rank, world, port, out_dir):
     assert bool((i_own < ex.n_own).all()) and bool((i_rem >= ex.n_own).all())
     y_two = oracle.spmm_f64(p_own, i_own, x_buf) + oracle.spmm_f64(p_rem, i_rem, x_buf)
     assert float((y_two - oracle.spmm_f64(lptr, ex.lidx, x_buf)).abs().max()) < 1e-12
-    torch.save({"bounds": part.bounds, "y": y_local, "nnz": int(lptr[-1])}, os.path.join(out_dir, f"r{rank}.pt"))
+    # backward: partial gradients for every row this rank read go back to their owners and are summed there
+    dy = synthetic.node_features(3000, 16, seed=2)[r0:r1]
+    dx_buf = oracle.spmm_bwd_f64(lptr, ex.lidx, dy, (ex.buffer_rows(), 16))[0]
+    dx_needed = ex.exchange_backward(dx_buf).clone()
+    from cxgnncomp.distributed import reduce_gradients
+    dx_gather = oracle.spmm_bwd_f64(lptr, lidx, dy, (part.gather_rows(), 16))[0]
+    dx_all = reduce_gradients(dx_gather, part, rank)
+    assert float((dx_needed - dx_all).abs().max()) < 1e-12
+    torch.save({"bounds": part.bounds, "y": y_local, "nnz": int(lptr[-1]), "dx": dx_needed},
+               os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -75,6 +84,10 @@ def test_two_rank_partition_exchange_aggregate(tmp_path):
     parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
     assert parts[0]["bounds"] == parts[1]["bounds"]
     assert torch.equal(torch.cat([p["y"] for p in parts]), full)
+    # the distributed backward assembles to the single-process transpose product
+    dy = synthetic.node_features(3000, 16, seed=2)
+    dx_full = oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0]
+    assert float((torch.cat([p["dx"] for p in parts]) - dx_full).abs().max()) < 1e-12
     nnz = [p["nnz"] for p in parts]
     assert sum(nnz) == idx.shape[0]
     max_deg = int((ptr[1:] - ptr[:-1]).max())

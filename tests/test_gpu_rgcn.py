@@ -185,3 +185,24 @@ def test_aggr_rel_direct_autograd(cuda):
     ref.backward(go)
     assert rel_err(xg.grad.cpu(), xr.grad) < 1e-5
     assert rel_err(wg.grad.cpu(), wr.grad) < 1e-5
+
+
+def test_status_words_clear_after_normal_calls(cuda):
+    """The bounded waits of the typed matmul pipeline and of the bulk-copy SpMM leave their status words at zero
+    when nothing timed out; the read-back entry points return CXG_OK (they synchronise the stream)."""
+    import cxgnncomp_backend as be
+    R, E = 3, 2000
+    g = torch.Generator().manual_seed(90)
+    types = torch.randint(0, R, (E,), generator=g)
+    a, w = randn((E, 64), 91).bfloat16(), (randn((R, 64, 32), 92) * 0.2).bfloat16()
+    _, sorted_types, indices, _ = _preprocess(types.cuda(), R, 128)
+    be.typed_matmul_raw(a.cuda(), w.cuda(), sorted_types, sorted_types.shape[0], E, src_idx=indices)
+    be.check_device_status("typed_matmul")
+    ptr, idx = random_csr(300, 300, 8, seed=93)
+    old = be.EXTRA_SPMM_FLAGS
+    be.EXTRA_SPMM_FLAGS = be.CXG_SPMM_BULK_ROWS
+    try:
+        be.sage_sum_forward(randn((300, 64), 94).cuda(), ptr.cuda(), idx.cuda(), 300)
+        be.check_device_status("spmm")
+    finally:
+        be.EXTRA_SPMM_FLAGS = old
