@@ -439,6 +439,10 @@ def main():
                 "traffic": NCU_DRAM_BYTES.get(args.workload) if world == 1 else None, "peak_source": peak_src,
                 "kernel": "cxg_spmm_csr (plan + spmm_stream + fix kernels)",
                 "ms": spmm_ms, "algorithmic_bytes": b_alg_local}
+    if roofline["traffic"]:
+        # DRAM bytes actually moved (ncu, one launch) over the event-timed duration: how busy HBM is
+        roofline["hbm_util"] = roofline["traffic"] / (spmm_ms * 1e-3) / 1e9 / peak
+        roofline["traffic_over_algorithmic"] = roofline["traffic"] / b_alg_local
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline_sample(full_ptr, lidx, feat, dtype)
