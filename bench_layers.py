@@ -198,7 +198,7 @@ def config3(steps, flush, scale=1.0):
     fanouts, bs = [15, 10, 5], 1024
     torch.manual_seed(0)
     model = cxgnncomp.SAGE(100, 256, 47, 3).cuda()
-    opt = torch.optim.Adam(model.parameters(), lr=0.003)
+    opt = torch.optim.Adam(model.parameters(), lr=0.003, fused=True)
     sampler = cxgnncomp.NeighborSampler(ptr, idx, fanouts)
     nb = cxgnncomp.num_batches(train.shape[0], bs)
     cxgnncomp.train_epoch(model, opt, sampler, x, y, train, bs, epoch=0, max_batches=10)  # warm-up

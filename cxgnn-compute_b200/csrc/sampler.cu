@@ -84,3 +84,98 @@ extern "C" int cxg_sample_neighbors(const void *graph_ptr, const void *graph_idx
   count_launches(1);
   return check_launch("cxg_sample_neighbors");
 }
+
+namespace cxg {
+namespace {
+
+// Renumbering of sampled neighbours into batch-local ids, step 1: every sampled global id that has no local
+// id yet (local_of < 0) is claimed once (atomicCAS on its table entry, -1 -> -2) and appended to `fresh`
+// (order of arrival; the caller sorts the list, so the batch does not depend on that order).
+__global__ void __launch_bounds__(256) claim_fresh_kernel(const int64_t *picked, int64_t n, int64_t *local_of,
+                                                          int64_t *fresh, unsigned long long *n_fresh) {
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t v = picked[i];
+    if (local_of[v] == -1) {
+      const unsigned long long old = atomicCAS(reinterpret_cast<unsigned long long *>(local_of + v),
+                                               static_cast<unsigned long long>(-1ll), static_cast<unsigned long long>(-2ll));
+      if (old == static_cast<unsigned long long>(-1ll)) fresh[atomicAdd(n_fresh, 1ull)] = v;
+    }
+  }
+}
+
+// step 2 (after the caller has sorted fresh[0 .. n_fresh)): local_of[fresh[i]] = base + i
+__global__ void __launch_bounds__(256) number_fresh_kernel(const int64_t *fresh, int64_t n_fresh, int64_t base,
+                                                           int64_t *local_of) {
+  const int64_t i = blockIdx.x * 256ll + threadIdx.x;
+  if (i < n_fresh) local_of[fresh[i]] = base + i;
+}
+
+// step 3: out[i] = local_of[picked[i]]
+__global__ void __launch_bounds__(256) translate_kernel(const int64_t *picked, int64_t n, const int64_t *local_of,
+                                                        int64_t *out) {
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256)
+    out[i] = local_of[picked[i]];
+}
+
+unsigned grid_for(int64_t n) {
+  const int64_t want = (n + 255) / 256;
+  return static_cast<unsigned>(want < kNumSM * 16 ? (want > 0 ? want : 1) : kNumSM * 16);
+}
+
+}  // namespace
+}  // namespace cxg
+
+namespace cxg {
+namespace {
+__global__ void __launch_bounds__(256) sample_counts_kernel(const void *gptr, int ptr_bytes, const int64_t *frontier,
+                                                            int64_t n_front, int fanout, int64_t *counts) {
+  const int64_t i = blockIdx.x * 256ll + threadIdx.x;
+  if (i >= n_front) return;
+  const int64_t v = frontier[i];
+  const int64_t deg = load_ptr(gptr, v + 1, ptr_bytes) - load_ptr(gptr, v, ptr_bytes);
+  counts[i] = deg < fanout ? deg : fanout;
+}
+}  // namespace
+}  // namespace cxg
+
+extern "C" int cxg_sample_counts(const void *graph_ptr, int ptr_bytes, const int64_t *frontier, int64_t n_front,
+                                 int fanout, int64_t *counts, void *stream) {
+  CXG_REQUIRE(n_front >= 0 && fanout >= 1 && (ptr_bytes == 4 || ptr_bytes == 8), CXG_EINVAL,
+              "cxg_sample_counts: bad arguments");
+  if (n_front == 0) return CXG_OK;
+  CXG_REQUIRE(graph_ptr && frontier && counts, CXG_ENULL, "cxg_sample_counts: NULL argument");
+  sample_counts_kernel<<<static_cast<unsigned>((n_front + 255) / 256), 256, 0, as_stream(stream)>>>(
+      graph_ptr, ptr_bytes, frontier, n_front, fanout, counts);
+  count_launches(1);
+  return check_launch("cxg_sample_counts");
+}
+
+extern "C" int cxg_renumber_claim(const int64_t *picked, int64_t n_picked, int64_t *local_of, int64_t *fresh,
+                                  int64_t *n_fresh, void *stream) {
+  CXG_REQUIRE(n_picked >= 0, CXG_EINVAL, "cxg_renumber_claim: bad size");
+  CXG_REQUIRE(local_of && fresh && n_fresh && (picked || n_picked == 0), CXG_ENULL, "cxg_renumber_claim: NULL argument");
+  cudaStream_t st = as_stream(stream);
+  if (cudaMemsetAsync(n_fresh, 0, sizeof(int64_t), st) != cudaSuccess) return check_launch("cxg_renumber_claim: memset");
+  if (n_picked == 0) return CXG_OK;
+  claim_fresh_kernel<<<grid_for(n_picked), 256, 0, st>>>(picked, n_picked, local_of, fresh,
+                                                        reinterpret_cast<unsigned long long *>(n_fresh));
+  count_launches(1);
+  return check_launch("cxg_renumber_claim");
+}
+
+extern "C" int cxg_renumber_assign(const int64_t *fresh_sorted, int64_t n_fresh, int64_t base, const int64_t *picked,
+                                   int64_t n_picked, int64_t *local_of, int64_t *out, void *stream) {
+  CXG_REQUIRE(n_fresh >= 0 && n_picked >= 0 && base >= 0, CXG_EINVAL, "cxg_renumber_assign: bad sizes");
+  CXG_REQUIRE(local_of && (fresh_sorted || n_fresh == 0) && ((picked && out) || n_picked == 0), CXG_ENULL,
+              "cxg_renumber_assign: NULL argument");
+  cudaStream_t st = as_stream(stream);
+  if (n_fresh > 0) {
+    number_fresh_kernel<<<static_cast<unsigned>((n_fresh + 255) / 256), 256, 0, st>>>(fresh_sorted, n_fresh, base, local_of);
+    count_launches(1);
+  }
+  if (n_picked > 0) {
+    translate_kernel<<<grid_for(n_picked), 256, 0, st>>>(picked, n_picked, local_of, out);
+    count_launches(1);
+  }
+  return check_launch("cxg_renumber_assign");
+}

@@ -36,15 +36,23 @@ int typed_rows_launch(const void *a, const void *w, void *out, const void *rel, 
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kEpiWarps = 4, kProdWarps = 4;
+#ifndef TMM_PROD_WARPS
+#define TMM_PROD_WARPS 4
+#endif
+constexpr int kEpiWarps = 4, kProdWarps = TMM_PROD_WARPS;
+constexpr int kRowsPerProdWarp = 128 / kProdWarps;  // rows of a tile that one producer warp copies
 constexpr int kMmaWarp = kEpiWarps;                              // warp 4
-constexpr int kMmThreads = 32 * (kEpiWarps + 1 + kProdWarps);    // 288
-constexpr int kMaxStages = 6;
+constexpr int kMmThreads = 32 * (kEpiWarps + 1 + kProdWarps);
+#ifndef TMM_MAX_STAGES
+#define TMM_MAX_STAGES 6
+#endif
+constexpr int kMaxStages = 6;       // barrier slots
+constexpr int kUseStages = TMM_MAX_STAGES;  // stages used at most
 #ifndef TMM_RPI
 #define TMM_RPI 8
 #endif
 constexpr int kRpi = TMM_RPI, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction
-constexpr int kSlots = 4 * (8 / kRpi);           // rows of a tile whose chunks one producer thread copies
+constexpr int kSlots = kRowsPerProdWarp / kRpi;  // rows of a tile whose chunks one producer thread copies
 constexpr int kSmemBudget = 226 * 1024;
 constexpr long long kWaitCycles = 1ll << 31;
 
@@ -157,6 +165,20 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 // is what a gather of re-used rows wants), otherwise L2 only (faster when every row is read once).
 template <bool CA>
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int bytes) {
+#ifdef TMM_NO_COPY
+  if (bytes != 7) return;
+#endif
+#ifdef TMM_PLAIN_CP
+  if (bytes == 0) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+    return;
+  }
+  if (CA)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  else
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  return;
+#endif
   if (CA)
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
   else
@@ -164,6 +186,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int by
 }
 
 __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
+#ifdef TMM_NO_STORE
+  if (v.x != 0x12345678u) return;
+#endif
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
@@ -248,7 +273,7 @@ __global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
       r = tile < tile_hi ? a.rel[m0] : -1;
 #pragma unroll
       for (int gi = 0; gi < kSlots; ++gi) {
-        const int64_t pos = m0 + pw * 32 + gi * kRpi + rsub;  // warp pw owns rows 32 pw .. 32 pw + 31
+        const int64_t pos = m0 + pw * kRowsPerProdWarp + gi * kRpi + rsub;  // warp pw owns kRowsPerProdWarp rows
         ia[gi] = -1;
         if (tile < tile_hi && pos < a.m) ia[gi] = a.src != nullptr ? a.src[pos] : pos;
       }
@@ -281,21 +306,53 @@ __global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
         if (!alive) break;
       }
       const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+#ifdef TMM_LDG
+      // experiment: coalesced 16-byte loads into registers, then shared-memory stores
 #pragma unroll
       for (int gi = 0; gi < kSlots; ++gi) {
-        const int row = pw * 32 + gi * kRpi + rsub;  // row of the tile
+        const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;
+        const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
+        const T *src_row = ok ? A + ia[gi] * a.k : A;
+        uint8_t *d0 = smem_a + s * a_bytes + (row >> 3) * sbo + (row & 7) * 16;
+        for (int c = cq; c < chunks; c += kCpi * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (ok && c + u * kCpi < chunks) v[u] = __ldg(reinterpret_cast<const uint4 *>(src_row) + c + u * kCpi);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (c + u * kCpi < chunks) *reinterpret_cast<uint4 *>(d0 + (c + u * kCpi) * 128) = v[u];
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ++it;
+      signal_upto(0);
+#else
+#pragma unroll
+      for (int gi = 0; gi < kSlots; ++gi) {
+        const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;  // row of the tile
         const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
         const T *src_row = ok ? A + ia[gi] * a.k : A;
         const int bytes = ok ? 16 : 0;  // size 0 writes zeros
         const uint32_t d0 = a0 + (row >> 3) * sbo + (row & 7) * 16;
         for (int c = cq; c < chunks; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
       }
+#ifdef TMM_NOINC
+      // the full barrier counts this thread's arrival when all its copies issued so far have landed
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&bars.full[s])) : "memory");
+      ++it;
+      signalled = it;
+#else
       asm volatile("cp.async.commit_group;" ::: "memory");
       ++it;
       signal_upto(S - 1);
+#endif
+#endif
     }
     if (alive) signal_upto(0);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
     if (lane == 0) {
@@ -474,7 +531,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
               "cxg_typed_matmul: one tile of %zu bytes exceeds shared memory", a_bytes + b_bytes);
   int stages = static_cast<int>((kSmemBudget - b_bytes) / a_bytes);
-  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > kUseStages) stages = kUseStages;
   const size_t smem = b_bytes + stages * a_bytes;
   CXG_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (k * elem) % 16 == 0 &&
                   (n * elem) % 16 == 0,

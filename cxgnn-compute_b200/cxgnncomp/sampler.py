@@ -24,6 +24,14 @@ class NeighborSampler:
         self.num_nodes = graph_ptr.shape[0] - 1
         # global id -> position in the batch, -1 outside the batch; cleared after every batch
         self.local_of = torch.full((self.num_nodes,), -1, dtype=torch.int64, device=graph_ptr.device)
+        self.n_fresh = torch.zeros(1, dtype=torch.int64, device=graph_ptr.device)
+        self._fresh_buf = torch.empty(0, dtype=torch.int64, device=graph_ptr.device)
+
+    def _scratch(self, n):
+        if self._fresh_buf.shape[0] < n:
+            self._fresh_buf = torch.empty(max(n, 2 * self._fresh_buf.shape[0]), dtype=torch.int64,
+                                          device=self._fresh_buf.device)
+        return self._fresh_buf
 
     def sample(self, seeds, seed=0):
         """seeds: distinct int64 global ids on the graph's device. Returns (nodes, ptr, idx, num_node_in_layer,
@@ -39,9 +47,12 @@ class NeighborSampler:
         for hop, fanout in enumerate(self.fanouts):
             out_ptr, picked = cxgnncomp_backend.sample_neighbors(self.ptr, self.idx, frontier, fanout,
                                                                  seed * 1000003 + hop)
-            fresh = torch.unique(picked[local_of[picked] < 0])  # ascending ids
-            local_of[fresh] = n_known + torch.arange(fresh.shape[0], device=dev)
-            idx_parts.append(local_of[picked])
+            # ids seen for the first time: claimed once each on the device, then sorted so that the batch does
+            # not depend on the order in which threads claimed them
+            fresh_buf = self._scratch(min(picked.shape[0], self.num_nodes))
+            cxgnncomp_backend.renumber_claim(picked, local_of, fresh_buf, self.n_fresh)
+            fresh = torch.sort(fresh_buf[:int(self.n_fresh)]).values
+            idx_parts.append(cxgnncomp_backend.renumber_assign(fresh, n_known, picked, local_of))
             ptr_parts.append(out_ptr[1:] + edge_base)
             edge_base += picked.shape[0]
             n_known += fresh.shape[0]

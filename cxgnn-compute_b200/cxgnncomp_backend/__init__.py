@@ -420,6 +420,9 @@ _sample = _sig("cxg_sample_neighbors", [_vp, _vp, ctypes.c_int, ctypes.c_int, _v
                                         ctypes.c_uint64, _vp])
 
 
+_sample_counts = _sig("cxg_sample_counts", [_vp, ctypes.c_int, _vp, _i64, ctypes.c_int, _vp, _vp])
+
+
 def sample_neighbors(graph_ptr, graph_idx, frontier, fanout, seed):
     """min(degree, fanout) distinct in-neighbours of every frontier node, uniformly without replacement, as a CSR
     (out_ptr int64 [n + 1], out int64 global ids). Deterministic in (seed, node id). This is the step the reference
@@ -428,15 +431,42 @@ def sample_neighbors(graph_ptr, graph_idx, frontier, fanout, seed):
     _cuda(graph_idx, "graph_idx", _INDEX_DTYPES)
     _cuda(frontier, "frontier", (torch.int64,))
     n = frontier.shape[0]
-    deg = (graph_ptr[frontier + 1] - graph_ptr[frontier]).long()
     out_ptr = torch.zeros(n + 1, dtype=torch.int64, device=frontier.device)
-    torch.cumsum(deg.clamp(max=int(fanout)), 0, out=out_ptr[1:])
+    with torch.cuda.device(frontier.device):
+        _check(_sample_counts(_p(graph_ptr), graph_ptr.element_size(), _p(frontier), n, int(fanout),
+                              out_ptr[1:].data_ptr(), _stream()), "cxg_sample_counts")
+    out_ptr[1:].cumsum_(0)
     out = torch.empty(int(out_ptr[-1]), dtype=torch.int64, device=frontier.device)
     with torch.cuda.device(frontier.device):
         _check(_sample(_p(graph_ptr), _p(graph_idx), graph_ptr.element_size(), graph_idx.element_size(), _p(frontier), n,
                        int(fanout), _p(out_ptr), _p(out), int(seed) & 0xFFFFFFFFFFFFFFFF, _stream()),
                "cxg_sample_neighbors")
     return out_ptr, out
+
+
+_claim = _sig("cxg_renumber_claim", [_vp, _i64, _vp, _vp, _vp, _vp])
+_assign = _sig("cxg_renumber_assign", [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp])
+
+
+def renumber_claim(picked, local_of, fresh, n_fresh):
+    """Appends the ids of `picked` that have no batch position yet (local_of == -1) to `fresh`, each once, and
+    marks them claimed; n_fresh (int64 [1], device) receives the count. See cxg_renumber_claim."""
+    for t_, name in ((picked, "picked"), (local_of, "local_of"), (fresh, "fresh"), (n_fresh, "n_fresh")):
+        _cuda(t_, name, (torch.int64,))
+    with torch.cuda.device(picked.device):
+        _check(_claim(_p(picked), picked.shape[0], _p(local_of), _p(fresh), _p(n_fresh), _stream()),
+               "cxg_renumber_claim")
+
+
+def renumber_assign(fresh_sorted, base, picked, local_of):
+    """local_of[fresh_sorted[i]] = base + i, then returns local_of[picked]. See cxg_renumber_assign."""
+    for t_, name in ((picked, "picked"), (local_of, "local_of"), (fresh_sorted, "fresh_sorted")):
+        _cuda(t_, name, (torch.int64,))
+    out = torch.empty_like(picked)
+    with torch.cuda.device(picked.device):
+        _check(_assign(_p(fresh_sorted), fresh_sorted.shape[0], int(base), _p(picked), picked.shape[0], _p(local_of),
+                       _p(out), _stream()), "cxg_renumber_assign")
+    return out
 
 
 class REDUCEOP(enum.IntEnum):

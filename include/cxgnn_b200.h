@@ -281,9 +281,26 @@ int cxg_gather_rows(const void *in, const int64_t *rows, void *out, int64_t n_ro
  * d <= fanout, else a uniform subset drawn by Floyd's algorithm from a counter-based generator keyed by
  * (seed, v). out_ptr is the caller's exclusive prefix sum of min(d, fanout). fanout <= 64.
  */
+/* counts[i] = min(in-degree of frontier[i], fanout): the row lengths whose prefix sum is out_ptr below. */
+int cxg_sample_counts(const void *graph_ptr, int ptr_bytes, const int64_t *frontier, int64_t n_front,
+                      int fanout, int64_t *counts, void *stream);
 int cxg_sample_neighbors(const void *graph_ptr, const void *graph_idx, int ptr_bytes, int idx_bytes,
                          const int64_t *frontier, int64_t n_front, int fanout,
                          const int64_t *out_ptr, int64_t *out, uint64_t seed, void *stream);
+
+/*
+ * Renumbering of sampled neighbours into batch-local ids (what the reference's loader does before it hands
+ * over a CSR_Layer batch). local_of [num_nodes] int64 maps global id -> position in the batch, -1 outside it.
+ * cxg_renumber_claim appends every id of picked[] that has no position yet to fresh[] exactly once (in no
+ * fixed order; *n_fresh, a device counter, receives how many) and marks it as claimed (-2). The caller reads
+ * n_fresh, sorts fresh[0 .. n_fresh) and calls cxg_renumber_assign: local_of[fresh_sorted[i]] = base + i, then
+ * out[i] = local_of[picked[i]]. fresh needs room for min(n_picked, num_nodes) entries.
+ */
+int cxg_renumber_claim(const int64_t *picked, int64_t n_picked, int64_t *local_of, int64_t *fresh,
+                       int64_t *n_fresh, void *stream);
+int cxg_renumber_assign(const int64_t *fresh_sorted, int64_t n_fresh, int64_t base,
+                        const int64_t *picked, int64_t n_picked, int64_t *local_of, int64_t *out,
+                        void *stream);
 
 /*
  * topo_sort (src/cpp/src/schedule.cu:72-124, python_bindings/binding.cpp:33) on HOST arrays: nodes in
