@@ -12,8 +12,13 @@
 // keeps the reference's order: lane l takes edges l, l+32, ...; the row maximum starts at
 // -100000; the row sum adds the lanes' partial sums with the shuffle-down tree 16, 8, 4, 2, 1;
 // the quotient is an exact fp32 division. Rows with more than kHeavyRow edges are handed to a
-// second kernel that puts a whole CTA on each of them (their sum order is a CTA tree instead).
+// second kernel that puts a thread-block cluster of 8 CTAs on each of them (their sums join warps through
+// shared memory and CTAs through distributed shared memory, in a fixed order).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace cxg {
 namespace {
@@ -23,6 +28,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kHeavyRow = 1024;      // rows above this many edges get a whole CTA
 constexpr int kHeavyThreads = 1024;  // threads of that CTA
 constexpr int kHeavyWarps = kHeavyThreads / 32;
+constexpr int kHeavyCluster = 8;     // CTAs (one thread-block cluster) that share such a row
 constexpr int kHC = 4;  // heads carried together
 
 struct SoftmaxArgs {
@@ -55,34 +61,48 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// Block-wide sum / max of one value per thread (kHeavyThreads threads), result to all.
-__device__ __forceinline__ float block_sum(float v, float *sh) {
+// Sum / max over all threads of a cluster (kHeavyCluster CTAs of kHeavyThreads threads) of kHC values per
+// thread at once; every thread receives the results. Warps are joined through shared memory, CTAs through
+// distributed shared memory, both in a fixed order. sh: [kHeavyWarps][kHC] floats, cl: [kHC] floats.
+template <bool MAX>
+__device__ __forceinline__ void cluster_reduce(float (&v)[4], float *sh, float *cl) {
+  static_assert(kHC == 4, "reductions carry four heads");
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = 0.f;
+  for (int k = 0; k < kHC; ++k)
 #pragma unroll
-  for (int w = 0; w < kHeavyWarps; ++w) r += sh[w];
-  return r;
-}
-__device__ __forceinline__ float block_max(float v, float *sh) {
-  v = warp_max(v);
+    for (int o = 16; o > 0; o >>= 1) {
+      const float t = __shfl_xor_sync(0xffffffffu, v[k], o);
+      v[k] = MAX ? fmaxf(v[k], t) : v[k] + t;
+    }
   __syncthreads();
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = sh[0];
+  if ((threadIdx.x & 31) == 0)
 #pragma unroll
-  for (int w = 1; w < kHeavyWarps; ++w) r = fmaxf(r, sh[w]);
-  return r;
+    for (int k = 0; k < kHC; ++k) sh[(threadIdx.x >> 5) * kHC + k] = v[k];
+  __syncthreads();
+  if (threadIdx.x < kHC) {
+    float r = sh[threadIdx.x];
+    for (int w = 1; w < kHeavyWarps; ++w) r = MAX ? fmaxf(r, sh[w * kHC + threadIdx.x]) : r + sh[w * kHC + threadIdx.x];
+    cl[threadIdx.x] = r;
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+#pragma unroll
+  for (int k = 0; k < kHC; ++k) {
+    float r = cluster.map_shared_rank(cl, 0)[k];
+    for (int c = 1; c < kHeavyCluster; ++c) {
+      const float t = cluster.map_shared_rank(cl, c)[k];
+      r = MAX ? fmaxf(r, t) : r + t;
+    }
+    v[k] = r;
+  }
+  cluster.sync();  // nobody overwrites cl while a peer still reads it
 }
 
 // Forward for one row; the STEP threads that share the row take edges first+k*STEP.
 // HEAVY = false: one warp, reference summation order. HEAVY = true: one CTA.
 template <typename IdxT, bool HEAVY>
-__device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh) {
-  constexpr int STEP = HEAVY ? kHeavyThreads : 32;
+__device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh, float *cl) {
+  constexpr int STEP = HEAVY ? kHeavyThreads * kHeavyCluster : 32;
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const int H = a.heads;
   const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
@@ -106,8 +126,12 @@ __device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d,
           mx[k] = fmaxf(mx[k], t);
         }
     }
+    if (HEAVY) {
+      cluster_reduce<true>(mx, sh, cl);
+    } else {
 #pragma unroll
-    for (int k = 0; k < kHC; ++k) mx[k] = HEAVY ? block_max(mx[k], sh) : warp_max(mx[k]);
+      for (int k = 0; k < kHC; ++k) mx[k] = warp_max(mx[k]);
+    }
     for (int64_t i = b + first; i < e; i += STEP) {
 #pragma unroll
       for (int k = 0; k < kHC; ++k)
@@ -117,8 +141,12 @@ __device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d,
           part[k] += p;
         }
     }
+    if (HEAVY) {
+      cluster_reduce<false>(part, sh, cl);
+    } else {
 #pragma unroll
-    for (int k = 0; k < kHC; ++k) part[k] = HEAVY ? block_sum(part[k], sh) : warp_tree_sum(part[k]);
+      for (int k = 0; k < kHC; ++k) part[k] = warp_tree_sum(part[k]);
+    }
     for (int64_t i = b + first; i < e; i += STEP) {
 #pragma unroll
       for (int k = 0; k < kHC; ++k)
@@ -131,8 +159,8 @@ __device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d,
 // slope where the forward pre-activation was not positive; grad_src[src] += tmp;
 // grad_dst = sum tmp, written only when the row has both signs (it is 0 otherwise).
 template <typename IdxT, bool HEAVY>
-__device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh) {
-  constexpr int STEP = HEAVY ? kHeavyThreads : 32;
+__device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d, int first, float *sh, float *cl) {
+  constexpr int STEP = HEAVY ? kHeavyThreads * kHeavyCluster : 32;
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const int H = a.heads;
   const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
@@ -144,8 +172,12 @@ __device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d,
 #pragma unroll
       for (int k = 0; k < kHC; ++k)
         if (h0 + k < H) s[k] += a.out[i * H + h0 + k] * a.grad[i * H + h0 + k];
+    if (HEAVY) {
+      cluster_reduce<false>(s, sh, cl);
+    } else {
 #pragma unroll
-    for (int k = 0; k < kHC; ++k) s[k] = HEAVY ? block_sum(s[k], sh) : warp_tree_sum(s[k]);
+      for (int k = 0; k < kHC; ++k) s[k] = warp_tree_sum(s[k]);
+    }
     for (int64_t i = b + first; i < e; i += STEP) {
       const int64_t src = static_cast<int64_t>(__ldg(idx + i));
 #pragma unroll
@@ -162,13 +194,21 @@ __device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d,
           atomicAdd(a.grad_src + src * H + h0 + k, tmp);
         }
     }
+    if (HEAVY) {
+      cluster_reduce<false>(dg, sh, cl);
+      cluster_reduce<false>(pos, sh, cl);
+      cluster_reduce<false>(neg, sh, cl);
+    } else {
 #pragma unroll
-    for (int k = 0; k < kHC; ++k) {
-      dg[k] = HEAVY ? block_sum(dg[k], sh) : warp_tree_sum(dg[k]);
-      pos[k] = HEAVY ? block_sum(pos[k], sh) : warp_tree_sum(pos[k]);
-      neg[k] = HEAVY ? block_sum(neg[k], sh) : warp_tree_sum(neg[k]);
-      if (first == 0 && h0 + k < H && pos[k] > 0.f && neg[k] > 0.f) a.grad_dst[d * H + h0 + k] = dg[k];
+      for (int k = 0; k < kHC; ++k) {
+        dg[k] = warp_tree_sum(dg[k]);
+        pos[k] = warp_tree_sum(pos[k]);
+        neg[k] = warp_tree_sum(neg[k]);
+      }
     }
+#pragma unroll
+    for (int k = 0; k < kHC; ++k)
+      if (first == 0 && h0 + k < H && pos[k] > 0.f && neg[k] > 0.f) a.grad_dst[d * H + h0 + k] = dg[k];
   }
 }
 
@@ -186,21 +226,43 @@ __global__ void __launch_bounds__(kThreads) edge_softmax_rows(SoftmaxArgs a) {
     return;
   }
   if (BWD)
-    softmax_bwd_row<IdxT, false>(a, d, lane, nullptr);
+    softmax_bwd_row<IdxT, false>(a, d, lane, nullptr, nullptr);
   else
-    softmax_fwd_row<IdxT, false>(a, d, lane, nullptr);
+    softmax_fwd_row<IdxT, false>(a, d, lane, nullptr, nullptr);
+}
+
+// Rows above kHeavyRow edges: one thread-block cluster per row (launched with cluster dimension kHeavyCluster).
+template <typename IdxT, bool BWD>
+__global__ void __launch_bounds__(kHeavyThreads) edge_softmax_heavy(SoftmaxArgs a) {
+  __shared__ float sh[kHeavyWarps * kHC];
+  __shared__ float cl[kHC];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int n = min(a.hdr[0], a.max_heavy);
+  const int first = static_cast<int>(cluster.block_rank()) * kHeavyThreads + threadIdx.x;
+  const int n_clusters = gridDim.x / kHeavyCluster;
+  for (int i = blockIdx.x / kHeavyCluster; i < n; i += n_clusters) {  // uniform over the cluster
+    if (BWD)
+      softmax_bwd_row<IdxT, true>(a, a.heavy[i], first, sh, cl);
+    else
+      softmax_fwd_row<IdxT, true>(a, a.heavy[i], first, sh, cl);
+  }
 }
 
 template <typename IdxT, bool BWD>
-__global__ void __launch_bounds__(kHeavyThreads) edge_softmax_heavy(SoftmaxArgs a) {
-  __shared__ float sh[kHeavyWarps];
-  const int n = min(a.hdr[0], a.max_heavy);
-  for (int i = blockIdx.x; i < n; i += gridDim.x) {
-    if (BWD)
-      softmax_bwd_row<IdxT, true>(a, a.heavy[i], threadIdx.x, sh);
-    else
-      softmax_fwd_row<IdxT, true>(a, a.heavy[i], threadIdx.x, sh);
-  }
+cudaError_t launch_heavy(const SoftmaxArgs &a, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((kNumSM / kHeavyCluster) * kHeavyCluster);  // 144 CTAs = 18 clusters
+  cfg.blockDim = dim3(kHeavyThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kHeavyCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, edge_softmax_heavy<IdxT, BWD>, a);
 }
 
 // out[e,h] = <src_feat[src[e],h,:], dst_feat[dst[e],(h),:]>; one warp per edge, the lanes of a
@@ -307,10 +369,10 @@ extern "C" int cxg_edge_softmax_forward(const void *ptr, const void *idx, int pt
   const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
   if (idx_bytes == 8) {
     edge_softmax_rows<int64_t, false><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int64_t, false><<<kNumSM, kHeavyThreads, 0, st>>>(a);
+    if (launch_heavy<int64_t, false>(a, st) != cudaSuccess) return check_launch("edge_softmax_heavy");
   } else {
     edge_softmax_rows<int32_t, false><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int32_t, false><<<kNumSM, kHeavyThreads, 0, st>>>(a);
+    if (launch_heavy<int32_t, false>(a, st) != cudaSuccess) return check_launch("edge_softmax_heavy");
   }
   count_launches(2);
   return check_launch("cxg_edge_softmax_forward");
@@ -334,10 +396,10 @@ extern "C" int cxg_edge_softmax_backward(const void *ptr, const void *idx, int p
   const unsigned grid = static_cast<unsigned>((n_dst + kWarps - 1) / kWarps);
   if (idx_bytes == 8) {
     edge_softmax_rows<int64_t, true><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int64_t, true><<<kNumSM, kHeavyThreads, 0, st>>>(a);
+    if (launch_heavy<int64_t, true>(a, st) != cudaSuccess) return check_launch("edge_softmax_heavy");
   } else {
     edge_softmax_rows<int32_t, true><<<grid, kThreads, 0, st>>>(a);
-    edge_softmax_heavy<int32_t, true><<<kNumSM, kHeavyThreads, 0, st>>>(a);
+    if (launch_heavy<int32_t, true>(a, st) != cudaSuccess) return check_launch("edge_softmax_heavy");
   }
   count_launches(2);
   return check_launch("cxg_edge_softmax_backward");

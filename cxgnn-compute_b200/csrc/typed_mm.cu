@@ -8,11 +8,15 @@
 //
 // A persistent, warp-specialised CTA per SM owns a contiguous range of 128-position tiles (so the
 // relation changes at most num_rel times per CTA) and runs three roles that meet only at mbarriers:
-//   * 4 producer warps gather the 128 rows of A of a tile with 16-byte `cp.async` copies into one
-//     stage of a shared-memory ring, in the K-major "core matrix" layout the tensor core reads
+//   * 4 or 8 producer warps gather the 128 rows of A of a tile with 16-byte `cp.async` copies into
+//     one stage of a shared-memory ring, in the K-major "core matrix" layout the tensor core reads
 //     without swizzle (8 rows x 16 bytes per core matrix; padding rows are zero-filled by a copy
-//     of size 0). Up to `stages` tiles are in flight per CTA, which is what keeps HBM busy: the
-//     op is memory-bound at RGCN shapes (K = 128, N = 64: 43 flop per byte in bf16). W[rel]
+//     of size 0), and hand the stage over with `cp.async.mbarrier.arrive.noinc`: the barrier counts
+//     a thread's arrival when its copies have landed, so a producer never waits for its own
+//     copies and up to `stages` tiles are in flight per CTA (waiting with `cp.async.wait_group`
+//     plus a proxy fence in the producer serialised copy and MMA latency and was 13-19 % slower).
+//     The thread that issues the MMAs executes the generic-to-async proxy fence after the barrier.
+//     The op is memory-bound at RGCN shapes (K = 128, N = 64: 43 flop per byte in bf16). W[rel]
 //     (pre-transposed once to [N][K]) is copied the same way when the relation changes, after
 //     the MMAs that read the previous one have drained;
 //   * one thread issues K/16 (bf16) or K/8 (tf32) `tcgen05.mma` instructions per tile with M = 128,
@@ -36,23 +40,11 @@ int typed_rows_launch(const void *a, const void *w, void *out, const void *rel, 
 namespace {
 
 constexpr int kTileM = 128;
-#ifndef TMM_PROD_WARPS
-#define TMM_PROD_WARPS 4
-#endif
-constexpr int kEpiWarps = 4, kProdWarps = TMM_PROD_WARPS;
-constexpr int kRowsPerProdWarp = 128 / kProdWarps;  // rows of a tile that one producer warp copies
+constexpr int kEpiWarps = 4;
+constexpr int kMaxProdWarps = 8;  // producer warps: 8 for 4-byte elements, 4 for 2-byte ones (measured)
 constexpr int kMmaWarp = kEpiWarps;                              // warp 4
-constexpr int kMmThreads = 32 * (kEpiWarps + 1 + kProdWarps);
-#ifndef TMM_MAX_STAGES
-#define TMM_MAX_STAGES 6
-#endif
-constexpr int kMaxStages = 6;       // barrier slots
-constexpr int kUseStages = TMM_MAX_STAGES;  // stages used at most
-#ifndef TMM_RPI
-#define TMM_RPI 8
-#endif
-constexpr int kRpi = TMM_RPI, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction
-constexpr int kSlots = kRowsPerProdWarp / kRpi;  // rows of a tile whose chunks one producer thread copies
+constexpr int kMaxStages = 6;
+constexpr int kRpi = 8, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction
 constexpr int kSmemBudget = 226 * 1024;
 constexpr long long kWaitCycles = 1ll << 31;
 
@@ -135,7 +127,7 @@ __global__ void transpose_w(const T *w, T *wt, int num_rel, int k, int n) {
 }
 
 struct Barriers {
-  uint64_t full[kMaxStages];   // producers -> MMA: the stage holds a tile (128 arrivals)
+  uint64_t full[kMaxStages];   // producers -> MMA: the stage holds a tile (one arrival per producer thread)
   uint64_t empty[kMaxStages];  // MMA -> producers: the MMAs that read the stage are done (1 commit)
   uint64_t acc_full[2];        // MMA -> epilogue (1 commit)
   uint64_t acc_empty[2];       // epilogue -> MMA (128 arrivals)
@@ -165,20 +157,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 // is what a gather of re-used rows wants), otherwise L2 only (faster when every row is read once).
 template <bool CA>
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int bytes) {
-#ifdef TMM_NO_COPY
-  if (bytes != 7) return;
-#endif
-#ifdef TMM_PLAIN_CP
-  if (bytes == 0) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
-    return;
-  }
-  if (CA)
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-  else
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-  return;
-#endif
   if (CA)
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
   else
@@ -186,27 +164,15 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int by
 }
 
 __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
-#ifdef TMM_NO_STORE
-  if (v.x != 0x12345678u) return;
-#endif
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// Wait until at most `pending` of this thread's copy groups are still in flight.
-__device__ __forceinline__ void cp_async_wait(int pending) {
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-  }
-}
-
-// T = __nv_bfloat16 (kind::f16, 16 K per instruction) or float (kind::tf32, 8 K per instruction).
-template <typename T, bool CA>
-__global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
+// PW producer warps; each copies 128 / PW rows of a tile, kSlots of them per thread.
+template <typename T, bool CA, int PW>
+__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmArgs a) {
+  constexpr int kProdWarps = PW;
+  constexpr int kRowsPerProdWarp = kTileM / kProdWarps;
+  constexpr int kSlots = kRowsPerProdWarp / kRpi;
   constexpr bool TF32 = sizeof(T) == 4;
   constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
   extern __shared__ __align__(128) uint8_t smem[];
@@ -252,21 +218,13 @@ __global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
 
   if (warp > kMmaWarp) {
     // ================= producers: gather A (and W on a relation change) =================
-    const int pw = warp - kMmaWarp - 1;          // 0..3: owns row groups 4 pw .. 4 pw + 3 of a tile
+    const int pw = warp - kMmaWarp - 1;          // producer warp: owns rows pw * kRowsPerProdWarp .. of every tile
     // one copy instruction of a warp covers kRpi rows x kCpi consecutive 16-byte chunks
     const int rsub = lane / kCpi, cq = lane % kCpi;
     const T *Wt = static_cast<const T *>(a.wt);
     int64_t loaded_rel = -1;
     int64_t it = 0;        // tiles issued by this CTA
-    int64_t signalled = 0; // tiles whose full barrier this thread has arrived on
     bool alive = true;
-    // arrive on the full barrier of every issued tile except the newest `keep` ones
-    auto signal_upto = [&](int keep) {
-      if (it - signalled <= keep) return;
-      cp_async_wait(keep);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      for (; signalled < it - keep; ++signalled) mbar_arrive(&bars.full[signalled % S]);
-    };
     // the relation and the row indices of a tile are fetched one tile ahead, off the critical path
     auto fetch = [&](int64_t tile, int64_t &r, int64_t (&ia)[kSlots]) {
       const int64_t m0 = tile * kTileM;
@@ -288,8 +246,7 @@ __global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
       fetch(tile + 1, r_next, ia_next);
       if (r < 0 || r >= a.num_rel) continue;  // a tile of padding only
       if (r != loaded_rel) {
-        // every MMA issued so far reads the old W: hand over what is pending and let them finish
-        signal_upto(0);
+        // every MMA issued so far reads the old W: let them finish
         for (int64_t j = (it > S ? it - S : 0); j < it && alive; ++j)
           alive = wait_bar(&bars.empty[j % S], static_cast<uint32_t>((j / S) & 1), abort_flag, a.status);
         if (!alive) break;
@@ -306,30 +263,6 @@ __global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
         if (!alive) break;
       }
       const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
-#ifdef TMM_LDG
-      // experiment: coalesced 16-byte loads into registers, then shared-memory stores
-#pragma unroll
-      for (int gi = 0; gi < kSlots; ++gi) {
-        const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;
-        const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
-        const T *src_row = ok ? A + ia[gi] * a.k : A;
-        uint8_t *d0 = smem_a + s * a_bytes + (row >> 3) * sbo + (row & 7) * 16;
-        for (int c = cq; c < chunks; c += kCpi * 8) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            v[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (ok && c + u * kCpi < chunks) v[u] = __ldg(reinterpret_cast<const uint4 *>(src_row) + c + u * kCpi);
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (c + u * kCpi < chunks) *reinterpret_cast<uint4 *>(d0 + (c + u * kCpi) * 128) = v[u];
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      ++it;
-      signal_upto(0);
-#else
 #pragma unroll
       for (int gi = 0; gi < kSlots; ++gi) {
         const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;  // row of the tile
@@ -339,19 +272,11 @@ __global__ void __launch_bounds__(kMmThreads, 1) typed_mm_tc(TmmArgs a) {
         const uint32_t d0 = a0 + (row >> 3) * sbo + (row & 7) * 16;
         for (int c = cq; c < chunks; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
       }
-#ifdef TMM_NOINC
-      // the full barrier counts this thread's arrival when all its copies issued so far have landed
+      // the tile's full barrier counts this thread's arrival when all copies it has issued so far (this tile's
+      // rows, and W when it was re-copied) have landed: the producer never waits for its own copies
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&bars.full[s])) : "memory");
       ++it;
-      signalled = it;
-#else
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      ++it;
-      signal_upto(S - 1);
-#endif
-#endif
     }
-    if (alive) signal_upto(0);
     asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
@@ -531,7 +456,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
               "cxg_typed_matmul: one tile of %zu bytes exceeds shared memory", a_bytes + b_bytes);
   int stages = static_cast<int>((kSmemBudget - b_bytes) / a_bytes);
-  if (stages > kUseStages) stages = kUseStages;
+  if (stages > kMaxStages) stages = kMaxStages;
   const size_t smem = b_bytes + stages * a_bytes;
   CXG_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (k * elem) % 16 == 0 &&
                   (n * elem) % 16 == 0,
@@ -561,17 +486,17 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   // rows that are gathered several times each go through L1, rows read once bypass it
   const bool ca = src_idx != nullptr && m_valid * 2 <= m;
   cudaError_t e = cudaSuccess;
-  auto launch = [&](auto kernel) {
+  auto launch = [&](auto kernel, int prod_warps) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), kMmThreads, smem, st>>>(t);
+    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), 32 * (kEpiWarps + 1 + prod_warps), smem, st>>>(t);
   };
   if (dtype == CXG_F32) {
     transpose_w<float><<<kNumSM, 256, 0, st>>>(static_cast<const float *>(w), static_cast<float *>(wt), num_rel, k, n);
-    if (ca) launch(typed_mm_tc<float, true>); else launch(typed_mm_tc<float, false>);
+    if (ca) launch(typed_mm_tc<float, true, 8>, 8); else launch(typed_mm_tc<float, false, 8>, 8);
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),
                                                        static_cast<__nv_bfloat16 *>(wt), num_rel, k, n);
-    if (ca) launch(typed_mm_tc<__nv_bfloat16, true>); else launch(typed_mm_tc<__nv_bfloat16, false>);
+    if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4>, 4); else launch(typed_mm_tc<__nv_bfloat16, false, 4>, 4);
   }
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_typed_matmul: %s", cudaGetErrorString(e));
   count_launches(2);
