@@ -310,12 +310,12 @@ def main():
             # the edges that read this rank's own rows are aggregated while the remote rows are in flight,
             # the rest is accumulated onto them afterwards
             work = ex.exchange(x_full, send_buf, async_op=True)
-            be._spmm_forward(x_full, graph_own[0], graph_own[1], n_local, out=y)
+            be.spmm_into(y, graph_own[0], graph_own[1], x_full, n_local)
             work.wait()
-            return be._spmm_forward(x_full, graph_rem[0], graph_rem[1], n_local, out=y, accumulate=True)
+            return be.spmm_into(y, graph_rem[0], graph_rem[1], x_full, n_local, accumulate=True)
         if world > 1:
             exchange()
-        return be._spmm_forward(x_full, lptr, lidx, n_local, out=y)
+        return be.spmm_into(y, lptr, lidx, x_full, n_local)
 
     def timed(fn, k):
         """k calls of fn, each between its own pair of events on the current stream, L2 flushed before."""
@@ -339,7 +339,7 @@ def main():
     launches = be.kernel_launch_count() - launches0
     barrier()
     # kernel-only time of the SpMM call (no exchange), for the roofline
-    spmm_ms = timed(lambda: be._spmm_forward(x_full, lptr, lidx, n_local, out=y), args.steps) / args.steps
+    spmm_ms = timed(lambda: be.spmm_into(y, lptr, lidx, x_full, n_local), args.steps) / args.steps
     barrier()
     exch_ms = timed(exchange, args.steps) / args.steps if world > 1 else 0.0
     barrier()
@@ -397,7 +397,7 @@ def main():
                         ev_in[b].record(s_in)
                     s_main.wait_event(ev_in[b])
                     s_main.wait_event(ev_out[b])  # the download that last read this output buffer
-                    be._spmm_forward(xb[b], pb[b], ib[b], n_local, out=yb[b])
+                    be.spmm_into(yb[b], pb[b], ib[b], xb[b], n_local)
                     ev_comp[b].record(s_main)
                     with torch.cuda.stream(s_out):
                         s_out.wait_event(ev_comp[b])
@@ -427,7 +427,7 @@ def main():
         d2h = hy.numel() * elem
         e2e = {"value": b_alg_total / (float(te[0]) * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": float(te[0]),
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": ksteps,
-               "api": ("cxg_spmm_csr through cxgnncomp_backend with a caller-supplied output, inputs from pinned host "
+               "api": ("cxgnncomp_backend.spmm_into (cxg_spmm_csr with a caller-owned output), inputs from pinned host "
                        "memory, two buffer sets: upload of step k+1, aggregation of step k and download of step k-1 "
                        "overlap") if pipelined else
                       "cxgnncomp_backend.run_spmm_configurable, inputs from pinned host memory"}

@@ -369,6 +369,15 @@ def run_spmm_configurable(ptr, idx, vin, num_node, grid_x=0, grid_y=0, block_x=0
     return _spmm_forward(vin, ptr, idx, num_node)
 
 
+def spmm_into(out, ptr, idx, vin, num_node, reduce="sum", accumulate=False):
+    """SpMM into a caller-owned [num_node, F] (or [num_node, H, F]) tensor: out = A vin, or out += A vin with
+    accumulate=True. Not in the reference (its outputs are always fresh tensors); for loops that keep their
+    buffers, e.g. double-buffered pipelines, and for accumulating several source blocks into one output."""
+    _cuda(out, "out", (vin.dtype,))
+    return _spmm_forward(vin, ptr, idx, num_node, out=out, accumulate=accumulate,
+                         reduce=CXG_MEAN if reduce == "mean" else CXG_SUM)
+
+
 def run_spmm_configurable_int32(ptr, idx, vin, num_node, *tuner_args):
     """int32 ptr/idx variant (spmm_host.cu:99-156)."""
     _cuda(ptr, "ptr", (torch.int32,))

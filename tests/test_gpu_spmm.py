@@ -370,3 +370,18 @@ def test_gather_rows(cuda, dtype, width):
     got = be.gather_rows(x.cuda(), rows.cuda())
     assert torch.equal(got.cpu(), x[rows])
     assert be.gather_rows(x.cuda(), rows[:0].cuda()).shape == (0, width)
+
+
+def test_spmm_into_overwrites_and_accumulates(cuda):
+    import cxgnncomp_backend as be
+    ptr, idx = random_csr(300, 280, 7, seed=95, hub=400)
+    x = randn((280, 64), 96)
+    p, i, xg = ptr.cuda(), idx.cuda(), x.cuda()
+    want = be.run_spmm_configurable(p, i, xg, 300)
+    out = torch.full((300, 64), 7.0, device="cuda")
+    assert be.spmm_into(out, p, i, xg, 300) is out and torch.equal(out, want)
+    be.spmm_into(out, p, i, xg, 300, accumulate=True)
+    assert rel_err(out.cpu(), 2 * want.cpu()) < 1e-6
+    mean = torch.empty_like(out)
+    be.spmm_into(mean, p, i, xg, 300, reduce="mean")
+    assert torch.equal(mean, be._spmm_forward(xg, p, i, 300, reduce=be.CXG_MEAN))
