@@ -259,9 +259,11 @@ class MyRGCNConv(torch.nn.Module):
     into the destination rows (atomic, so the order of the additions is not fixed); "transform_first" multiplies
     every node by every relation's weight (one batched GEMM) and aggregates rows of that [R * N, out] table
     with `aggr_rel`, the ordering of TypedLinearS2DMMAggrOP (typed_linear.py:191-221): it moves `out` instead of
-    `in` values per edge and wins when the mean degree exceeds num_rel * out / in."""
+    `in` values per edge and wins when the mean degree exceeds num_rel * out / in; fp32 inputs take that GEMM in
+    TF32, the precision of the typed matmul (and of the reference's `tl.dot`). "auto" (default) picks between
+    "fused_gather" and "transform_first" by the bytes each moves for the graph at hand."""
 
-    def __init__(self, in_channels, hidden_channels, num_rel, norm="total", schedule="fused_gather"):
+    def __init__(self, in_channels, hidden_channels, num_rel, norm="total", schedule="auto"):
         super().__init__()
         assert num_rel > 0
         self.in_channels = in_channels
@@ -274,6 +276,7 @@ class MyRGCNConv(torch.nn.Module):
         self.single_linear = torch.nn.Linear(in_channels, hidden_channels)
         self.reset_parameters()
         self.preprocessed = []
+        self._types32 = None
 
     def reset_parameters(self):
         glorot(self.linear)
@@ -282,16 +285,34 @@ class MyRGCNConv(torch.nn.Module):
     def forward(self, x, ptr, idx, edge_types, num_node):
         if idx.shape[0] > 1e8:
             return RGCNOP.apply(x, self.linear, ptr, idx, edge_types, num_node)
-        if len(self.preprocessed) == 0:
-            self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)
         num_edge = edge_types.shape[0]
         deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(x.dtype)
-        if self.norm == "total" and self.schedule == "transform_first":
-            xw = torch.matmul(x.unsqueeze(0), self.linear)  # [R, N_src, out]
-            out = cxgnncomp_backend.aggr_rel(xw.reshape(-1, xw.shape[-1]), ptr, idx, edge_types.int(), num_node,
+        schedule = self.schedule
+        if schedule == "auto":
+            # values moved per call: per-edge gather of `in` + write of `out`, against one pass over x, the
+            # [R, N, out] table written and `out` values gathered per edge
+            k, o, n_src = self.in_channels, self.hidden_channels, x.shape[0]
+            fused = num_edge * (k + o)
+            table = n_src * k + self.num_rel * n_src * o + num_edge * o
+            schedule = "transform_first" if table < fused else "fused_gather"
+        if self.norm == "total" and schedule == "transform_first":
+            if x.dtype == torch.float32:
+                old = torch.backends.cuda.matmul.allow_tf32
+                torch.backends.cuda.matmul.allow_tf32 = True
+                try:
+                    xw = torch.matmul(x.unsqueeze(0), self.linear)  # [R, N_src, out]
+                finally:
+                    torch.backends.cuda.matmul.allow_tf32 = old
+            else:
+                xw = torch.matmul(x.unsqueeze(0), self.linear)
+            if self._types32 is None or self._types32[0] is not edge_types:
+                self._types32 = (edge_types, edge_types.int())  # aggr_rel takes int32 relation ids
+            out = cxgnncomp_backend.aggr_rel(xw.reshape(-1, xw.shape[-1]), ptr, idx, self._types32[1], num_node,
                                              self.num_rel)
             return out / deg.unsqueeze(-1)
-        if self.norm == "total" and self.schedule != "e2e":
+        if len(self.preprocessed) == 0:  # relation buckets, built on the first call like the reference caches them
+            self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)
+        if self.norm == "total" and schedule != "e2e":
             if len(self.preprocessed) == 4:  # first call on this graph: positions -> source / destination node
                 sorted_types, _, indices, _ = self.preprocessed
                 dst = torch.repeat_interleave(torch.arange(num_node, device=x.device),
@@ -303,7 +324,7 @@ class MyRGCNConv(torch.nn.Module):
                                                          torch.where(ok, dst[safe], minus)]
             sorted_types, _, indices, count, src_sorted, dst_sorted = self.preprocessed
             out = RGCNFusedOP.apply(x, self.linear, ptr, sorted_types, src_sorted, dst_sorted, indices, num_node,
-                                    num_edge, self.schedule == "fused_scatter", count)
+                                    num_edge, schedule == "fused_scatter", count)
             return out / deg.unsqueeze(-1)
         if self.norm == "relation":
             # per-(destination, relation) degree: scale every edge's row before the segment sum
