@@ -295,13 +295,20 @@ def main():
     b_alg_total = algorithmic_bytes(n, n, nnz, feat, elem, idx_bytes)
     b_alg_local = algorithmic_bytes(n_local, n, int(lptr[n_local]), feat, elem, idx_bytes)
 
-    def exchange():
-        """x_full receives what this rank's aggregation reads: every shard (one NCCL all-gather) or the rows its
-        edges name (pack + one NCCL all-to-all)."""
+    def exchange(buf=None):
+        """The feature buffer (x_full by default) receives what this rank's aggregation reads: every shard (one
+        NCCL all-gather) or the rows its edges name (pack + one NCCL all-to-all)."""
+        buf = x_full if buf is None else buf
         if ex is not None:
-            ex.exchange(x_full, send_buf)
+            ex.exchange(buf, send_buf)
         else:
-            exchange_features(x_full, part, rank)
+            exchange_features(buf, part, rank)
+
+    def own_rows(buf):
+        """This rank's own feature rows inside a feature buffer."""
+        if world == 1:
+            return buf
+        return ex.own(buf) if ex is not None else part.shard(buf, rank)
 
     overlap = ex is not None and args.overlap
 
@@ -365,60 +372,47 @@ def main():
         hy = torch.empty(y.shape, dtype=dtype).pin_memory()
         d_idx, d_ptr = torch.empty_like(lidx), torch.empty_like(lptr)
 
-        def e2e_step():
-            x_own.copy_(hx, non_blocking=True)
-            d_idx.copy_(hidx, non_blocking=True)
-            d_ptr.copy_(hptr, non_blocking=True)
-            if world > 1:
-                exchange()
-            out = be.run_spmm_configurable(d_ptr, d_idx, x_full, n_local)
-            hy.copy_(out, non_blocking=True)
-
         ksteps = min(args.steps, 5)
-        pipelined = world == 1
-        if pipelined:
-            # Double-buffered: the upload of step k+1 runs on its own stream while step k aggregates and step k-1's
-            # result returns to the host (the link is full duplex), so a step costs max(upload, download), not their sum.
-            xb, ib, pb, yb = [x_full, torch.empty_like(x_full)], [d_idx, torch.empty_like(d_idx)], \
-                [d_ptr, torch.empty_like(d_ptr)], [y, torch.empty_like(y)]
-            s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-            ev_in = [torch.cuda.Event() for _ in range(2)]
-            ev_comp = [torch.cuda.Event() for _ in range(2)]
-            ev_out = [torch.cuda.Event() for _ in range(2)]
+        # Double-buffered: the upload of step k+1 runs on its own stream while step k aggregates and step k-1's
+        # result returns to the host (the link is full duplex), so a step costs max(upload, download), not their sum.
+        xb, ib, pb, yb = [x_full, torch.empty_like(x_full)], [d_idx, torch.empty_like(d_idx)], \
+            [d_ptr, torch.empty_like(d_ptr)], [y, torch.empty_like(y)]
+        s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_comp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
-            def run_pipelined(k_steps):
-                for k in range(k_steps):
-                    b = k & 1
-                    with torch.cuda.stream(s_in):
-                        s_in.wait_event(ev_comp[b])  # the aggregation that last read these buffers
-                        xb[b].copy_(hx, non_blocking=True)
-                        ib[b].copy_(hidx, non_blocking=True)
-                        pb[b].copy_(hptr, non_blocking=True)
-                        ev_in[b].record(s_in)
-                    s_main.wait_event(ev_in[b])
-                    s_main.wait_event(ev_out[b])  # the download that last read this output buffer
-                    be.spmm_into(yb[b], pb[b], ib[b], xb[b], n_local)
-                    ev_comp[b].record(s_main)
-                    with torch.cuda.stream(s_out):
-                        s_out.wait_event(ev_comp[b])
-                        hy.copy_(yb[b], non_blocking=True)
-                        ev_out[b].record(s_out)
-                s_main.wait_event(ev_out[0])
-                s_main.wait_event(ev_out[1])
+        def run_pipelined(k_steps):
+            for k in range(k_steps):
+                b = k & 1
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_comp[b])  # the aggregation that last read these buffers
+                    own_rows(xb[b]).copy_(hx, non_blocking=True)
+                    ib[b].copy_(hidx, non_blocking=True)
+                    pb[b].copy_(hptr, non_blocking=True)
+                    ev_in[b].record(s_in)
+                s_main.wait_event(ev_in[b])
+                s_main.wait_event(ev_out[b])  # the download that last read this output buffer
+                if world > 1:
+                    exchange(xb[b])
+                be.spmm_into(yb[b], pb[b], ib[b], xb[b], n_local)
+                ev_comp[b].record(s_main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[b])
+                    hy.copy_(yb[b], non_blocking=True)
+                    ev_out[b].record(s_out)
+            s_main.wait_event(ev_out[0])
+            s_main.wait_event(ev_out[1])
 
-            run_pipelined(2)
-            barrier()
-            a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a_ev.record()
-            run_pipelined(ksteps)
-            b_ev.record()
-            b_ev.synchronize()
-            e_ms = a_ev.elapsed_time(b_ev) / ksteps
-            del xb, ib, pb, yb
-        else:
-            e2e_step()
-            barrier()
-            e_ms = timed(e2e_step, ksteps) / ksteps
+        run_pipelined(2)
+        barrier()
+        a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_ev.record()
+        run_pipelined(ksteps)
+        b_ev.record()
+        b_ev.synchronize()
+        e_ms = a_ev.elapsed_time(b_ev) / ksteps
+        del xb, ib, pb, yb
         barrier()
         te = torch.tensor([e_ms], dtype=torch.float64, device=dev)
         if world > 1:
@@ -428,9 +422,8 @@ def main():
         e2e = {"value": b_alg_total / (float(te[0]) * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": float(te[0]),
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": ksteps,
                "api": ("cxgnncomp_backend.spmm_into (cxg_spmm_csr with a caller-owned output), inputs from pinned host "
-                       "memory, two buffer sets: upload of step k+1, aggregation of step k and download of step k-1 "
-                       "overlap") if pipelined else
-                      "cxgnncomp_backend.run_spmm_configurable, inputs from pinned host memory"}
+                       "memory, two buffer sets: upload of step k+1, exchange + aggregation of step k and download "
+                       "of step k-1 overlap")}
         del hx, hidx, hptr, hy
 
     peak, peak_src = load_peaks()
