@@ -106,6 +106,37 @@ __device__ __forceinline__ void softmax_fwd_row(const SoftmaxArgs &a, int64_t d,
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const int H = a.heads;
   const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
+  if (!HEAVY && e - b <= 32) {
+    // at most one edge per lane: the three passes collapse into one, every value stays in registers and is
+    // written once (same operations in the same order as below, so the same bits)
+    const int64_t i = b + first;
+    const bool has = i < e;
+    const int64_t s = has ? static_cast<int64_t>(__ldg(idx + i)) : 0;
+    for (int h0 = 0; h0 < H; h0 += kHC) {
+      float t[kHC], mx[kHC], p[kHC], sum[kHC];
+#pragma unroll
+      for (int k = 0; k < kHC; ++k) {
+        t[k] = 0.f;
+        mx[k] = -100000.f;
+        if (has && h0 + k < H) {
+          t[k] = __ldg(a.att_dst + d * H + h0 + k) + __ldg(a.att_src + s * H + h0 + k);
+          t[k] = fmaxf(t[k], t[k] * a.slope);
+          mx[k] = fmaxf(mx[k], t[k]);
+        }
+        mx[k] = warp_max(mx[k]);
+        p[k] = has && h0 + k < H ? expf(t[k] - mx[k]) : 0.f;
+        sum[k] = warp_tree_sum(p[k]);
+      }
+      if (has)
+#pragma unroll
+        for (int k = 0; k < kHC; ++k)
+          if (h0 + k < H) {
+            a.out[i * H + h0 + k] = __fdiv_rn(p[k], sum[k]);
+            a.mask[i * H + h0 + k] = t[k] > 0.f;
+          }
+    }
+    return;
+  }
   for (int h0 = 0; h0 < H; h0 += kHC) {
     float dv[kHC], mx[kHC], part[kHC];
 #pragma unroll
@@ -164,6 +195,37 @@ __device__ __forceinline__ void softmax_bwd_row(const SoftmaxArgs &a, int64_t d,
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const int H = a.heads;
   const int64_t b = load_ptr(a.ptr, d, a.ptr_bytes), e = load_ptr(a.ptr, d + 1, a.ptr_bytes);
+  if (!HEAVY && e - b <= 32) {
+    // at most one edge per lane: out, grad and mask are read once (same operations in the same order as below)
+    const int64_t i = b + first;
+    const bool has = i < e;
+    const int64_t src = has ? static_cast<int64_t>(__ldg(idx + i)) : 0;
+    for (int h0 = 0; h0 < H; h0 += kHC) {
+#pragma unroll
+      for (int k = 0; k < kHC; ++k) {
+        const bool on = has && h0 + k < H;
+        const float o = on ? a.out[i * H + h0 + k] : 0.f;
+        const float g = on ? a.grad[i * H + h0 + k] : 0.f;
+        const float sk = warp_tree_sum(on ? o * g : 0.f);
+        float tmp = 0.f, ps = 0.f, ng = 0.f;
+        if (on) {
+          tmp = o * (g - sk);
+          if (!a.mask[i * H + h0 + k]) {
+            tmp *= a.slope;
+            ng = 1.f;
+          } else {
+            ps = 1.f;
+          }
+          atomicAdd(a.grad_src + src * H + h0 + k, tmp);
+        }
+        const float dg = warp_tree_sum(tmp);
+        ps = warp_tree_sum(ps);
+        ng = warp_tree_sum(ng);
+        if (first == 0 && h0 + k < H && ps > 0.f && ng > 0.f) a.grad_dst[d * H + h0 + k] = dg;
+      }
+    }
+    return;
+  }
   for (int h0 = 0; h0 < H; h0 += kHC) {
     float s[kHC], dg[kHC], pos[kHC], neg[kHC];
 #pragma unroll
