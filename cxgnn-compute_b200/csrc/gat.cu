@@ -532,6 +532,86 @@ __global__ void head_sum_kernel(const T *in, T *out, int64_t n_row, int heads, i
 }  // namespace
 }  // namespace cxg
 
+namespace cxg {
+namespace {
+// alpha_src[n, h] = <feat[n, h, :], att_src[h, :]> for all n; alpha_dst[n, h] = <feat[n, h, :], att_dst[h, :]> for
+// n < n_dst: both attention scores of a GAT layer in one pass over the transformed features. One thread per
+// (node, head), the products of a row added in index order.
+__global__ void __launch_bounds__(kThreads) gat_scores_kernel(const float *feat, const float *att_src, const float *att_dst,
+                                                              float *alpha_src, float *alpha_dst, int64_t n_src,
+                                                              int64_t n_dst, int heads, int c) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x;
+  if (i >= n_src * heads) return;
+  const int h = static_cast<int>(i % heads);
+  const int64_t n = i / heads;
+  const float *f = feat + i * c, *as = att_src + h * c, *ad = att_dst + h * c;
+  float s = 0.f, d = 0.f;
+  if (c % 4 == 0) {
+    for (int j = 0; j < c; j += 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(f + j));
+      s = fmaf(v.x, __ldg(as + j), s), d = fmaf(v.x, __ldg(ad + j), d);
+      s = fmaf(v.y, __ldg(as + j + 1), s), d = fmaf(v.y, __ldg(ad + j + 1), d);
+      s = fmaf(v.z, __ldg(as + j + 2), s), d = fmaf(v.z, __ldg(ad + j + 2), d);
+      s = fmaf(v.w, __ldg(as + j + 3), s), d = fmaf(v.w, __ldg(ad + j + 3), d);
+    }
+  } else {
+    for (int j = 0; j < c; ++j) {
+      const float v = __ldg(f + j);
+      s = fmaf(v, __ldg(as + j), s), d = fmaf(v, __ldg(ad + j), d);
+    }
+  }
+  alpha_src[i] = s;
+  if (n < n_dst) alpha_dst[i] = d;
+}
+
+// grad_feat[n, h, :] = g_src[n, h] * att_src[h, :] + (n < n_dst ? g_dst[n, h] * att_dst[h, :] : 0)
+__global__ void __launch_bounds__(kThreads) gat_scores_bwd_kernel(const float *g_src, const float *g_dst,
+                                                                  const float *att_src, const float *att_dst,
+                                                                  float *grad_feat, int64_t n_src, int64_t n_dst,
+                                                                  int heads, int c) {
+  const int64_t total = n_src * heads * c;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t nh = i / c;
+    const int j = static_cast<int>(i - nh * c);
+    const int h = static_cast<int>(nh % heads);
+    float v = __ldg(g_src + nh) * __ldg(att_src + h * c + j);
+    if (nh / heads < n_dst) v = fmaf(__ldg(g_dst + nh), __ldg(att_dst + h * c + j), v);
+    grad_feat[i] = v;
+  }
+}
+}  // namespace
+}  // namespace cxg
+
+extern "C" int cxg_gat_scores(const float *feat, const float *att_src, const float *att_dst, float *alpha_src,
+                              float *alpha_dst, int64_t n_src, int64_t n_dst, int heads, int c, void *stream) {
+  CXG_REQUIRE(n_src >= 0 && n_dst >= 0 && n_dst <= n_src && heads > 0 && c > 0, CXG_EINVAL, "cxg_gat_scores: bad sizes");
+  if (n_src == 0) return CXG_OK;
+  CXG_REQUIRE(feat && att_src && att_dst && alpha_src && (alpha_dst || n_dst == 0), CXG_ENULL,
+              "cxg_gat_scores: NULL argument");
+  CXG_REQUIRE(c % 4 != 0 || reinterpret_cast<uintptr_t>(feat) % 16 == 0, CXG_EINVAL, "cxg_gat_scores: feat alignment");
+  const unsigned grid = static_cast<unsigned>((n_src * heads + kThreads - 1) / kThreads);
+  gat_scores_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(feat, att_src, att_dst, alpha_src, alpha_dst, n_src, n_dst,
+                                                             heads, c);
+  count_launches(1);
+  return check_launch("cxg_gat_scores");
+}
+
+extern "C" int cxg_gat_scores_backward(const float *g_src, const float *g_dst, const float *att_src, const float *att_dst,
+                                       float *grad_feat, int64_t n_src, int64_t n_dst, int heads, int c, void *stream) {
+  CXG_REQUIRE(n_src >= 0 && n_dst >= 0 && n_dst <= n_src && heads > 0 && c > 0, CXG_EINVAL,
+              "cxg_gat_scores_backward: bad sizes");
+  if (n_src == 0) return CXG_OK;
+  CXG_REQUIRE(g_src && (g_dst || n_dst == 0) && att_src && att_dst && grad_feat, CXG_ENULL,
+              "cxg_gat_scores_backward: NULL argument");
+  const int64_t want = (n_src * heads * c + kThreads - 1) / kThreads;
+  const unsigned grid = static_cast<unsigned>(want < kNumSM * 32 ? want : kNumSM * 32);
+  gat_scores_bwd_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(g_src, g_dst, att_src, att_dst, grad_feat, n_src, n_dst,
+                                                                 heads, c);
+  count_launches(1);
+  return check_launch("cxg_gat_scores_backward");
+}
+
 extern "C" int cxg_head_sum(const void *in, void *out, int64_t n_row, int heads, int feat, int dtype, void *stream) {
   CXG_REQUIRE(n_row >= 0 && heads > 0 && feat > 0 && (dtype == CXG_F32 || dtype == CXG_BF16), CXG_EINVAL,
               "cxg_head_sum: bad arguments");

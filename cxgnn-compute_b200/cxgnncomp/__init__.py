@@ -16,6 +16,7 @@ from .codegen import typed_matmul, spmm_torch, Tuner, compare, prof
 from .model import SAGE, GCN, GAT, GIN, RGCN, GNN, get_conv_from_str, get_model_from_str
 from .batch import Batch
 from .sampler import NeighborSampler
+from .neighbor_lstm import NeighborLstmOneByOneOP, NeighborLstmOP, NeighborLstmPadOP
 from .train import train_epoch, num_batches
 from .timer import TimerOP
 from .util import global_tuner

@@ -170,17 +170,70 @@ class NeededRowsExchange:
             unpack(dx_own, self.send_rows, recv_buf)
         return dx_own
 
-    def exchange(self, x_buf, send_buf=None, pack=None, async_op=False):
+    def exchange(self, x_buf, send_buf=None, pack=None, async_op=False, chunks=1):
         """x_buf [buffer_rows, F] with this rank's shard already in x_buf[:n_own]; fills the remote part.
         `pack(x_own, rows, out)` gathers the rows the peers asked for (default: the CUDA row-gather kernel).
-        async_op=True returns the collective's work handle instead of waiting for it on the current stream."""
+        async_op=True returns the collective's work handle instead of waiting for it on the current stream.
+        chunks > 1 cuts every peer's rows into that many parts and sends part c while part c + 1 is packed."""
         x_own = x_buf[:self.n_own]
         if send_buf is None:
             send_buf = torch.empty((self.send_rows.shape[0], x_buf.shape[1]), dtype=x_buf.dtype, device=x_buf.device)
         if pack is None:
             import cxgnncomp_backend
             pack = cxgnncomp_backend.gather_rows
-        pack(x_own, self.send_rows, send_buf)
-        work = dist.all_to_all_single(x_buf[self.n_own:], send_buf, self.recv_counts, self.send_counts,
-                                      group=self.group, async_op=async_op)
-        return work if async_op else x_buf
+        if chunks <= 1 or async_op:
+            pack(x_own, self.send_rows, send_buf)
+            work = dist.all_to_all_single(x_buf[self.n_own:], send_buf, self.recv_counts, self.send_counts,
+                                          group=self.group, async_op=async_op)
+            return work if async_op else x_buf
+        plan = self._chunk_plan(chunks)
+        works = []
+        for c in range(chunks):
+            lo, hi = plan["send_chunk"][c]
+            pack(x_own, plan["send_rows"][lo:hi], send_buf[lo:hi])
+            ops = []
+            for q in range(self.part.world):
+                (sa, sb), (ra, rb) = plan["send_parts"][c][q], plan["recv_parts"][c][q]
+                if sb > sa:
+                    ops.append(dist.P2POp(dist.isend, send_buf[sa:sb], q, group=self.group))
+                if rb > ra:
+                    ops.append(dist.P2POp(dist.irecv, x_buf[self.n_own + ra:self.n_own + rb], q, group=self.group))
+            if ops:
+                works += dist.batch_isend_irecv(ops)
+        for w in works:
+            w.wait()
+        return x_buf
+
+    def _chunk_plan(self, chunks):
+        """send_rows reordered as [part 0 of every peer | part 1 of every peer | ...] with the row ranges of every
+        (chunk, peer) block on the send side (in that reordered list) and on the receive side (in the remote part
+        of the buffer). Both sides cut a peer's list of k rows at the same places, i * k // chunks."""
+        cached = getattr(self, "_plans", {}).get(chunks)
+        if cached is not None:
+            return cached
+        world = self.part.world
+
+        def cuts(counts):
+            base, out = 0, []
+            for k in counts:
+                out.append([(base + i * k // chunks, base + (i + 1) * k // chunks) for i in range(chunks)])
+                base += k
+            return out  # [peer][chunk] -> (lo, hi) in the peer-major list
+
+        send_cut, recv_cut = cuts(self.send_counts), cuts(self.recv_counts)
+        order, send_parts, send_chunk, pos = [], [], [], 0
+        for c in range(chunks):
+            start, parts = pos, []
+            for q in range(world):
+                lo, hi = send_cut[q][c]
+                order.append(self.send_rows[lo:hi])
+                parts.append((pos, pos + hi - lo))
+                pos += hi - lo
+            send_parts.append(parts)
+            send_chunk.append((start, pos))
+        plan = {"send_rows": torch.cat(order) if order else self.send_rows, "send_parts": send_parts,
+                "send_chunk": send_chunk, "recv_parts": [[recv_cut[q][c] for q in range(world)] for c in range(chunks)]}
+        if not hasattr(self, "_plans"):
+            self._plans = {}
+        self._plans[chunks] = plan
+        return plan

@@ -362,6 +362,7 @@ class MyGATConv(torch.nn.Module):
         else:
             self.bias = None
         self.edge_softmax_schedule = "fused"
+        self.fused_scores = True  # both attention scores in one kernel instead of two multiply + sum pairs
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -394,9 +395,13 @@ class MyGATConv(torch.nn.Module):
     def forward_many(self, x, ptr, idx, num_dst, num_src, num_edge):
         H, C = self.heads, self.out_channels
         assert x.dim() == 2
-        x_src = x_dst = F.linear(x[:num_src], self.lin_src).view(-1, H, C)
-        alpha_src = (x_src * self.att_src).sum(dim=-1).view(-1, H)
-        alpha_dst = (x_dst[:num_dst] * self.att_dst).sum(dim=-1).view(-1, H)
+        x_src = F.linear(x[:num_src], self.lin_src).view(-1, H, C)
+        if x_src.dtype == torch.float32 and self.fused_scores:
+            alpha_src, alpha_dst = cxgnncomp_backend.gat_scores(x_src.contiguous(), self.att_src.contiguous(),
+                                                                self.att_dst.contiguous(), num_dst)
+        else:  # the reference's two multiply + sum pairs
+            alpha_src = (x_src * self.att_src).sum(dim=-1).view(-1, H)
+            alpha_dst = (x_src[:num_dst] * self.att_dst).sum(dim=-1).view(-1, H)
         edge_value = self.edge_softmax(ptr=ptr, idx=idx, att_src=alpha_src.contiguous(), att_dst=alpha_dst.contiguous(),
                                        num_edge=num_edge, relu_l=self.negative_slope)
         if self.heads == 1:

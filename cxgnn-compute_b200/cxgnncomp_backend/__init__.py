@@ -524,6 +524,54 @@ def GSpMM_u_e(A_rowptr, A_colind, A_csrVal, B, re_op, comp_op):
     return _gspmm_call(A_rowptr, A_colind, A_csrVal, B, re_op, comp_op)
 
 
+_gat_scores = _sig("cxg_gat_scores", [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp])
+_gat_scores_bwd = _sig("cxg_gat_scores_backward", [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp])
+
+
+class _GatScoresFunction(torch.autograd.Function):
+    """Both attention scores of a GAT layer from the transformed features in one kernel (the reference writes
+    them as two multiply + sum pairs, cxgnncomp/graph_conv.py:470-474)."""
+
+    @staticmethod
+    def forward(ctx, feat, att_src, att_dst, num_dst):
+        n, h, c = feat.shape
+        a_s = torch.empty((n, h), dtype=torch.float32, device=feat.device)
+        a_d = torch.empty((num_dst, h), dtype=torch.float32, device=feat.device)
+        with torch.cuda.device(feat.device):
+            _check(_gat_scores(_p(feat), _p(att_src), _p(att_dst), _p(a_s), _p(a_d), n, num_dst, h, c, _stream()),
+                   "cxg_gat_scores")
+        ctx.save_for_backward(feat, att_src, att_dst)
+        ctx.num_dst = num_dst
+        return a_s, a_d
+
+    @staticmethod
+    def backward(ctx, g_src, g_dst):
+        feat, att_src, att_dst = ctx.saved_tensors
+        n, h, c = feat.shape
+        g_src, g_dst = g_src.contiguous(), g_dst.contiguous()
+        grad_feat = grad_as = grad_ad = None
+        if ctx.needs_input_grad[0]:
+            grad_feat = torch.empty_like(feat)
+            with torch.cuda.device(feat.device):
+                _check(_gat_scores_bwd(_p(g_src), _p(g_dst), _p(att_src), _p(att_dst), _p(grad_feat), n, ctx.num_dst,
+                                       h, c, _stream()), "cxg_gat_scores_backward")
+        if ctx.needs_input_grad[1]:
+            grad_as = torch.einsum("nh,nhc->hc", g_src, feat).view_as(att_src)
+        if ctx.needs_input_grad[2]:
+            grad_ad = torch.einsum("nh,nhc->hc", g_dst, feat[:ctx.num_dst]).view_as(att_dst)
+        return grad_feat, grad_as, grad_ad, None
+
+
+def gat_scores(feat, att_src, att_dst, num_dst):
+    """(alpha_src [n_src, H], alpha_dst [num_dst, H]) from feat [n_src, H, C] and the attention vectors [.., H, C]."""
+    _cuda(feat, "feat", (torch.float32,))
+    _cuda(att_src, "att_src", (torch.float32,))
+    _cuda(att_dst, "att_dst", (torch.float32,))
+    if feat.dim() != 3 or att_src.numel() != feat.shape[1] * feat.shape[2] or att_dst.numel() != att_src.numel():
+        raise RuntimeError("feat must be [n, H, C] and the attention vectors [H, C]")
+    return _GatScoresFunction.apply(feat, att_src, att_dst, int(num_dst))
+
+
 _head_sum_c = _sig("cxg_head_sum", [_vp, _vp, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp])
 
 

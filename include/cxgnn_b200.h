@@ -220,6 +220,19 @@ int cxg_gspmm_csr(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes
                   void *stream);
 
 /*
+ * The two attention scores of a GAT layer in one pass over the transformed features
+ * (cxgnncomp/graph_conv.py:470-474: `(x_src * att_src).sum(-1)`, `(x_dst * att_dst).sum(-1)`):
+ * alpha_src[n, h] = <feat[n, h, :], att_src[h, :]> for n < n_src, alpha_dst[n, h] = <feat[n, h, :], att_dst[h, :]>
+ * for n < n_dst <= n_src. feat [n_src, heads, c] fp32. The backward writes
+ * grad_feat[n, h, :] = g_src[n, h] * att_src[h, :] + (n < n_dst) * g_dst[n, h] * att_dst[h, :].
+ */
+int cxg_gat_scores(const float *feat, const float *att_src, const float *att_dst, float *alpha_src,
+                   float *alpha_dst, int64_t n_src, int64_t n_dst, int heads, int c, void *stream);
+int cxg_gat_scores_backward(const float *g_src, const float *g_dst, const float *att_src,
+                            const float *att_dst, float *grad_feat, int64_t n_src, int64_t n_dst,
+                            int heads, int c, void *stream);
+
+/*
  * out[r, f] = sum over heads of in[r, h, f] (heads added in order into one fp32 accumulator): the head
  * reduction of spmm_multihead's PreReduce / Optimal schedules, which return [n, feat]
  * (src/cpp/src/spmm_host.cu:158-196).

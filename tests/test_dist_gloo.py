@@ -44,6 +44,11 @@ def _worker(rank, world, port, out_dir):
     x_buf = torch.zeros(ex.buffer_rows(), x.shape[1])
     ex.own(x_buf).copy_(x[r0:r1])
     ex.exchange(x_buf, pack=lambda src, rows, out: torch.index_select(src, 0, rows, out=out))
+    # the chunked exchange (parts of every peer's rows sent while the next part is packed) delivers the same buffer
+    x_buf2 = torch.zeros_like(x_buf)
+    ex.own(x_buf2).copy_(x[r0:r1])
+    ex.exchange(x_buf2, pack=lambda src, rows, out: torch.index_select(src, 0, rows, out=out), chunks=3)
+    assert torch.equal(x_buf2, x_buf)
     remote_ids = torch.unique(gidx[(gidx < r0) | (gidx >= r1)])
     assert torch.equal(ex.remote, remote_ids) and ex.recv_counts[rank] == 0 and ex.send_counts[rank] == 0
     assert torch.equal(x_buf[ex.n_own:], x[remote_ids])

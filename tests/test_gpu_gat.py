@@ -115,3 +115,24 @@ def test_gat_aggregation_chain(cuda):
     assert rel_err(xg.grad.cpu(), xr.grad) < 1e-5
     assert rel_err(asg.grad.cpu(), asr.grad) < 1e-4
     assert rel_err(adg.grad.cpu(), adr.grad) < 1e-4
+
+
+@pytest.mark.parametrize("heads,c", [(4, 32), (3, 20), (1, 7)])
+def test_gat_scores_forward_backward(cuda, heads, c):
+    """Both attention scores in one kernel against the reference's multiply + sum pairs
+    (cxgnncomp/graph_conv.py:470-474), values and gradients."""
+    import cxgnncomp_backend as be
+    feat = randn((300, heads, c), 40)
+    a_s, a_d = randn((1, heads, c), 41), randn((1, heads, c), 42)
+    f1, s1, d1 = (t.cuda().requires_grad_(True) for t in (feat, a_s, a_d))
+    got_s, got_d = be.gat_scores(f1, s1, d1, 120)
+    f2, s2, d2 = (t.double().requires_grad_(True) for t in (feat, a_s, a_d))
+    want_s, want_d = (f2 * s2).sum(-1), (f2[:120] * d2).sum(-1)
+    assert got_s.shape == (300, heads) and got_d.shape == (120, heads)
+    assert rel_err(got_s.detach().cpu(), want_s.detach()) < 1e-6 and rel_err(got_d.detach().cpu(), want_d.detach()) < 1e-6
+    gs, gd = randn(want_s.shape, 43), randn(want_d.shape, 44)
+    (got_s * gs.cuda()).sum().backward(retain_graph=True)
+    (got_d * gd.cuda()).sum().backward()
+    ((want_s * gs.double()).sum() + (want_d * gd.double()).sum()).backward()
+    for a, b in ((f1, f2), (s1, s2), (d1, d2)):
+        assert rel_err(a.grad.cpu(), b.grad) < 1e-5

@@ -165,3 +165,40 @@ def test_model_stack_sage(cuda):
     loss = F.nll_loss(model(batch), torch.randint(0, 47, (40,)).cuda())
     loss.backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+def test_neighbor_lstm_buckets(cuda):
+    """LSTM aggregation over degree buckets (neighbor_lstm.py:6-92): per-degree batches equal one call per row;
+    the padded groups equal an explicit zero-padded batch per group. (cuDNN's LSTM runs its GEMMs in TF32 and
+    picks them by batch shape, hence 2e-2.)"""
+    from cxgnncomp import neighbor_lstm as nl
+    torch.manual_seed(6)
+    g = torch.Generator().manual_seed(7)
+    deg = torch.sort(torch.randint(0, 9, (60,), generator=g)).values
+    ptr = torch.zeros(61, dtype=torch.int64)
+    ptr[1:] = torch.cumsum(deg, 0)
+    idx = torch.randint(0, 50, (int(ptr[-1]),), generator=g)
+    feat = randn((50, 16), 8).cuda()
+    lstm = torch.nn.LSTM(16, 16, batch_first=True).cuda()
+    deg_count = torch.bincount(deg, minlength=9)
+    p, i = ptr.cuda(), idx.cuda()
+    with torch.no_grad():
+        one = nl.NeighborLstmOneByOneOP(lstm, p, i, feat)
+        per_deg = nl.NeighborLstmOP(lstm, p, i, feat, deg_count)
+        n0 = int(deg_count[0])
+        # the bucketed form numbers its outputs from the first row with neighbours, like the reference
+        assert rel_err(per_deg[:60 - n0].cpu(), one[n0:].cpu()) < 2e-2
+        padded = nl.NeighborLstmPadOP(lstm, p, i, feat, deg_count, 20, 60)
+        groups = list(nl.padded_groups(deg_count, 20, 60))
+        assert sum(gp[2] for gp in groups) == 60 - n0 and len(groups) > 1
+        for lo_d, hi_d, rows, row0, edge0 in groups:
+            batch = torch.zeros(rows, hi_d, 16, device="cuda")
+            e = edge0
+            r = 0
+            for d in range(lo_d, hi_d + 1):
+                for _ in range(int(deg_count[d])):
+                    batch[r, :d] = feat[i[e:e + d]]
+                    e += d
+                    r += 1
+            want = lstm(batch, None)[0].sum(1)
+            assert rel_err(padded[row0:row0 + rows].cpu(), want.cpu()) < 2e-2
