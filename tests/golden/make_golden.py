@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE'S OWN PYTHON on CPU.
 
 Usage (only where the reference checkout is present):
-    python tests/golden/make_golden.py [/path/to/CxGNN-Compute]
+    python tests/golden/make_golden.py /path/to/CxGNN-Compute
 
 What can be executed of the reference without a GPU is its pure-torch / numpy code:
   cxgnncomp/schedule.py      neighbor_grouping{,_gpu}, partition_2d, reorder_by, remove_from_graph{,_by_edge}
@@ -28,7 +28,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python make_golden.py <path to a checkout of xxcclong/CxGNN-Compute>")
+REF = sys.argv[1]
 
 
 class _AnyStub(types.ModuleType):
