@@ -196,7 +196,7 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "needed"],
                     help="multi-GPU feature exchange: one padded all-gather, or an all-to-all of only the rows each "
                          "rank's edges name; auto takes the second when it moves under 80 %% of the rows")
-    ap.add_argument("--exchange-chunks", type=int, default=int(os.environ.get("CXG_BENCH_EXCHANGE_CHUNKS", "1")),
+    ap.add_argument("--exchange-chunks", type=int, default=int(os.environ.get("CXG_BENCH_EXCHANGE_CHUNKS", "4")),
                     help="needed-rows mode: cut every peer's rows into this many parts and send a part while the next "
                          "one is packed")
     ap.add_argument("--overlap", action="store_true",
