@@ -97,3 +97,53 @@ def test_two_rank_partition_exchange_aggregate(tmp_path):
     assert sum(nnz) == idx.shape[0]
     max_deg = int((ptr[1:] - ptr[:-1]).max())
     assert abs(nnz[0] - nnz[1]) <= 2 * max_deg  # balanced by edges up to one row
+
+
+def _worker4(rank, world, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "cxgnn-compute_b200"), os.path.join(ROOT, "tests")):
+        sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from cxgnncomp import synthetic
+    from cxgnncomp.distributed import NeededRowsExchange, RowPartition
+    ptr, idx = synthetic.powerlaw_graph(2000, 9000, seed=3)
+    x = synthetic.node_features(2000, 8, seed=3)
+    part = RowPartition(ptr, world)
+    r0, r1 = part.rows(rank)
+    lptr, gidx = part.local_graph(ptr, idx, rank, gather_ids=False)
+    ex = NeededRowsExchange(part, lptr, gidx, rank, 2000)
+    pack = lambda src, rows, out: torch.index_select(src, 0, rows, out=out)  # noqa: E731
+    bufs = []
+    for chunks in (1, 3):
+        buf = torch.zeros(ex.buffer_rows(), 8)
+        ex.own(buf).copy_(x[r0:r1])
+        ex.exchange(buf, pack=pack, chunks=chunks)
+        bufs.append(buf)
+    assert torch.equal(bufs[0], bufs[1])
+    assert torch.equal(bufs[0][ex.lidx.long()], x[gidx])
+    y = oracle.spmm(lptr, ex.lidx, bufs[0])
+    dy = synthetic.node_features(2000, 8, seed=4)[r0:r1]
+    dx = ex.exchange_backward(oracle.spmm_bwd_f64(lptr, ex.lidx, dy, (ex.buffer_rows(), 8))[0]).clone()
+    torch.save({"y": y, "dx": dx}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_four_rank_needed_rows_exchange(tmp_path):
+    """Four ranks: every rank sends to and receives from three peers, whole and in chunks; forward and backward
+    assemble to the single-process results."""
+    world = 4
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_worker4, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    sys.path.insert(0, os.path.join(ROOT, "cxgnn-compute_b200"))
+    import oracle
+    from cxgnncomp import synthetic
+    ptr, idx = synthetic.powerlaw_graph(2000, 9000, seed=3)
+    x = synthetic.node_features(2000, 8, seed=3)
+    dy = synthetic.node_features(2000, 8, seed=4)
+    parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
+    assert torch.equal(torch.cat([p["y"] for p in parts]), oracle.spmm(ptr, idx, x))
+    want = oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0]
+    assert float((torch.cat([p["dx"] for p in parts]) - want).abs().max()) < 1e-12
