@@ -196,9 +196,9 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "needed"],
                     help="multi-GPU feature exchange: one padded all-gather, or an all-to-all of only the rows each "
                          "rank's edges name; auto takes the second when it moves under 80 %% of the rows")
-    ap.add_argument("--exchange-chunks", type=int, default=int(os.environ.get("CXG_BENCH_EXCHANGE_CHUNKS", "4")),
+    ap.add_argument("--exchange-chunks", type=int, default=int(os.environ.get("CXG_BENCH_EXCHANGE_CHUNKS", "0")),
                     help="needed-rows mode: cut every peer's rows into this many parts and send a part while the next "
-                         "one is packed")
+                         "one is packed (0 = 4 parts on 2 GPUs, where it was measured; 1 part on more)")
     ap.add_argument("--overlap", action="store_true",
                     help="needed-rows mode: aggregate the own-source edges while the exchange is in flight (measured: "
                          "no gain, the persistent aggregation kernel fills every SM and the NCCL kernel waits for it)")
@@ -298,12 +298,14 @@ def main():
     b_alg_total = algorithmic_bytes(n, n, nnz, feat, elem, idx_bytes)
     b_alg_local = algorithmic_bytes(n_local, n, int(lptr[n_local]), feat, elem, idx_bytes)
 
+    exchange_chunks = args.exchange_chunks if args.exchange_chunks > 0 else (4 if world == 2 else 1)
+
     def exchange(buf=None):
         """The feature buffer (x_full by default) receives what this rank's aggregation reads: every shard (one
         NCCL all-gather) or the rows its edges name (pack + one NCCL all-to-all)."""
         buf = x_full if buf is None else buf
         if ex is not None:
-            ex.exchange(buf, send_buf, chunks=args.exchange_chunks)
+            ex.exchange(buf, send_buf, chunks=exchange_chunks)
         else:
             exchange_features(buf, part, rank)
 
@@ -459,7 +461,7 @@ def main():
                 "config": {"workload": args.workload, "description": desc, "nodes": n, "nnz": nnz, "feat": feat,
                            "idx_bytes": idx_bytes, "partition": f"rows by edge count over {world} GPU(s)",
                            "exchange": exchange_mode + (" + overlap with own-source edges" if overlap else "") +
-                           (f" in {args.exchange_chunks} chunks" if ex is not None and args.exchange_chunks > 1 else ""),
+                           (f" in {exchange_chunks} chunks" if ex is not None and exchange_chunks > 1 else ""),
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
                 "gpu_launches": int(launches), "roofline": roofline, "exchange": exchange_info, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
