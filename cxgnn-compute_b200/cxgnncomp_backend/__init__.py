@@ -212,37 +212,47 @@ def _spmm_forward(x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, out=N
 
 # dX = A^T dY is a forward aggregation over the transposed graph: deterministic and on the fast forward
 # kernel, where the scatter kernel adds with atomics in no fixed order (like the reference's backward,
-# aggr_kernel.cu:188-273). Transposing costs a sort of the edges, so it is done for a graph whose backward is
-# asked for the second time (full-graph training) and kept in a small cache; sampled batches, whose graphs are
-# seen once, stay on the scatter kernel. BACKWARD_MODE: "auto" | "scatter" | "transpose".
+# aggr_kernel.cu:188-273). The transposed graph is built on the device (cxg_csr_transpose: a stable radix sort
+# of the edges by source) the first time a backward is asked for a graph and kept in a small cache keyed by the
+# ptr / idx tensors. BACKWARD_MODE: "auto" (= "transpose" wherever it applies) | "scatter" | "transpose".
 BACKWARD_MODE = os.environ.get("CXG_BACKWARD_MODE", "auto")
 _TRANSPOSE_CACHE = {}
-_TRANSPOSE_SEEN = {}
-_TRANSPOSE_CACHE_MAX = 4
+_TRANSPOSE_CACHE_MAX = 8
+_transpose_ws = _sig("cxg_csr_transpose_workspace_size", [_i64, ctypes.POINTER(_sz)])
+_transpose = _sig("cxg_csr_transpose", [_vp, _vp, ctypes.c_int, ctypes.c_int, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
+                                        _vp, _sz, _vp])
+
+
+def csr_transpose(ptr, idx, num_node, num_src, want_eid=True):
+    """(t_ptr int64 [num_src + 1], t_idx, t_eid, inv_deg float [num_node]) of the first `num_node` rows of the CSR
+    graph (ptr, idx): row s of the transposed graph lists the destinations of source s in ascending order, t_eid
+    the forward edge of every transposed edge (what a stable sort of idx returns), inv_deg 1 / in-degree per
+    destination. t_idx / t_eid have the dtype and length of idx; entries past ptr[num_node] are not written."""
+    _cuda(ptr, "ptr", _INDEX_DTYPES)
+    _cuda(idx, "idx", _INDEX_DTYPES)
+    n = _num_rows(ptr, num_node)
+    nnz = idx.shape[0]
+    dev = ptr.device
+    t_ptr = torch.empty(num_src + 1, dtype=torch.int64, device=dev)
+    t_idx = torch.empty(nnz, dtype=idx.dtype, device=dev)
+    t_eid = torch.empty(nnz, dtype=idx.dtype, device=dev) if want_eid else None
+    inv_deg = torch.empty(n, dtype=torch.float32, device=dev)
+    need = _sz(0)
+    _check(_transpose_ws(nnz, ctypes.byref(need)), "cxg_csr_transpose_workspace_size")
+    ws = _workspace(dev, need.value)
+    with torch.cuda.device(dev):
+        _check(_transpose(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), n, int(num_src), nnz, _p(t_ptr),
+                          _p(t_idx), _p(t_eid), _p(inv_deg), _p(ws), ws.numel(), _stream()), "cxg_csr_transpose")
+    return t_ptr, t_idx, t_eid, inv_deg
 
 
 def _transposed_graph(ptr, idx, n, n_src):
-    """(t_ptr [n_src + 1], t_idx = destination of every transposed edge, t_eid = its edge id in the forward
-    graph, 1 / in-degree per destination) for the first n rows, or None while the graph has been seen once."""
+    """Cached csr_transpose of the first n rows."""
     key = (ptr.data_ptr(), idx.data_ptr(), n, n_src, ptr._version, idx._version, str(ptr.device))
     hit = _TRANSPOSE_CACHE.get(key)
     if hit is not None:
         return hit[:4]
-    if BACKWARD_MODE == "auto":
-        seen = _TRANSPOSE_SEEN.get(key, 0)
-        if len(_TRANSPOSE_SEEN) > 64:
-            _TRANSPOSE_SEEN.clear()
-        _TRANSPOSE_SEEN[key] = seen + 1
-        if seen == 0:
-            return None
-    deg = (ptr[1:n + 1] - ptr[:n]).long()
-    nnz = int(ptr[n])
-    dst = torch.repeat_interleave(torch.arange(n, device=ptr.device, dtype=idx.dtype), deg)
-    src = idx[:nnz]
-    order = torch.sort(src, stable=True).indices  # stable: destinations ascending within a source row
-    t_ptr = torch.zeros(n_src + 1, dtype=torch.int64, device=ptr.device)
-    torch.cumsum(torch.bincount(src, minlength=n_src), 0, out=t_ptr[1:])
-    entry = (t_ptr, dst[order].contiguous(), order, 1.0 / deg.clamp(min=1).float())
+    entry = csr_transpose(ptr, idx, n, n_src)
     while len(_TRANSPOSE_CACHE) >= _TRANSPOSE_CACHE_MAX:
         _TRANSPOSE_CACHE.pop(next(iter(_TRANSPOSE_CACHE)))
     # ptr and idx are kept alive with the entry, so their addresses cannot be handed to another graph
@@ -261,27 +271,27 @@ def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG
     if x_shape is None:
         x_shape = x.shape
     dx_t = None
-    # with edge-value gradients asked for, the scatter kernel yields dx and dval in one pass over the edges:
-    # "auto" keeps it; the transposed graph is used for the plain dx = A^T dy
-    if (need_dx and BACKWARD_MODE != "scatter" and not (need_dval and BACKWARD_MODE == "auto") and grad_x is None
-            and edge_mask is None and edge_rel is None and targets is None and n > 0):
-        tg = _transposed_graph(ptr, idx, n, x_shape[0])
-        if tg is not None:
-            t_ptr, t_idx, t_eid, inv_deg = tg
-            dy = grad_out
-            if reduce == CXG_MEAN:
-                dy = (grad_out.float() * inv_deg.view(-1, *([1] * (grad_out.dim() - 1)))).to(grad_out.dtype)
-            t_val = None
-            if edge_val is not None:  # the edge values in transposed order
-                ev = edge_val.contiguous()
-                t_val = torch.empty_like(ev)
-                with torch.cuda.device(ev.device):
-                    _check(_gather(_p(ev), _p(t_eid), t_eid.element_size(), _p(t_val), t_eid.shape[0],
-                                   ev.shape[1] if ev.dim() == 2 else 1, 1, _stream()), "cxg_gather_edges")
-            dx_t = _spmm_forward(dy, t_ptr, t_idx, x_shape[0], edge_val=t_val)
-            need_dx = False
-            if not need_dval:
-                return dx_t, None
+    # dx on the transposed graph (deterministic); the edge-value gradient, when asked for, is a second pass
+    # over the forward edges with a fixed order of its own
+    if (need_dx and BACKWARD_MODE != "scatter" and grad_x is None and edge_mask is None and edge_rel is None
+            and targets is None and n > 0 and idx.shape[0] > 0):
+        t_ptr, t_idx, t_eid, inv_deg = _transposed_graph(ptr, idx, n, x_shape[0])
+        dy = grad_out[:n]
+        if reduce == CXG_MEAN:
+            dy = (dy.float() * inv_deg.view(-1, *([1] * (grad_out.dim() - 1)))).to(grad_out.dtype)
+        t_val = None
+        if edge_val is not None:  # the edge values in transposed order
+            ev = edge_val.contiguous()
+            t_val = torch.empty_like(ev)
+            with torch.cuda.device(ev.device):
+                _check(_gather(_p(ev), _p(t_eid), t_eid.element_size(), _p(t_val), min(t_eid.shape[0], ev.shape[0]),
+                               ev.shape[1] if ev.dim() == 2 else 1, 1, _stream()), "cxg_gather_edges")
+        dx_t = _spmm_forward(dy.contiguous(), t_ptr, t_idx, x_shape[0], edge_val=t_val)
+        if dx_t.dtype != torch.float32:
+            dx_t = dx_t.float()
+        need_dx = False
+        if not need_dval:
+            return dx_t, None
     dx = None
     if need_dx:
         dx = grad_x if grad_x is not None else torch.zeros(x_shape, dtype=torch.float32, device=grad_out.device)

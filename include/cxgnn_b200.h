@@ -151,6 +151,24 @@ int cxg_spmm_csr_backward(const cxg_spmm_desc *desc, const void *dy, float *dx,
                           float *dval, void *stream);
 
 /*
+ * Transposed graph of a CSR_Layer graph, built on the device by a stable radix sort of the edges by
+ * source id (no atomics, same result on every run; equal to a stable sort of idx):
+ *   t_ptr [n_src + 1] int64    transposed row of source s = [t_ptr[s], t_ptr[s+1])
+ *   t_idx [nnz]  (idx width)   destination (forward row) of every transposed edge, ascending inside a row
+ *   t_eid [nnz]  (idx width)   forward edge id of every transposed edge (optional, may be NULL)
+ *   inv_deg [n_dst] float      1 / max(1, edges of forward row r) (optional, may be NULL)
+ * Only the first min(ptr[n_dst], nnz) edges are read. With it dX = A^T dY runs on cxg_spmm_csr over
+ * (t_ptr, t_idx) instead of the atomic scatter of the reference's backward kernels
+ * (src/cpp/src/aggr_kernel.cu:188-249); the reference has no transpose of its own: AggrOP.backward
+ * assumes a symmetric graph instead (cxgnncomp/graph_conv.py:57-77). nnz < 2^31, n_src < 2^32.
+ */
+int cxg_csr_transpose_workspace_size(int64_t nnz, size_t *bytes);
+int cxg_csr_transpose(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes,
+                      int64_t n_dst, int64_t n_src, int64_t nnz, int64_t *t_ptr, void *t_idx,
+                      void *t_eid, float *inv_deg, void *workspace, size_t workspace_bytes,
+                      void *stream);
+
+/*
  * Edge softmax of GAT. For every destination d and head h over the edges e of row d:
  *   t = att_dst[d,h] + att_src[idx[e],h];  t = max(t, t*slope)      (LeakyReLU)
  *   out[e,h] = exp(t - max_row t) / sum_row exp(t - max_row t);     mask[e,h] = t > 0

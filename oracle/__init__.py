@@ -255,6 +255,20 @@ def typed_linear_f64(a, w, rel, src=None):
 # ----------------------------------------------------------------------------------------
 # The reference's pure-torch formulations ("its CPU path"), restated.
 # ----------------------------------------------------------------------------------------
+def csr_transpose(ptr, idx, n_dst, n_src):
+    """(t_ptr, t_idx, t_eid) of the first n_dst rows: edges ordered by (source, forward edge id), i.e. a stable
+    sort of idx, which is what the reference's users build with torch.sort when they need the reverse graph
+    (the symmetric-graph shortcut of AggrOP.backward, cxgnncomp/graph_conv.py:57-77, avoids it)."""
+    ptr_n, idx_n = _np(ptr, np.int64), _np(idx, np.int64)
+    e = int(ptr_n[n_dst])
+    src = idx_n[:e]
+    order = np.argsort(src, kind="stable")
+    dst = np.repeat(np.arange(n_dst, dtype=np.int64), np.diff(ptr_n[:n_dst + 1]))
+    t_ptr = np.zeros(n_src + 1, dtype=np.int64)
+    np.cumsum(np.bincount(src, minlength=n_src), out=t_ptr[1:])
+    return torch.from_numpy(t_ptr), torch.from_numpy(dst[order]), torch.from_numpy(order.astype(np.int64))
+
+
 def dst_of_edges(ptr, n=None):
     n = ptr.shape[0] - 1 if n is None else n
     return torch.repeat_interleave(torch.arange(n, device=ptr.device), ptr[1:n + 1] - ptr[:n])
