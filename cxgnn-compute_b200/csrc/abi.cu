@@ -20,6 +20,13 @@ static long long g_launches = 0;
 
 void count_launches(int n) { __atomic_fetch_add(&g_launches, static_cast<long long>(n), __ATOMIC_RELAXED); }
 
+static long long g_wait_cycles = 0;  // 0 = default
+
+long long wait_limit_cycles() {
+  const long long v = __atomic_load_n(&g_wait_cycles, __ATOMIC_RELAXED);
+  return v > 0 ? v : (1ll << 31);  // ~1 s: a wait that long is a fault, not latency
+}
+
 int check_launch(const char *what) {
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return CXG_OK;
@@ -45,10 +52,18 @@ int read_status_word(const void *workspace, size_t word, void *stream, const cha
   cudaError_t e = cudaMemcpyAsync(&v, static_cast<const int32_t *>(workspace) + word, sizeof(v), cudaMemcpyDeviceToHost, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return cxg::set_error(CXG_ECUDA, "%s: %s", who, cudaGetErrorString(e));
+  if (v == 2)
+    return cxg::set_error(CXG_EINVAL, "%s: ptr[n_dst] exceeds the declared nnz; only the declared edges were read and the result is incomplete", who);
   if (v != 0) return cxg::set_error(CXG_ETIMEOUT, "%s: a bounded device-side wait ran out; the result is incomplete", who);
   return CXG_OK;
 }
 }  // namespace
+
+extern "C" int cxg_set_wait_limit_cycles(long long cycles) {
+  if (cycles < 0) return cxg::set_error(CXG_EINVAL, "cxg_set_wait_limit_cycles: %lld", cycles);
+  __atomic_store_n(&cxg::g_wait_cycles, cycles, __ATOMIC_RELAXED);
+  return CXG_OK;
+}
 
 extern "C" int cxg_spmm_csr_status(const void *workspace, void *stream) {
   return read_status_word(workspace, 63, stream, "cxg_spmm_csr_status");

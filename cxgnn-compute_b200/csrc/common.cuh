@@ -19,6 +19,8 @@ int set_error(int code, const char *fmt, ...);
 int check_launch(const char *what);
 // Adds n to the process-wide count of kernels this library has launched.
 void count_launches(int n);
+// Cycle limit of one bounded device-side wait (cxg_set_wait_limit_cycles; default about a second).
+long long wait_limit_cycles();
 
 #define CXG_REQUIRE(cond, code, ...)                   \
   do {                                                 \

@@ -561,9 +561,10 @@ extern "C" int cxg_spmm_csr(const cxg_spmm_desc *d, void *workspace, size_t work
   a.heavy_blocks = may_split ? kNumSM * kHeavyBlocksPerSM : 0;
 
   cudaStream_t st = as_stream(stream);
+  // the header (plan counters, error word 63 read by cxg_spmm_csr_status) starts from zero on every call
+  if (cudaMemsetAsync(a.hdr, 0, kHdrWords * sizeof(int32_t), st) != cudaSuccess)
+    return check_launch("cxg_spmm_csr: clearing the plan header");
   if (may_split) {
-    if (cudaMemsetAsync(a.hdr, 0, kHdrWords * sizeof(int32_t), st) != cudaSuccess)
-      return check_launch("cxg_spmm_csr: clearing the plan header");
     unsigned pb = static_cast<unsigned>((d->n_dst + kThreads - 1) / kThreads);
     spmm_plan_rows<<<pb, kThreads, 0, st>>>(a);
     spmm_plan_chunks<<<kNumSM, kThreads, 0, st>>>(a);

@@ -89,3 +89,10 @@ extern "C" int cxg_spmm_csr_static(const cxg_spmm_desc *d, void *stream) {
   if (rc != CXG_OK) return rc;
   return cxg_spmm_csr(d, scratch, kStaticScratchBytes, stream);
 }
+
+extern "C" int cxg_spmm_csr_static_status(void *stream) {
+  void *scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc != CXG_OK) return rc;
+  return cxg_spmm_csr_status(scratch, stream);
+}

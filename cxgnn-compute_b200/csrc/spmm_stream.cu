@@ -37,7 +37,6 @@ constexpr int kStageBytes = 8192;  // feature bytes per stage and warp
 constexpr int kCtasPerSM = 6;
 constexpr int kSeqPartials = 64;   // longer chains are added in 8 ordered blocks
 constexpr int kFar = 1 << 30;      // "no row end in sight" in tile-relative positions
-constexpr long long kWaitCycles = 1ll << 31;  // ~1 s: a wait that long is a fault, not latency
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -208,15 +207,24 @@ __device__ __forceinline__ int64_t row_of_edge(const void *ptr, int ptr_bytes, i
   return lo;
 }
 
+// Edges the kernels walk: ptr[n_dst], but never more than the caller declared (the workspace and the idx
+// array are only that large). A larger ptr[n_dst] is a caller error, recorded by the plan kernel.
+__device__ __forceinline__ int64_t stream_edge_total(const StreamArgs &a) {
+  const int64_t e = load_ptr(a.ptr, a.n_dst, a.ptr_bytes);
+  return e > a.nnz ? a.nnz : e;
+}
+
 __global__ void spmm_stream_plan(StreamArgs a) {
   int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (t == 0) {
     a.hdr[kSHdrNumLong] = 0;
-    a.hdr[kSHdrError] = 0;
+    a.hdr[kSHdrError] = load_ptr(a.ptr, a.n_dst, a.ptr_bytes) > a.nnz ? kSErrEdgeCount : kSErrNone;
   }
-  int64_t e_total = load_ptr(a.ptr, a.n_dst, a.ptr_bytes);
+  if (t >= a.max_tiles) return;
+  a.tail_row[t] = -1;  // no unfinished row unless the tile's walk says so
+  int64_t e_total = stream_edge_total(a);
   int64_t pos = t * a.tile;
-  if (t >= a.max_tiles || pos >= e_total) return;
+  if (pos >= e_total) return;
   a.tile_row[t] = row_of_edge(a.ptr, a.ptr_bytes, a.n_dst, pos);
 }
 
@@ -252,7 +260,7 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream(StreamArgs 
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const uint8_t *x = reinterpret_cast<const uint8_t *>(a.x);
   uint8_t *y = reinterpret_cast<uint8_t *>(a.y);
-  const int64_t e_total = load_ptr(a.ptr, a.n_dst, a.ptr_bytes);
+  const int64_t e_total = stream_edge_total(a);
   const int64_t n_tiles = (e_total + a.tile - 1) / a.tile;
   const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kSWarps + warp;
   const int64_t nwarps = static_cast<int64_t>(gridDim.x) * kSWarps;
@@ -371,7 +379,8 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream(StreamArgs 
         const uint32_t bar = smem_u32(bars + s);
         // order earlier generic-proxy reads of this slot before the async-proxy writes
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(cnt * row_bytes));
+        // (test hook: stage 0 of tile 0 announces 16 bytes that no copy delivers, so its wait must run out)
+        if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(cnt * row_bytes) + ((a.test_stall && t == 0 && k == 0) ? 16u : 0u));
         __syncwarp();
         if (lane < cnt) bulk_g2s(dst0 + lane * row_bytes, x + nid * row_bytes, row_bytes, bar);
       } else {
@@ -441,14 +450,17 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream(StreamArgs 
         if (!mbar_try_wait(bar, parity)) {
           const long long t0 = clock64();
           while (!mbar_try_wait(bar, parity)) {
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > a.wait_cycles) {
               dead = true;
               break;
             }
           }
         }
         if (dead) {
-          if (lane == 0) atomicExch(a.hdr + kSHdrError, 1);
+          // Nothing else of this warp is in flight: one stage per warp, and the copies of that stage are what
+          // the wait was for. The tile's tail_row keeps the -1 of the plan kernel and the fix-up kernels do
+          // nothing once the error word is set.
+          if (lane == 0) atomicExch(a.hdr + kSHdrError, kSErrTimeout);
           break;
         }
         phases ^= 1u << s;
@@ -588,15 +600,16 @@ __device__ __forceinline__ void finish_row(const StreamArgs &a, PVec<VW> &s, T *
 template <typename T, int VW>
 __global__ void __launch_bounds__(256) spmm_stream_fix(StreamArgs a) {
   const int lane = threadIdx.x & 31;
-  const int64_t e_total = load_ptr(a.ptr, a.n_dst, a.ptr_bytes);
+  if (a.hdr[kSHdrError] != kSErrNone) return;  // the walk did not finish: the partials are not all there
+  const int64_t e_total = stream_edge_total(a);
   const int64_t n_tiles = (e_total + a.tile - 1) / a.tile;
   const int64_t gwarp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   T *y = reinterpret_cast<T *>(a.y);
   for (int64_t t = gwarp; t < n_tiles; t += nwarps) {
     const int64_t r = a.tail_row[t];
-    if (r < 0) continue;
-    const int64_t rb = load_ptr(a.ptr, r, a.ptr_bytes), re = load_ptr(a.ptr, r + 1, a.ptr_bytes);
+    if (r < 0 || r >= a.n_dst) continue;
+    const int64_t rb = load_ptr(a.ptr, r, a.ptr_bytes), re = min(load_ptr(a.ptr, r + 1, a.ptr_bytes), e_total);
     const int64_t t_last = (re - 1) / a.tile;
     const int64_t m = t_last - t + 1;  // partials in the chain
     if (m > kSeqPartials) {
@@ -626,12 +639,15 @@ template <typename T, int VW>
 __global__ void __launch_bounds__(256) spmm_stream_fix_long(StreamArgs a) {
   __shared__ float stage[8][32 * VW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (a.hdr[kSHdrError] != kSErrNone) return;
+  const int64_t e_total = stream_edge_total(a);
   const int n_long = min(a.hdr[kSHdrNumLong], a.max_long);
   T *y = reinterpret_cast<T *>(a.y);
   for (int i = blockIdx.x; i < n_long; i += gridDim.x) {
     const int64_t t = a.long_tiles[i];
     const int64_t r = a.tail_row[t];
-    const int64_t rb = load_ptr(a.ptr, r, a.ptr_bytes), re = load_ptr(a.ptr, r + 1, a.ptr_bytes);
+    if (r < 0 || r >= a.n_dst) continue;  // uniform over the CTA
+    const int64_t rb = load_ptr(a.ptr, r, a.ptr_bytes), re = min(load_ptr(a.ptr, r + 1, a.ptr_bytes), e_total);
     const int64_t m = (re - 1) / a.tile - t + 1;
     const int64_t kb = m * warp / 8, ke = m * (warp + 1) / 8;
     const int64_t out = a.targets != nullptr ? a.targets[r] : r;
@@ -761,7 +777,9 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
   StreamArgs a;
   a.ptr = d->ptr, a.idx = d->idx, a.x = d->x, a.y = d->y;
   a.edge_val = d->edge_val, a.edge_rel = d->edge_rel, a.targets = d->targets;
-  a.n_dst = d->n_dst, a.rel_stride = d->rel_stride;
+  a.n_dst = d->n_dst, a.nnz = d->nnz, a.rel_stride = d->rel_stride;
+  a.wait_cycles = wait_limit_cycles();
+  a.test_stall = (d->flags & CXG_SPMM_TEST_STALL) ? 1 : 0;
   a.feat = d->feat, a.heads = d->heads, a.width = d->feat * d->heads;
   a.ptr_bytes = d->ptr_bytes, a.reduce = d->reduce;
   a.accumulate = (d->flags & CXG_SPMM_ACCUMULATE) ? 1 : 0;

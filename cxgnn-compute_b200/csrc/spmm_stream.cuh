@@ -6,6 +6,8 @@ namespace cxg {
 
 // Header words of the streaming workspace.
 enum { kSHdrNumLong = 0, kSHdrError = 63 };  // word 63 is the error word of every SpMM workspace header
+// Values of the error word.
+enum { kSErrNone = 0, kSErrTimeout = 1, kSErrEdgeCount = 2 };
 // Row fetch variants: 16-byte async copies into shared memory (default), one bulk
 // async copy per row into shared memory.
 enum { kModeCpAsync = 0, kModeBulk = 1 };
@@ -19,8 +21,11 @@ struct StreamArgs {
   const int32_t *edge_rel;
   const int64_t *targets;
   int64_t n_dst;
+  int64_t nnz;  // edges the caller declared: the workspace is sized for them, no kernel goes beyond
   int64_t rel_stride;
   int64_t max_tiles;
+  long long wait_cycles;  // limit of one mbarrier wait (bulk-copy variant)
+  int test_stall;         // test hook: the first stage of tile 0 announces bytes that never arrive
   int width, feat, heads, ptr_bytes, reduce, accumulate;
   int tile;         // edges per tile
   int stage_edges;  // edges per ring stage
@@ -49,5 +54,6 @@ bool stream_eligible(const cxg_spmm_desc *d);
 int stream_tile_edges(const cxg_spmm_desc *d);
 int stream_layout(int64_t nnz, int64_t width, int tile, StreamLayout *L);
 int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_bytes, cudaStream_t st);
+
 
 }  // namespace cxg

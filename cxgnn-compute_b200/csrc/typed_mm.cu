@@ -46,7 +46,6 @@ constexpr int kMmaWarp = kEpiWarps;                              // warp 4
 constexpr int kMaxStages = 6;
 constexpr int kRpi = 8, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction
 constexpr int kSmemBudget = 226 * 1024;
-constexpr long long kWaitCycles = 1ll << 31;
 
 struct TmmArgs {
   const void *a;
@@ -60,6 +59,8 @@ struct TmmArgs {
   int atomic;  // add the rows into a float32 C with vector reductions instead of storing them
   int tmem_cols;  // columns of ONE accumulator buffer (two are allocated)
   int stages;     // shared-memory stages of A
+  int test_stall;  // test hook: the producers never hand over the first tile, so the waits for it run out
+  long long wait_cycles;  // limit of one barrier wait
   int32_t *status;  // [0] error flag
 };
 
@@ -134,13 +135,14 @@ struct Barriers {
 };
 
 // Bounded wait on phase `parity`; false after a time-out here or an abort raised by another role.
-__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status) {
+__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
+                                         long long limit) {
   const uint32_t b = smem_addr(bar);
   if (mbar_try_wait(b, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(b, parity)) {
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       atomicExch(status, 1);
       return false;
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
       if (r != loaded_rel) {
         // every MMA issued so far reads the old W: let them finish
         for (int64_t j = (it > S ? it - S : 0); j < it && alive; ++j)
-          alive = wait_bar(&bars.empty[j % S], static_cast<uint32_t>((j / S) & 1), abort_flag, a.status);
+          alive = wait_bar(&bars.empty[j % S], static_cast<uint32_t>((j / S) & 1), abort_flag, a.status, a.wait_cycles);
         if (!alive) break;
         const T *wr = Wt + r * static_cast<int64_t>(a.n) * a.k;
         const uint32_t b0 = smem_addr(smem_b);
@@ -259,7 +261,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
       }
       const int s = static_cast<int>(it % S);
       if (it >= S) {
-        alive = wait_bar(&bars.empty[s], static_cast<uint32_t>(((it / S) - 1) & 1), abort_flag, a.status);
+        alive = wait_bar(&bars.empty[s], static_cast<uint32_t>(((it / S) - 1) & 1), abort_flag, a.status, a.wait_cycles);
         if (!alive) break;
       }
       const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
@@ -274,7 +276,8 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
       }
       // the tile's full barrier counts this thread's arrival when all copies it has issued so far (this tile's
       // rows, and W when it was re-copied) have landed: the producer never waits for its own copies
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&bars.full[s])) : "memory");
+      if (!(a.test_stall && it == 0))
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&bars.full[s])) : "memory");
       ++it;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -292,9 +295,9 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
         r_next = tile + 1 < tile_hi ? a.rel[(tile + 1) * kTileM] : -1;
         if (r < 0 || r >= a.num_rel) continue;
         const int s = static_cast<int>(it % S), buf = static_cast<int>(it & 1);
-        alive = wait_bar(&bars.full[s], static_cast<uint32_t>((it / S) & 1), abort_flag, a.status);
+        alive = wait_bar(&bars.full[s], static_cast<uint32_t>((it / S) & 1), abort_flag, a.status, a.wait_cycles);
         if (alive && it >= 2)
-          alive = wait_bar(&bars.acc_empty[buf], static_cast<uint32_t>(((it >> 1) - 1) & 1), abort_flag, a.status);
+          alive = wait_bar(&bars.acc_empty[buf], static_cast<uint32_t>(((it >> 1) - 1) & 1), abort_flag, a.status, a.wait_cycles);
         if (!alive) break;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -338,7 +341,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
       int64_t oc = -1;
       if (sv >= 0 && sv < a.m_valid) oc = dv != -2 ? dv : (a.out_follows_src ? sv : tile * kTileM + warp * 32 + lane);
       const int buf = static_cast<int>(it & 1);
-      alive = wait_bar(&bars.acc_full[buf], static_cast<uint32_t>((it >> 1) & 1), abort_flag, a.status);
+      alive = wait_bar(&bars.acc_full[buf], static_cast<uint32_t>((it >> 1) & 1), abort_flag, a.status, a.wait_cycles);
       if (!alive) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + buf * a.tmem_cols;
@@ -471,6 +474,8 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   t.a = a, t.c = c, t.rel = rel, t.src = src_idx, t.dst = dst_idx;
   t.m = m, t.m_valid = m_valid, t.k = k, t.n = n, t.num_rel = num_rel, t.out_follows_src = follows;
   t.atomic = atomic;
+  t.test_stall = (flags & CXG_TMM_TEST_STALL) ? 1 : 0;
+  t.wait_cycles = wait_limit_cycles();
   t.status = reinterpret_cast<int32_t *>(workspace);
   void *wt = reinterpret_cast<char *>(workspace) + 256;
   t.wt = wt;

@@ -16,10 +16,21 @@ own edges name. Requests are exchanged once per graph; every step the owners pac
 variable-size all-to-all delivers them into a compact local buffer, into whose numbering the column ids were
 renumbered. It moves (rows needed from other ranks) x F instead of (world - 1) / world x N x F per rank.
 """
+import os
+
+import numpy as np
 import torch
 import torch.distributed as dist
 
 from .partition import local_rows, row_partition_by_nnz
+
+
+def _dump(directory, name, t):
+    t.detach().cpu().contiguous().numpy().tofile(os.path.join(directory, name + ".dat"))
+
+
+def _read(directory, name, dtype=np.int64):
+    return torch.from_numpy(np.fromfile(os.path.join(directory, name + ".dat"), dtype=dtype))
 
 
 class RowPartition:
@@ -33,6 +44,19 @@ class RowPartition:
 
     def rows(self, rank):
         return self.bounds[rank], self.bounds[rank + 1]
+
+    def tofile(self, directory):
+        """bounds.dat: world + 1 int64 row bounds, raw like the reference's partition cache (cxgnncomp/batch.py:38-47)."""
+        os.makedirs(directory, exist_ok=True)
+        _dump(directory, "bounds", torch.tensor(self.bounds, dtype=torch.int64))
+
+    @classmethod
+    def fromfile(cls, directory):
+        self = cls.__new__(cls)
+        self.bounds = _read(directory, "bounds").tolist()
+        self.world = len(self.bounds) - 1
+        self.shard_rows = max(self.bounds[r + 1] - self.bounds[r] for r in range(self.world))
+        return self
 
     def gather_rows(self):
         """Rows of the gather buffer: world * shard_rows."""
@@ -128,6 +152,35 @@ class NeededRowsExchange:
         self.send_counts = counts_in.tolist()
         self.send_rows = torch.empty(sum(self.send_counts), dtype=torch.int64, device=dev)
         dist.all_to_all_single(self.send_rows, want_local, self.send_counts, self.recv_counts, group=group)
+
+    def tofile(self, directory):
+        """The plan of this rank as raw int64 arrays (remote.dat, send_rows.dat, lidx.dat, counts.dat = receive
+        counts then send counts, meta.dat = [world, rank, n_own, bytes per lidx entry]), so that a later run skips
+        the request exchange; same raw format as the reference's partition cache (cxgnncomp/batch.py:38-47)."""
+        os.makedirs(directory, exist_ok=True)
+        _dump(directory, "remote", self.remote)
+        _dump(directory, "send_rows", self.send_rows)
+        _dump(directory, "lidx", self.lidx.long())
+        _dump(directory, "counts", torch.tensor(self.recv_counts + self.send_counts, dtype=torch.int64))
+        _dump(directory, "meta", torch.tensor([self.part.world, self.rank, self.n_own, self.lidx.element_size()],
+                                              dtype=torch.int64))
+
+    @classmethod
+    def fromfile(cls, directory, part, rank, device, group=None):
+        """Rebuilds the plan written by `tofile`; no collective is needed. Raises when the cache was written for
+        another partition or rank."""
+        world, rank_f, n_own, isz = _read(directory, "meta").tolist()
+        r0, r1 = part.rows(rank)
+        if world != part.world or rank_f != rank or n_own != r1 - r0:
+            raise RuntimeError(f"{directory}: cache is for world {world} rank {rank_f} ({n_own} rows)")
+        self = cls.__new__(cls)
+        self.part, self.rank, self.group, self.n_own = part, rank, group, n_own
+        self.remote = _read(directory, "remote").to(device)
+        self.send_rows = _read(directory, "send_rows").to(device)
+        self.lidx = _read(directory, "lidx").to(torch.int32 if isz == 4 else torch.int64).to(device)
+        counts = _read(directory, "counts").tolist()
+        self.recv_counts, self.send_counts = counts[:world], counts[world:]
+        return self
 
     def buffer_rows(self):
         """Rows of the local feature buffer: own shard + remote rows."""

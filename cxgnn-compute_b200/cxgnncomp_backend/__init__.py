@@ -105,16 +105,23 @@ _workspaces = {}
 SPLIT_EDGES = 0
 # OR-ed into cxg_spmm_desc.flags; CXG_SPMM_BULK_ROWS (4) selects the bulk-copy (TMA) row fetch.
 CXG_SPMM_BULK_ROWS = 4
+CXG_SPMM_TEST_STALL = 8  # test hook, see include/cxgnn_b200.h
+CXG_TMM_TEST_STALL = 4
 EXTRA_SPMM_FLAGS = int(os.environ.get("CXG_SPMM_FLAGS", "0"))
 
 
-def _workspace(device, nbytes):
-    """Scratch buffer per (device, stream); grows on demand, contents never carry over."""
+_last_kind = {}
+
+
+def _workspace(device, nbytes, kind=None):
+    """Scratch buffer per (device, stream); grows on demand, contents never carry over. `kind` names the entry
+    point family that uses it now (its status word is the one check_device_status can answer for)."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
+    _last_kind[key] = kind
     return buf
 
 
@@ -163,23 +170,35 @@ _tmm_status = _sig("cxg_typed_matmul_status", [_vp, _vp])
 
 
 def check_device_status(kind="spmm", device=None):
-    """Synchronises the current stream and raises if a bounded device-side wait of the LAST call of that kind
-    ("spmm" or "typed_matmul") on this stream ran out (the kernels give up after about a second instead of
-    spinning forever). The calls of one stream share a scratch buffer, so ask right after the call in question."""
+    """Synchronises the current stream and raises if the LAST call on this stream was of that kind ("spmm" or
+    "typed_matmul") and a bounded device-side wait of it ran out (the kernels give up after a cycle limit instead
+    of spinning forever) or, for "spmm", ptr[num_node] exceeded the length of idx. The calls of one stream share
+    a scratch buffer, so only the last call can be asked about; for any other kind nothing is checked."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    ws = _workspaces.get((device.index, torch.cuda.current_stream(device).cuda_stream))
-    if ws is None:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or _last_kind.get(key) != kind:
         return
     fn, name = (_spmm_status, "cxg_spmm_csr_status") if kind == "spmm" else (_tmm_status, "cxg_typed_matmul_status")
     with torch.cuda.device(device):
         _check(fn(_p(ws), _stream()), name)
 
 
+_set_wait = _lib.cxg_set_wait_limit_cycles
+_set_wait.argtypes = [ctypes.c_longlong]
+_set_wait.restype = ctypes.c_int
+
+
+def set_wait_limit_cycles(cycles):
+    """Cycle limit of one bounded device-side wait for the launches that follow (0 = default, about a second)."""
+    _check(_set_wait(int(cycles)), "cxg_set_wait_limit_cycles")
+
+
 def _run_spmm(desc, device):
     need = _sz(0)
     _check(_spmm_ws(desc.n_dst, desc.nnz, desc.feat, desc.heads, desc.split_edges, ctypes.byref(need)),
            "cxg_spmm_csr_workspace_size")
-    ws = _workspace(device, need.value)
+    ws = _workspace(device, need.value, "spmm")
     with torch.cuda.device(device):
         _check(_spmm_fwd(ctypes.byref(desc), _p(ws), ws.numel(), _stream()), "cxg_spmm_csr")
 

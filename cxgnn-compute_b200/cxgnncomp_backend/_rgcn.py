@@ -173,7 +173,7 @@ def aggr_rel_direct(x, ptr, idx, weights, etype, num_node, num_rel):
 
 
 def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None, seq_output=False, exact=False,
-                     out_rows=None, atomic_out=None):
+                     out_rows=None, atomic_out=None, extra_flags=0):
     """C = typed matmul through the C ABI. a [*, K], b [R, K, N], rel int64 per position; see cxg_typed_matmul.
     C has `out_rows` rows (default: m_positions for sequential output, else m_valid). With `atomic_out` (a
     float32 [*, N] tensor) the rows are ADDED into it with vector atomics instead (rows may repeat)."""
@@ -187,7 +187,7 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
     num_rel, k, n = b.shape
     if a.shape[1] != k:
         raise RuntimeError("incompatible dimensions")
-    flags = 1 if seq_output else 0
+    flags = (1 if seq_output else 0) | int(extra_flags)
     if atomic_out is not None:
         _cuda(atomic_out, "atomic_out", (torch.float32,))
         if atomic_out.shape[1] != n:
@@ -202,7 +202,7 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
     dtype = CXG_F32 if a.dtype == torch.float32 else CXG_BF16
     need = _sz(0)
     _check(_tmm_ws(num_rel, k, n, dtype, ctypes.byref(need)), "cxg_typed_matmul_workspace_size")
-    ws = _workspace(a.device, need.value)
+    ws = _workspace(a.device, need.value, "typed_matmul")
     with torch.cuda.device(a.device):
         _check(_tmm(_p(a), _p(b), _p(c), _p(rel), _p(src_idx), _p(dst_idx), int(m_positions), int(m_valid), k, n, num_rel,
                     dtype, 0 if exact else 1, flags, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")

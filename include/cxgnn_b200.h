@@ -51,6 +51,11 @@ extern "C" {
    bit-identical. Default: 16-byte async copies into shared memory. */
 #define CXG_SPMM_BULK_ROWS 4u /* one bulk async copy (TMA) per row into shared
                                  memory, completion on an mbarrier             */
+/* Test hook of the bulk-copy variant: the first stage of the first tile announces 16 bytes
+   that no copy delivers, so that its bounded wait runs out and the time-out path (status
+   CXG_ETIMEOUT, kernels return, nothing written out of bounds) can be exercised. Use it
+   with a short cxg_set_wait_limit_cycles. */
+#define CXG_SPMM_TEST_STALL 8u
 
 const char *cxg_last_error_string(void);
 int cxg_abi_version(void);
@@ -101,11 +106,14 @@ typedef struct cxg_spmm_desc {
 
 /*
  * The kernels never spin without a limit: a wait on an mbarrier (the bulk-copy variant of cxg_spmm_csr,
- * the pipeline of cxg_typed_matmul) gives up after about a second, records that in the call's workspace
- * and returns. These two read the record: they WAIT for everything queued on `stream`, then return CXG_OK
- * or CXG_ETIMEOUT (the result of the call that used `workspace` last is then incomplete). Optional: nothing
- * else in the library synchronises.
+ * the pipeline of cxg_typed_matmul) gives up after a cycle limit (default 2^31 cycles, about a second;
+ * cxg_set_wait_limit_cycles changes it for the launches that follow, 0 restores the default), records that
+ * in the call's workspace and returns. These two read the record: they WAIT for everything queued on
+ * `stream`, then return CXG_OK, CXG_ETIMEOUT (a wait ran out) or, for cxg_spmm_csr, CXG_EINVAL (ptr[n_dst]
+ * was larger than desc->nnz: the kernels read only the declared edges); in both failure cases the result of
+ * the call that used `workspace` last is incomplete. Optional: nothing else in the library synchronises.
  */
+int cxg_set_wait_limit_cycles(long long cycles);
 int cxg_spmm_csr_status(const void *workspace, void *stream);
 int cxg_typed_matmul_status(const void *workspace, void *stream);
 
@@ -373,6 +381,10 @@ int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
  */
 #define CXG_TMM_SEQ_OUTPUT 1
 #define CXG_TMM_ATOMIC_F32 2
+/* Test hook: the first tile of every CTA is never handed to the tensor-core role, so the bounded
+   waits for it run out (status CXG_ETIMEOUT, all roles leave, tensor memory is released). Use it
+   with a short cxg_set_wait_limit_cycles. */
+#define CXG_TMM_TEST_STALL 4
 int cxg_typed_matmul_workspace_size(int num_rel, int k, int n, int dtype, size_t *bytes);
 int cxg_typed_matmul(const void *a, const void *w, void *c, const int64_t *rel,
                      const int64_t *src_idx, const int64_t *dst_idx, int64_t m,
@@ -396,13 +408,16 @@ int cxg_typed_matmul(const void *a, const void *w, void *c, const int64_t *rel,
  *   - All calls share the array. Its previous contents do not matter, but calls
  *     that overlap on the GPU (other streams, other host threads) corrupt each
  *     other: order them on the device.
- *   - The first call on each device looks the array's device address up
+ *   - The array used is the one of the CURRENT device (cudaGetDevice at the time of the call); `stream`
+ *     must belong to that device. The first call on each device looks the array's device address up
  *     (cudaGetSymbolAddress).
  *   - It never calls cudaMalloc, cudaFree or any other allocating routine.
- * Results are those of cxg_spmm_csr, bit for bit.
+ * Results are those of cxg_spmm_csr, bit for bit. cxg_spmm_csr_static_status is cxg_spmm_csr_status for
+ * the built-in array of the current device (the caller never sees its address).
  */
 #define CXG_SPMM_STATIC_SCRATCH_BYTES (32u << 20)
 int cxg_spmm_csr_static(const cxg_spmm_desc *desc, void *stream);
+int cxg_spmm_csr_static_status(void *stream);
 
 #ifdef __cplusplus
 }

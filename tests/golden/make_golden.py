@@ -10,6 +10,8 @@ What can be executed of the reference without a GPU is its pure-torch / numpy co
   cxgnncomp/codegen/rgcn_kernel.py  rgcn_scatter                    (gather -> mm -> index_add_)
   cxgnncomp/typed_linear.py  TypedLinearS2DSort, TypedLinearNaiveS2D
   cxgnncomp/graph_conv.py    MyGATConv.edge_softmax_opwise, MyGCNConv.gcn_norm, RGCNOP_sorted
+  cxgnncomp/typed_linear.py  SelectMMS2EOP
+  cxgnncomp/batch.py         Batch.tofile / fromfile (the raw .dat files of the partition cache)
 The modules are imported from the reference tree as they are. Packages they import but that
 are not installed here (the CUDA extension `cxgnncomp_backend`, torch_geometric, torch_scatter,
 dgl, cxgnndl) are replaced by stubs; of those only torch_scatter's `segment_csr` / `gather_csr`
@@ -194,6 +196,27 @@ def main():
         srel, order = torch.sort(rel, stable=True)
         cnt = torch.bincount(rel, minlength=R)
         out["rgcn_sorted"] = graph_conv.RGCNOP_sorted(x, w, idx[order], dst[order], cnt.tolist(), 64)
+
+        for i, o in enumerate(typed_linear.SelectMMS2EOP(x, w, idx, rel)):
+            out[f"rgcn_select_{i}"] = o
+
+    # ---- batch.py: the .dat wire format, bytes written by the reference's own Batch.tofile -----------------
+    import tempfile
+    batch_mod = importlib.import_module("cxgnncomp.batch")
+    ptr_b, idx_b = small_graph(30, 4, seed=6, hub=False)
+    gb = torch.Generator().manual_seed(7)
+    x_b = torch.randn(30, 12, generator=gb)
+    target_b = torch.randperm(50, generator=gb)[:30]
+    out["batch_x"], out["batch_ptr"], out["batch_idx"], out["batch_target"] = x_b, ptr_b, idx_b, target_b
+    with tempfile.TemporaryDirectory() as tmp:
+        batch_mod.Batch(x_b, ptr_b, idx_b, target=target_b).tofile(tmp)
+        for name in ("x", "ptr", "idx", "target"):
+            out[f"batch_{name}_dat"] = np.fromfile(os.path.join(tmp, name + ".dat"), dtype=np.uint8)
+        back = batch_mod.Batch(None, None, None)
+        back.fromfile(tmp)
+        assert torch.equal(back.x, x_b.reshape(-1)) and torch.equal(back.ptr, ptr_b) and torch.equal(back.target, target_b)
+        # a sub-graph without features, as the partition cache stores them (test_mgpu_model.py:546-554)
+        batch_mod.Batch(x=None, ptr=ptr_b, idx=idx_b, target=target_b).tofile(tmp + "/")
 
     arrays = {k: (v.numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in out.items()}
     np.savez_compressed(os.path.join(HERE, "reference_cpu.npz"), **arrays)

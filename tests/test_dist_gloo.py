@@ -56,6 +56,16 @@ def _worker(rank, world, port, out_dir):
     assert 0 < ex.remote_rows() <= 3000 - (r1 - r0)
     y_need = oracle.spmm(lptr, ex.lidx, x_buf)
     assert torch.equal(y_need, y_local)
+    # the plan survives a trip through the on-disk cache and needs no collective to come back
+    ex.tofile(os.path.join(out_dir, f"needed_{rank}"))
+    ex2 = NeededRowsExchange.fromfile(os.path.join(out_dir, f"needed_{rank}"), part, rank, torch.device("cpu"))
+    assert torch.equal(ex2.remote, ex.remote) and torch.equal(ex2.send_rows, ex.send_rows)
+    assert torch.equal(ex2.lidx, ex.lidx) and ex2.lidx.dtype == ex.lidx.dtype
+    assert ex2.recv_counts == ex.recv_counts and ex2.send_counts == ex.send_counts and ex2.n_own == ex.n_own
+    x_buf3 = torch.zeros_like(x_buf)
+    ex2.own(x_buf3).copy_(x[r0:r1])
+    ex2.exchange(x_buf3, pack=lambda src, rows, out: torch.index_select(src, 0, rows, out=out))
+    assert torch.equal(x_buf3, x_buf)
     # the two-phase form: own-source edges (no exchange needed) + remote-source edges
     (p_own, i_own), (p_rem, i_rem) = ex.split_graph(lptr)
     assert int(p_own[-1]) + int(p_rem[-1]) == int(lptr[-1]) and torch.equal(p_own + p_rem, lptr)
