@@ -26,9 +26,21 @@
 //     atomically add) the rows of C at their scattered destinations while the next tile's MMAs
 //     run into the other buffer.
 //
+// fp32 inputs have two tensor-core modes. Plain TF32 (precision 1) feeds the fp32 words to `kind::tf32` as they
+// are, like the reference's tl.dot: products carry 10 mantissa bits (about 6e-4 relative on these shapes). The
+// error-compensated mode (precision 2, "3xTF32") splits every operand into hi = tf32(v) and lo = tf32(v - hi) and
+// accumulates A_hi.W_lo + A_lo.W_hi + A_hi.W_hi into the same tensor-memory accumulator, which restores fp32
+// accuracy (about 1e-6) while the tensor pipe, idle most of the time on this memory-bound op, absorbs the two
+// extra instructions. W is split once by the transposing pre-pass; a tile of A is split in shared memory by
+// four converter warps between the producers and the MMA thread (raw -> hi in place, lo into the second half of
+// the stage). To keep several stages in flight with stages twice as large, the K dimension is cut into blocks:
+// the pipeline unit is (tile, K-block) and all blocks of a tile accumulate into one accumulator buffer.
+//
 // Every wait is bounded: a role that waits longer than about a second raises a CTA-wide abort
 // flag and an error status; all roles then leave their loops, the copies in flight are waited
 // for, the tensor memory is released and the kernel returns.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace cxg {
@@ -42,6 +54,7 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kEpiWarps = 4;
 constexpr int kMaxProdWarps = 8;  // producer warps: 8 for 4-byte elements, 4 for 2-byte ones (measured)
+constexpr int kConvWarps = 4;     // converter warps of the error-compensated fp32 mode
 constexpr int kMmaWarp = kEpiWarps;                              // warp 4
 constexpr int kMaxStages = 6;
 constexpr int kRpi = 8, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction
@@ -59,6 +72,7 @@ struct TmmArgs {
   int atomic;  // add the rows into a float32 C with vector reductions instead of storing them
   int tmem_cols;  // columns of ONE accumulator buffer (two are allocated)
   int stages;     // shared-memory stages of A
+  int kb;         // K-block: columns of A per pipeline unit (= k unless the stage would not fit several times)
   int test_stall;  // test hook: the producers never hand over the first tile, so the waits for it run out
   long long wait_cycles;  // limit of one barrier wait
   int32_t *status;  // [0] error flag
@@ -114,21 +128,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// W [R][K][N] -> Wt [R][N][K]
+__device__ __forceinline__ float to_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+__device__ __forceinline__ float trunc_tf32(float v) { return __uint_as_float(__float_as_uint(v) & 0xffffe000u); }
+
+// W [R][K][N] -> Wt [R][N][K]; with `wt_lo` (fp32 only) the two TF32 terms hi = tf32(w), lo = tf32(w - hi).
 template <typename T>
-__global__ void transpose_w(const T *w, T *wt, int num_rel, int k, int n) {
+__global__ void transpose_w(const T *w, T *wt, T *wt_lo, int num_rel, int k, int n) {
   const int64_t total = static_cast<int64_t>(num_rel) * k * n;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / (static_cast<int64_t>(k) * n);
     const int rem = static_cast<int>(i - r * k * n);
     const int nn = rem / k, kk = rem - nn * k;
-    wt[i] = w[(r * k + kk) * n + nn];
+    const T v = w[(r * k + kk) * n + nn];
+    if constexpr (sizeof(T) == 4) {
+      if (wt_lo != nullptr) {
+        const float hi = to_tf32(v);
+        wt[i] = hi;
+        wt_lo[i] = to_tf32(v - hi);
+        continue;
+      }
+    }
+    wt[i] = v;
   }
 }
 
 struct Barriers {
-  uint64_t full[kMaxStages];   // producers -> MMA: the stage holds a tile (one arrival per producer thread)
+  uint64_t full[kMaxStages];   // producers -> MMA (or -> converters): the stage holds a unit (one arrival per producer thread)
+  uint64_t conv[kMaxStages];   // converters -> MMA: hi / lo halves of the stage are written (128 arrivals)
   uint64_t empty[kMaxStages];  // MMA -> producers: the MMAs that read the stage are done (1 commit)
   uint64_t acc_full[2];        // MMA -> epilogue (1 commit)
   uint64_t acc_empty[2];       // epilogue -> MMA (128 arrivals)
@@ -169,27 +201,35 @@ __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// PW producer warps; each copies 128 / PW rows of a tile, kSlots of them per thread.
-template <typename T, bool CA, int PW>
-__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmArgs a) {
+// PW producer warps; each copies 128 / PW rows of a tile, kSlots of them per thread. X3: error-compensated
+// fp32 (three TF32 products per term), with kConvWarps converter warps behind the producers.
+template <typename T, bool CA, int PW, bool X3>
+__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 0)), 1) typed_mm_tc(TmmArgs a) {
   constexpr int kProdWarps = PW;
   constexpr int kRowsPerProdWarp = kTileM / kProdWarps;
   constexpr int kSlots = kRowsPerProdWarp / kRpi;
   constexpr bool TF32 = sizeof(T) == 4;
   constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
+  constexpr int kFirstConvWarp = kMmaWarp + 1 + PW;
+  static_assert(!X3 || TF32, "the error-compensated mode is for fp32 inputs");
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) Barriers bars;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_slot;
   volatile int *abort_flag = &abort_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int chunks = a.k / EPC;             // 16-byte chunks per row
+  const int chunks = a.k / EPC;             // 16-byte chunks per full row (layout of W in shared memory)
+  const int chunks_blk = a.kb / EPC;        // 16-byte chunks per row of one K-block (layout of a stage of A)
+  const int nkb = a.k / a.kb;               // K-blocks per tile
   const uint32_t lbo = 128;                 // next core matrix along K
-  const uint32_t sbo = chunks * 128;        // next 8-row group
+  const uint32_t sbo_a = chunks_blk * 128;  // next 8-row group inside a stage of A
+  const uint32_t sbo_b = chunks * 128;      // next 8-row group of W
   const int S = a.stages;
-  const size_t a_bytes = static_cast<size_t>(kTileM) * a.k * sizeof(T);
-  uint8_t *smem_b = smem;                                          // n rows of W[rel]^T
-  uint8_t *smem_a = smem + static_cast<size_t>(a.n) * a.k * sizeof(T);  // S stages of 128 rows
+  const size_t half_bytes = static_cast<size_t>(kTileM) * a.kb * sizeof(T);  // one [128][kb] tile
+  const size_t a_bytes = X3 ? 2 * half_bytes : half_bytes;                   // a stage: raw / hi (+ lo)
+  const size_t w_bytes = static_cast<size_t>(a.n) * a.k * sizeof(T);        // n rows of W[rel]^T
+  uint8_t *smem_b = smem;                                    // W (hi), then W lo in the compensated mode
+  uint8_t *smem_a = smem + (X3 ? 2 * w_bytes : w_bytes);     // S stages
 
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
@@ -201,6 +241,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
     abort_slot = 0;
     for (int s = 0; s < kMaxStages; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.full[s])), "r"(32 * kProdWarps) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.conv[s])), "r"(32 * kConvWarps) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars.empty[s])) : "memory");
     }
     for (int b = 0; b < 2; ++b) {
@@ -218,14 +259,14 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
   const int64_t n_tiles = (a.m + kTileM - 1) / kTileM;
   const int64_t tile_lo = n_tiles * blockIdx.x / gridDim.x, tile_hi = n_tiles * (blockIdx.x + 1) / gridDim.x;
 
-  if (warp > kMmaWarp) {
+  if (warp > kMmaWarp && warp < kFirstConvWarp) {
     // ================= producers: gather A (and W on a relation change) =================
     const int pw = warp - kMmaWarp - 1;          // producer warp: owns rows pw * kRowsPerProdWarp .. of every tile
     // one copy instruction of a warp covers kRpi rows x kCpi consecutive 16-byte chunks
     const int rsub = lane / kCpi, cq = lane % kCpi;
     const T *Wt = static_cast<const T *>(a.wt);
     int64_t loaded_rel = -1;
-    int64_t it = 0;        // tiles issued by this CTA
+    int64_t it = 0;        // units (tile, K-block) issued by this CTA
     bool alive = true;
     // the relation and the row indices of a tile are fetched one tile ahead, off the critical path
     auto fetch = [&](int64_t tile, int64_t &r, int64_t (&ia)[kSlots]) {
@@ -252,66 +293,123 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW), 1) typed_mm_tc(TmmA
         for (int64_t j = (it > S ? it - S : 0); j < it && alive; ++j)
           alive = wait_bar(&bars.empty[j % S], static_cast<uint32_t>((j / S) & 1), abort_flag, a.status, a.wait_cycles);
         if (!alive) break;
-        const T *wr = Wt + r * static_cast<int64_t>(a.n) * a.k;
+        const int64_t w_elems = static_cast<int64_t>(a.n) * a.k;
         const uint32_t b0 = smem_addr(smem_b);
-        for (int row = pw * kRpi + rsub; row < a.n; row += kProdWarps * kRpi)
-          for (int c = cq; c < chunks; c += kCpi)
-            cp_async16<false>(b0 + (row >> 3) * sbo + c * 128 + (row & 7) * 16, wr + static_cast<int64_t>(row) * a.k + c * EPC, 16);
+        for (int part = 0; part < (X3 ? 2 : 1); ++part) {  // hi, then lo
+          const T *wr = Wt + (part * static_cast<int64_t>(a.num_rel) + r) * w_elems;
+          const uint32_t bp = b0 + part * static_cast<uint32_t>(w_bytes);
+          for (int row = pw * kRpi + rsub; row < a.n; row += kProdWarps * kRpi)
+            for (int c = cq; c < chunks; c += kCpi)
+              cp_async16<false>(bp + (row >> 3) * sbo_b + c * 128 + (row & 7) * 16, wr + static_cast<int64_t>(row) * a.k + c * EPC, 16);
+        }
         loaded_rel = r;
       }
-      const int s = static_cast<int>(it % S);
-      if (it >= S) {
-        alive = wait_bar(&bars.empty[s], static_cast<uint32_t>(((it / S) - 1) & 1), abort_flag, a.status, a.wait_cycles);
-        if (!alive) break;
-      }
-      const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+      for (int kb = 0; kb < nkb && alive; ++kb) {
+        const int s = static_cast<int>(it % S);
+        if (it >= S) {
+          alive = wait_bar(&bars.empty[s], static_cast<uint32_t>(((it / S) - 1) & 1), abort_flag, a.status, a.wait_cycles);
+          if (!alive) break;
+        }
+        const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
 #pragma unroll
-      for (int gi = 0; gi < kSlots; ++gi) {
-        const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;  // row of the tile
-        const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
-        const T *src_row = ok ? A + ia[gi] * a.k : A;
-        const int bytes = ok ? 16 : 0;  // size 0 writes zeros
-        const uint32_t d0 = a0 + (row >> 3) * sbo + (row & 7) * 16;
-        for (int c = cq; c < chunks; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
+        for (int gi = 0; gi < kSlots; ++gi) {
+          const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;  // row of the tile
+          const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
+          const T *src_row = ok ? A + ia[gi] * a.k + kb * a.kb : A;
+          const int bytes = ok ? 16 : 0;  // size 0 writes zeros
+          const uint32_t d0 = a0 + (row >> 3) * sbo_a + (row & 7) * 16;
+          for (int c = cq; c < chunks_blk; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
+        }
+        // the unit's full barrier counts this thread's arrival when all copies it has issued so far (this unit's
+        // rows, and W when it was re-copied) have landed: the producer never waits for its own copies
+        if (!(a.test_stall && it == 0))
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&bars.full[s])) : "memory");
+        ++it;
       }
-      // the tile's full barrier counts this thread's arrival when all copies it has issued so far (this tile's
-      // rows, and W when it was re-copied) have landed: the producer never waits for its own copies
-      if (!(a.test_stall && it == 0))
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&bars.full[s])) : "memory");
-      ++it;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (X3 && warp >= kFirstConvWarp) {
+    // ================= converters: raw fp32 stage -> hi (in place) and lo (second half) =================
+    const int ct = tid - 32 * kFirstConvWarp;  // 0 .. 32 * kConvWarps - 1
+    const int n16 = static_cast<int>(half_bytes / 16);
+    int64_t it = 0;
+    bool alive = true;
+    for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
+      const int64_t r = a.rel[tile * kTileM];
+      if (r < 0 || r >= a.num_rel) continue;
+      for (int kb = 0; kb < nkb && alive; ++kb) {
+        const int s = static_cast<int>(it % S);
+        alive = wait_bar(&bars.full[s], static_cast<uint32_t>((it / S) & 1), abort_flag, a.status, a.wait_cycles);
+        if (!alive) break;
+        float4 *hi = reinterpret_cast<float4 *>(smem_a + s * a_bytes);
+        float4 *lo = reinterpret_cast<float4 *>(smem_a + s * a_bytes + half_bytes);
+        for (int c = ct; c < n16; c += 32 * kConvWarps) {
+          // hi = the upper 19 bits of v, lo = the upper 19 bits of v - hi: both are exact TF32 values (one
+          // logic op each instead of a conversion instruction), v - hi is exact in fp32
+          const float4 v = hi[c];
+          float4 h, l;
+          h.x = trunc_tf32(v.x), h.y = trunc_tf32(v.y), h.z = trunc_tf32(v.z), h.w = trunc_tf32(v.w);
+          l.x = trunc_tf32(v.x - h.x), l.y = trunc_tf32(v.y - h.y), l.z = trunc_tf32(v.z - h.z), l.w = trunc_tf32(v.w - h.w);
+          hi[c] = h;
+          lo[c] = l;
+        }
+        // these generic-proxy writes are read by the tensor core through the async proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&bars.conv[s]);
+        ++it;
+      }
+    }
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
     if (lane == 0) {
       const uint32_t idesc = make_idesc(TF32 ? 2 : 1, kTileM, a.n);
       const uint32_t b0 = smem_addr(smem_b);
-      const int steps = chunks / 2;  // two chunks (32 bytes) of K per instruction
-      int64_t it = 0;
+      const int steps = chunks_blk / 2;  // two chunks (32 bytes) of K per instruction
+      int64_t it = 0, tile_it = 0;
       bool alive = true;
       int64_t r_next = tile_lo < tile_hi ? a.rel[tile_lo * kTileM] : -1;
       for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
         const int64_t r = r_next;
         r_next = tile + 1 < tile_hi ? a.rel[(tile + 1) * kTileM] : -1;
         if (r < 0 || r >= a.num_rel) continue;
-        const int s = static_cast<int>(it % S), buf = static_cast<int>(it & 1);
-        alive = wait_bar(&bars.full[s], static_cast<uint32_t>((it / S) & 1), abort_flag, a.status, a.wait_cycles);
-        if (alive && it >= 2)
-          alive = wait_bar(&bars.acc_empty[buf], static_cast<uint32_t>(((it >> 1) - 1) & 1), abort_flag, a.status, a.wait_cycles);
-        if (!alive) break;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+        const int buf = static_cast<int>(tile_it & 1);
         const uint32_t d = tmem_d + buf * a.tmem_cols;
-        for (int j = 0; j < steps; ++j)
-          mma_ss<TF32>(d, make_desc(a0 + j * 256, lbo, sbo), make_desc(b0 + j * 256, lbo, sbo), idesc, j > 0 ? 1u : 0u);
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                         smem_addr(&bars.empty[s]))
-                     : "memory");
+        for (int kb = 0; kb < nkb && alive; ++kb) {
+          const int s = static_cast<int>(it % S);
+          alive = wait_bar(X3 ? &bars.conv[s] : &bars.full[s], static_cast<uint32_t>((it / S) & 1), abort_flag, a.status,
+                           a.wait_cycles);
+          if (alive && kb == 0 && tile_it >= 2)
+            alive = wait_bar(&bars.acc_empty[buf], static_cast<uint32_t>(((tile_it >> 1) - 1) & 1), abort_flag, a.status,
+                             a.wait_cycles);
+          if (!alive) break;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+          const uint32_t bk = b0 + kb * chunks_blk * 128;  // this K-block's columns of W
+          for (int j = 0; j < steps; ++j) {
+            const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
+            if (X3) {
+              const uint64_t da_hi = make_desc(a0 + j * 256, lbo, sbo_a);
+              const uint64_t da_lo = make_desc(a0 + static_cast<uint32_t>(half_bytes) + j * 256, lbo, sbo_a);
+              const uint64_t db_hi = make_desc(bk + j * 256, lbo, sbo_b);
+              const uint64_t db_lo = make_desc(bk + static_cast<uint32_t>(w_bytes) + j * 256, lbo, sbo_b);
+              mma_ss<TF32>(d, da_hi, db_lo, idesc, first);  // the two small terms first, the large one last
+              mma_ss<TF32>(d, da_lo, db_hi, idesc, 1u);
+              mma_ss<TF32>(d, da_hi, db_hi, idesc, 1u);
+            } else {
+              mma_ss<TF32>(d, make_desc(a0 + j * 256, lbo, sbo_a), make_desc(bk + j * 256, lbo, sbo_b), idesc, first);
+            }
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           smem_addr(&bars.empty[s]))
+                       : "memory");
+          ++it;
+        }
+        if (!alive) break;
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                          smem_addr(&bars.acc_full[buf]))
                      : "memory");
-        ++it;
+        ++tile_it;
       }
       // the epilogue of the last tiles must be over before the tensor memory goes away: it arrives on
       // acc_empty, which the final __syncthreads of the epilogue warps also orders.
@@ -427,7 +525,8 @@ extern "C" int cxg_typed_matmul_workspace_size(int num_rel, int k, int n, int dt
   CXG_REQUIRE(bytes != nullptr, CXG_ENULL, "cxg_typed_matmul_workspace_size: bytes is NULL");
   CXG_REQUIRE(num_rel > 0 && k > 0 && n > 0 && (dtype == CXG_F32 || dtype == CXG_BF16), CXG_EINVAL,
               "cxg_typed_matmul_workspace_size: bad arguments");
-  *bytes = 256 + align_up(static_cast<size_t>(num_rel) * k * n * (dtype == CXG_F32 ? 4 : 2), 256);
+  // status words + W transposed; fp32 keeps room for the hi and lo parts of the error-compensated mode
+  *bytes = 256 + align_up(static_cast<size_t>(num_rel) * k * n * (dtype == CXG_F32 ? 8 : 2), 256);
   return CXG_OK;
 }
 
@@ -438,12 +537,19 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   const int atomic = (flags & CXG_TMM_ATOMIC_F32) ? 1 : 0;
   CXG_REQUIRE(m >= 0 && m_valid >= 0 && k > 0 && n > 0 && num_rel > 0, CXG_EINVAL, "cxg_typed_matmul: bad sizes");
   CXG_REQUIRE(dtype == CXG_F32 || dtype == CXG_BF16, CXG_EINVAL, "cxg_typed_matmul: dtype %d", dtype);
-  CXG_REQUIRE(precision == 0 || precision == 1, CXG_EINVAL, "cxg_typed_matmul: precision %d", precision);
+  CXG_REQUIRE(precision >= 0 && precision <= 2, CXG_EINVAL, "cxg_typed_matmul: precision %d", precision);
   if (m == 0) return CXG_OK;
   CXG_REQUIRE(a && w && c && rel, CXG_ENULL, "cxg_typed_matmul: NULL argument");
   cudaStream_t st = as_stream(stream);
   const int follows = (src_idx != nullptr && dst_idx == nullptr && !seq_output) ? 1 : 0;
   if (precision == 0) {  // exact fp32 accumulation of every product, no tensor cores
+    CXG_REQUIRE(!atomic || dtype == CXG_F32, CXG_EUNSUPPORTED, "cxg_typed_matmul: exact mode adds atomically in fp32 only");
+    return typed_rows_launch(a, w, c, rel, 8, src_idx, dst_idx, m, m_valid, k, n, num_rel, dtype, atomic ? 2 : 0, follows,
+                             st);
+  }
+  const bool x3 = precision == 2 && dtype == CXG_F32;  // bf16 inputs have nothing to compensate
+  if (x3 && static_cast<size_t>(n) * k * 8 + static_cast<size_t>(kTileM) * 8 * 8 > static_cast<size_t>(kSmemBudget)) {
+    // both TF32 terms of W[rel] do not fit in shared memory next to one stage: the exact kernel keeps the accuracy
     CXG_REQUIRE(!atomic || dtype == CXG_F32, CXG_EUNSUPPORTED, "cxg_typed_matmul: exact mode adds atomically in fp32 only");
     return typed_rows_launch(a, w, c, rel, 8, src_idx, dst_idx, m, m_valid, k, n, num_rel, dtype, atomic ? 2 : 0, follows,
                              st);
@@ -455,9 +561,20 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
               k, 2 * epc);
   CXG_REQUIRE(n % 16 == 0 && n >= 16 && n <= 256, CXG_EUNSUPPORTED,
               "cxg_typed_matmul: N = %d must be a multiple of 16 in [16, 256] on the tensor path", n);
-  const size_t a_bytes = static_cast<size_t>(kTileM) * k * elem, b_bytes = static_cast<size_t>(n) * k * elem;
+  const size_t b_bytes = static_cast<size_t>(n) * k * elem * (x3 ? 2 : 1);
+  // K-block: the whole row when a stage then fits at least `want` times next to W, else halved while it stays a
+  // multiple of one instruction's K (32 bytes)
+  auto stage_bytes = [&](int kb) { return static_cast<size_t>(kTileM) * kb * elem * (x3 ? 2 : 1); };
+  int kb = k;
+  const int want = x3 ? 4 : 1;
+  while (b_bytes + want * stage_bytes(kb) > static_cast<size_t>(kSmemBudget) && kb % (4 * epc) == 0) kb /= 2;
+  if (const char *env = getenv("CXG_TMM_KBLOCK")) {  // tuning aid: force the K-block (must divide K, multiple of 32 bytes)
+    const int v = atoi(env);
+    if (v > 0 && k % v == 0 && v % (2 * epc) == 0) kb = v;
+  }
+  const size_t a_bytes = stage_bytes(kb);
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
-              "cxg_typed_matmul: one tile of %zu bytes exceeds shared memory", a_bytes + b_bytes);
+              "cxg_typed_matmul: one stage of %zu bytes plus W of %zu bytes exceeds shared memory", a_bytes, b_bytes);
   int stages = static_cast<int>((kSmemBudget - b_bytes) / a_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   const size_t smem = b_bytes + stages * a_bytes;
@@ -483,6 +600,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   while (cols < n) cols <<= 1;
   t.tmem_cols = cols;  // two buffers: 2 * cols <= 512
   t.stages = stages;
+  t.kb = kb;
   if (cudaMemsetAsync(t.status, 0, 256, st) != cudaSuccess) return check_launch("cxg_typed_matmul: memset");
   const int64_t n_tiles = (m + kTileM - 1) / kTileM;
   // one persistent CTA per SM (its shared-memory ring fills the SM), contiguous tile ranges
@@ -491,17 +609,25 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   // rows that are gathered several times each go through L1, rows read once bypass it
   const bool ca = src_idx != nullptr && m_valid * 2 <= m;
   cudaError_t e = cudaSuccess;
-  auto launch = [&](auto kernel, int prod_warps) {
+  auto launch = [&](auto kernel, int warps) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), 32 * (kEpiWarps + 1 + prod_warps), smem, st>>>(t);
+    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), 32 * warps, smem, st>>>(t);
   };
   if (dtype == CXG_F32) {
-    transpose_w<float><<<kNumSM, 256, 0, st>>>(static_cast<const float *>(w), static_cast<float *>(wt), num_rel, k, n);
-    if (ca) launch(typed_mm_tc<float, true, 8>, 8); else launch(typed_mm_tc<float, false, 8>, 8);
+    float *wt_f = static_cast<float *>(wt);
+    transpose_w<float><<<kNumSM, 256, 0, st>>>(static_cast<const float *>(w), wt_f,
+                                               x3 ? wt_f + static_cast<size_t>(num_rel) * k * n : nullptr, num_rel, k, n);
+    constexpr int kW = kEpiWarps + 1 + 8;
+    if (x3) {
+      if (ca) launch(typed_mm_tc<float, true, 8, true>, kW + kConvWarps); else launch(typed_mm_tc<float, false, 8, true>, kW + kConvWarps);
+    } else {
+      if (ca) launch(typed_mm_tc<float, true, 8, false>, kW); else launch(typed_mm_tc<float, false, 8, false>, kW);
+    }
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),
-                                                       static_cast<__nv_bfloat16 *>(wt), num_rel, k, n);
-    if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4>, 4); else launch(typed_mm_tc<__nv_bfloat16, false, 4>, 4);
+                                                       static_cast<__nv_bfloat16 *>(wt), nullptr, num_rel, k, n);
+    constexpr int kW = kEpiWarps + 1 + 4;
+    if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4, false>, kW); else launch(typed_mm_tc<__nv_bfloat16, false, 4, false>, kW);
   }
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_typed_matmul: %s", cudaGetErrorString(e));
   count_launches(2);

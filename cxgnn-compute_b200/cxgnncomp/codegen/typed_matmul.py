@@ -11,7 +11,8 @@ def typed_matmul(a, b, rel, num_valid_item=-1, src_idx=None, dst_idx=None, seq_o
     relation; positions whose index is negative or >= num_valid_item are padding. Unlike the reference,
     which launches cdiv(num_valid_item, BLOCK_M) tiles over the padded array and so skips the last
     positions (its FIXME at :777), every position of `rel` is visited.
-    fp32 inputs are multiplied as TF32 on the tensor cores (as tl.dot does), bf16 inputs as bf16."""
+    bf16 inputs are multiplied as bf16 on the tensor cores; fp32 inputs as error-compensated TF32 (fp32 accuracy),
+    or as plain TF32 like the reference's tl.dot when cxgnncomp_backend.ALLOW_TF32 is set."""
     assert a.shape[1] == b.shape[1], "incompatible dimensions"
     assert a.is_contiguous() and b.is_contiguous() and rel.is_contiguous()
     positions = rel.shape[0]

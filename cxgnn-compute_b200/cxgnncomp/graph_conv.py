@@ -296,7 +296,7 @@ class MyRGCNConv(torch.nn.Module):
             table = n_src * k + self.num_rel * n_src * o + num_edge * o
             schedule = "transform_first" if table < fused else "fused_gather"
         if self.norm == "total" and schedule == "transform_first":
-            if x.dtype == torch.float32:
+            if x.dtype == torch.float32 and cxgnncomp_backend.ALLOW_TF32:
                 old = torch.backends.cuda.matmul.allow_tf32
                 torch.backends.cuda.matmul.allow_tf32 = True
                 try:

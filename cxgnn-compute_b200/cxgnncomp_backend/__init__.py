@@ -837,6 +837,11 @@ def gather(x_edge, dest, num_node):
     return _GatherFunction.apply(x_edge, dest, int(num_node))
 
 
+# fp32 inputs of the typed matmul on the tensor cores: False (default) = error-compensated TF32 (three products per
+# term, fp32 accuracy); True = plain TF32 like the reference's tl.dot (test/2-benchmark/bench-memory-rgcn.py:121
+# sets allow_tf32).
+ALLOW_TF32 = os.environ.get("CXG_ALLOW_TF32", "0") == "1"
+
 from ._rgcn import (pad_rel, pad_rel_idx, typed_linear, typed_linear_s2e, typed_linear_s2d,  # noqa: E402,F401
                     aggr_rgcn_direct_func, rel_schedule, typed_matmul_raw, topo_sort, aggr_rel_direct)
 

@@ -2,6 +2,7 @@
 rel_schedule and the typed matmul entry used by `cxgnncomp.codegen.typed_matmul`
 (reference: init_rel_spmm / init_compute in src/cpp/python_bindings/binding.cpp:28,44-55)."""
 import ctypes
+import sys
 
 import torch
 
@@ -173,10 +174,12 @@ def aggr_rel_direct(x, ptr, idx, weights, etype, num_node, num_rel):
 
 
 def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None, seq_output=False, exact=False,
-                     out_rows=None, atomic_out=None, extra_flags=0):
+                     out_rows=None, atomic_out=None, extra_flags=0, allow_tf32=None):
     """C = typed matmul through the C ABI. a [*, K], b [R, K, N], rel int64 per position; see cxg_typed_matmul.
     C has `out_rows` rows (default: m_positions for sequential output, else m_valid). With `atomic_out` (a
-    float32 [*, N] tensor) the rows are ADDED into it with vector atomics instead (rows may repeat)."""
+    float32 [*, N] tensor) the rows are ADDED into it with vector atomics instead (rows may repeat).
+    exact: fp32 fma without tensor cores. allow_tf32 (default: cxgnncomp_backend.ALLOW_TF32): plain TF32 products
+    for fp32 inputs instead of the error-compensated ones."""
     _cuda(a, "a", (torch.float32, torch.bfloat16))
     _cuda(b, "b", (a.dtype,))
     _cuda(rel, "rel", (torch.int64,))
@@ -200,10 +203,13 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
         # rows that no position writes are left unset, like the reference's torch.empty output
         c = torch.empty((int(out_rows), n), dtype=a.dtype, device=a.device)
     dtype = CXG_F32 if a.dtype == torch.float32 else CXG_BF16
+    if allow_tf32 is None:
+        allow_tf32 = sys.modules[__package__].ALLOW_TF32
+    precision = 0 if exact else (1 if (allow_tf32 or dtype == CXG_BF16) else 2)
     need = _sz(0)
     _check(_tmm_ws(num_rel, k, n, dtype, ctypes.byref(need)), "cxg_typed_matmul_workspace_size")
     ws = _workspace(a.device, need.value, "typed_matmul")
     with torch.cuda.device(a.device):
         _check(_tmm(_p(a), _p(b), _p(c), _p(rel), _p(src_idx), _p(dst_idx), int(m_positions), int(m_valid), k, n, num_rel,
-                    dtype, 0 if exact else 1, flags, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")
+                    dtype, precision, flags, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")
     return c

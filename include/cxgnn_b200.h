@@ -372,8 +372,11 @@ int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
  * Replaces typed_matmul and its four Triton kernels (cxgnncomp/codegen/
  * triton_typed_matmul.py:145-860). A [*, k], W [num_rel, k, n], C [*, n] of dtype (fp32/bf16).
  * precision 1: tcgen05 tensor cores, fp32 accumulation in tensor memory (bf16 inputs, or fp32
- * inputs as TF32 like the reference's tl.dot); needs k % 16 == 0 (bf16) / % 8 (fp32), n % 16
- * == 0, n <= 256. precision 0: exact fp32 fma of every product (no tensor cores), any k, n.
+ * inputs as TF32 like the reference's tl.dot: about 1e-3 relative); precision 2: fp32 inputs with
+ * error-compensated TF32 (every operand split into two TF32 terms, three products per term summed in
+ * the same accumulator: fp32 accuracy, about 1e-6; same as 1 for bf16). Both need k % 16 == 0
+ * (bf16) / % 8 (fp32), n % 16 == 0, n <= 256. precision 0: exact fp32 fma of every product (no
+ * tensor cores), any k, n.
  * flags: CXG_TMM_SEQ_OUTPUT as above; CXG_TMM_ATOMIC_F32 adds the rows into C, which is then
  * float32 [*, n] whatever dtype is (vector atomics; rows of C may be hit by many positions, e.g.
  * oc = destination node of an edge, which fuses the segment sum of the RGCN layer into the
