@@ -153,8 +153,18 @@ def cpu_baseline_sample(ptr, idx, feat, dtype, budget_s=20.0):
             "sample_own_GBps": b_alg / best[form] / 1e9}
 
 
+def load_synthetic():
+    """cxgnncomp/synthetic.py (seeded generators, plain torch) loaded by path: importing the package would load
+    the CUDA library, which the reference arm must not touch."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("cxg_synthetic", os.path.join(PKG, "cxgnncomp", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def build_workload(name, device, seed=0):
-    from cxgnncomp import synthetic
+    synthetic = load_synthetic()
     n, e_und, feat, dt, it, desc = WORKLOADS[name]
     idx_dtype = torch.int32 if it == "int32" else torch.int64
     ptr, idx = synthetic.powerlaw_graph(n, e_und, seed=seed, device=device, idx_dtype=idx_dtype)
@@ -177,10 +187,12 @@ def run_reference(args, rank):
     ms = sum(ts[args.warmup:]) / max(1, args.steps)
     base["value"] = base["value"] * base["ms"] / ms  # mean over the timed steps instead of the last one
     line = {"impl": "reference", "metric": "spmm_algorithmic_hbm_throughput", "value": base["value"], "unit": "GB/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": base["extrapolated_pass_s"] * 1e3 * ms / base["ms"],  # one whole pass, extrapolated
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name, "description": desc, "sample": base["sample"]},
-            "cpu_baseline": base,
+            "config": {"workload": name, "description": desc, "nodes": n, "nnz": int(ptr[n]), "feat": feat,
+                       "sample": base["sample"]},
+            "extrapolated": True, "sample_ms_per_step": ms, "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -203,6 +215,8 @@ def main():
                     help="needed-rows mode: aggregate the own-source edges while the exchange is in flight (measured: "
                          "no gain, the persistent aggregation kernel fills every SM and the NCCL kernel waits for it)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-layers", action="store_true",
+                    help="skip the per-layer records of configurations 1, 2 and 4 (added at 1 GPU by default)")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -370,18 +384,14 @@ def main():
     if not args.no_e2e:
         hx = torch.empty(x_own.shape, dtype=dtype).pin_memory()
         hx.copy_(x_own)
-        hidx = torch.empty(lidx.shape, dtype=lidx.dtype).pin_memory()
-        hidx.copy_(lidx)
-        hptr = torch.empty(lptr.shape, dtype=lptr.dtype).pin_memory()
-        hptr.copy_(lptr)
         hy = torch.empty(y.shape, dtype=dtype).pin_memory()
-        d_idx, d_ptr = torch.empty_like(lidx), torch.empty_like(lptr)
 
         ksteps = min(args.steps, 5)
+        # The graph (ptr, idx) does not change between steps and stays on the device, like a layer's weights; what
+        # a step brings in is the feature matrix and what it returns is the aggregated matrix.
         # Double-buffered: the upload of step k+1 runs on its own stream while step k aggregates and step k-1's
         # result returns to the host (the link is full duplex), so a step costs max(upload, download), not their sum.
-        xb, ib, pb, yb = [x_full, torch.empty_like(x_full)], [d_idx, torch.empty_like(d_idx)], \
-            [d_ptr, torch.empty_like(d_ptr)], [y, torch.empty_like(y)]
+        xb, yb = [x_full, torch.empty_like(x_full)], [y, torch.empty_like(y)]
         s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
         ev_in = [torch.cuda.Event() for _ in range(2)]
         ev_comp = [torch.cuda.Event() for _ in range(2)]
@@ -391,16 +401,14 @@ def main():
             for k in range(k_steps):
                 b = k & 1
                 with torch.cuda.stream(s_in):
-                    s_in.wait_event(ev_comp[b])  # the aggregation that last read these buffers
+                    s_in.wait_event(ev_comp[b])  # the aggregation that last read this buffer
                     own_rows(xb[b]).copy_(hx, non_blocking=True)
-                    ib[b].copy_(hidx, non_blocking=True)
-                    pb[b].copy_(hptr, non_blocking=True)
                     ev_in[b].record(s_in)
                 s_main.wait_event(ev_in[b])
                 s_main.wait_event(ev_out[b])  # the download that last read this output buffer
                 if world > 1:
                     exchange(xb[b])
-                be.spmm_into(yb[b], pb[b], ib[b], xb[b], n_local)
+                be.spmm_into(yb[b], lptr, lidx, xb[b], n_local)
                 ev_comp[b].record(s_main)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_comp[b])
@@ -417,24 +425,27 @@ def main():
         b_ev.record()
         b_ev.synchronize()
         e_ms = a_ev.elapsed_time(b_ev) / ksteps
-        del xb, ib, pb, yb
+        del xb, yb
         barrier()
         te = torch.tensor([e_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        h2d = hx.numel() * elem + hidx.numel() * idx_bytes + hptr.numel() * 8
+        h2d = hx.numel() * elem
         d2h = hy.numel() * elem
         e2e = {"value": b_alg_total / (float(te[0]) * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": float(te[0]),
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": ksteps,
-               "api": ("cxgnncomp_backend.spmm_into (cxg_spmm_csr with a caller-owned output), inputs from pinned host "
-                       "memory, two buffer sets: upload of step k+1, exchange + aggregation of step k and download "
-                       "of step k-1 overlap")}
-        del hx, hidx, hptr, hy
+               "api": ("cxgnncomp_backend.spmm_into (cxg_spmm_csr with a caller-owned output); every step the feature "
+                       "matrix comes from pinned host memory and the aggregated matrix goes back to it, the graph "
+                       "(ptr, idx) stays on the device; two buffer sets: upload of step k+1, exchange + aggregation "
+                       "of step k and download of step k-1 overlap")}
+        del hx, hy
 
     peak, peak_src = load_peaks()
     achieved = b_alg_local / (spmm_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_DRAM_BYTES.get(args.workload) if world == 1 else None, "peak_source": peak_src,
+                "traffic": NCU_DRAM_BYTES.get(args.workload) if world == 1 else None,
+                "traffic_source": "ncu capture summarised in profiles/spmm_stream_papers.md (a constant, not measured by this run)",
+                "peak_source": peak_src,
                 "kernel": "cxg_spmm_csr (plan + spmm_stream + fix kernels)",
                 "ms": spmm_ms, "algorithmic_bytes": b_alg_local}
     if roofline["traffic"]:
@@ -444,6 +455,13 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline_sample(full_ptr, lidx, feat, dtype)
+
+    layers = None
+    if rank == 0 and world == 1 and not args.no_layers:
+        del x_full, y, lidx, lptr, ptr, full_ptr, x_own, idx
+        torch.cuda.empty_cache()
+        import bench_layers
+        layers = bench_layers.quick()
 
     exchange_info = None
     if world > 1:
@@ -464,7 +482,7 @@ def main():
                            (f" in {exchange_chunks} chunks" if ex is not None and exchange_chunks > 1 else ""),
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
-                "gpu_launches": int(launches), "roofline": roofline, "exchange": exchange_info, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
+                "gpu_launches": int(launches), "roofline": roofline, "layers": layers, "exchange": exchange_info, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:

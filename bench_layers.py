@@ -63,8 +63,9 @@ def rel(a, b):
     return float((a - b).abs().max() / b.abs().max().clamp(min=1e-30))
 
 
-def config1(steps, flush):
-    """GCN aggregation, 169,343 nodes / 2,332,487 edges, F = 128 fp32, forward and backward w.r.t. features."""
+def config1(steps, flush, cpu=True):
+    """GCN aggregation, 169,343 nodes / 2,332,487 edges, F = 128 fp32, forward and backward w.r.t. features.
+    cpu=False skips the timing of the CPU formulation (the error checks against the oracle stay)."""
     import cxgnncomp_backend as be
     import oracle
     from cxgnncomp import synthetic
@@ -75,41 +76,47 @@ def config1(steps, flush):
     p, i, xg, dyg = ptr.cuda(), idx.cuda(), x.cuda(), dy.cuda()
     nnz = idx.shape[0]
     fwd = gpu_ms(lambda: be.run_spmm_configurable(p, i, xg, n), steps, flush)
-    be.BACKWARD_MODE = "scatter"
+    want_b = oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0]
+    be.BACKWARD_MODE = "scatter"  # the reference's formulation: atomic adds, order not fixed
     bwd = gpu_ms(lambda: be.run_spmm_configurable_bwd(p, i, xg, dyg, n), steps, flush)
-    err_b = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0])
-    be.BACKWARD_MODE = "transpose"  # the transposed graph is built on the first call and cached
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    be.run_spmm_configurable_bwd(p, i, xg, dyg, n)
-    torch.cuda.synchronize()
-    transpose_build_ms = (time.perf_counter() - t0) * 1e3
+    err_b = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), want_b)
+    be.BACKWARD_MODE = "auto"  # default: forward kernel over the transposed graph, built on the device and cached
+    t_build = gpu_ms(lambda: be.csr_transpose(p, i, n, n), steps, flush)
+
+    def bwd_cold():
+        be._TRANSPOSE_CACHE.clear()
+        return be.run_spmm_configurable_bwd(p, i, xg, dyg, n)
+
+    bwd_first = gpu_ms(bwd_cold, steps, flush)
     bwd_t = gpu_ms(lambda: be.run_spmm_configurable_bwd(p, i, xg, dyg, n), steps, flush)
-    err_bt = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), oracle.spmm_bwd_f64(ptr, idx, dy, x.shape)[0])
-    be.BACKWARD_MODE = "auto"
-    bwd_sym = gpu_ms(lambda: be.run_spmm_configurable(p, i, dyg, n), steps, flush)  # AggrOP.backward on a symmetric graph
+    err_bt = rel(be.run_spmm_configurable_bwd(p, i, xg, dyg, n).cpu(), want_b)
     y = be.run_spmm_configurable(p, i, xg, n).cpu()
     err_f = rel(y, oracle.spmm_f64(ptr, idx, x))
-    xr = x.clone().requires_grad_(True)
-    dst = oracle.dst_of_edges(ptr)
-
-    def cpu_fb():
-        xr.grad = None
-        out = torch.zeros(n, 128).index_add_(0, dst, xr.index_select(0, idx))
-        out.backward(dy)
-
-    torch.set_num_threads(os.cpu_count() or 1)
-    c_fwd = cpu_ms(lambda: oracle.torch_spmm_sparse(x, ptr, idx, n))
-    c_fb = cpu_ms(cpu_fb)
     b_alg = 2 * n * 128 * 4 + nnz * 8 + (n + 1) * 8
-    return {"config": "c1 GCN SpMM fwd/bwd", "nodes": n, "nnz": nnz, "gpu_fwd_ms": fwd, "gpu_bwd_scatter_ms": bwd,
-            "gpu_bwd_transposed_ms": bwd_t, "transpose_build_first_call_ms": transpose_build_ms,
-            "max_rel_err_bwd_transposed": err_bt, "gpu_bwd_symmetric_ms": bwd_sym, "b_alg_bytes": b_alg, "fwd_GBps": b_alg / fwd / 1e6,
-            "fwd_gflops": 2 * nnz * 128 / fwd / 1e6, "cpu_fwd_sparse_mm_ms": c_fwd, "cpu_fwd_bwd_index_add_ms": c_fb,
-            "cpu_cores": torch.get_num_threads(), "max_rel_err_fwd": err_f, "max_rel_err_bwd": err_b}
+    hbm = peaks()[0]
+    out = {"config": "c1 GCN SpMM fwd/bwd (169,343 nodes, F=128 fp32, int64 idx)", "nodes": n, "nnz": nnz,
+           "gpu_fwd_ms": fwd, "gpu_bwd_ms": bwd_t, "gpu_bwd_first_call_ms": bwd_first, "transpose_build_ms": t_build,
+           "gpu_bwd_scatter_ms": bwd, "b_alg_bytes": b_alg, "fwd_GBps": b_alg / fwd / 1e6,
+           "fwd_frac_hbm_peak": b_alg / fwd / 1e6 / hbm, "bwd_frac_hbm_peak": b_alg / bwd_t / 1e6 / hbm,
+           "fwd_gflops": 2 * nnz * 128 / fwd / 1e6, "max_rel_err_fwd": err_f, "max_rel_err_bwd": err_bt,
+           "max_rel_err_bwd_scatter": err_b,
+           "note": "inputs (193 MB) fit the 126 MB L2 in large part: the kernel is latency / issue bound here, not HBM bound"}
+    if cpu:
+        xr = x.clone().requires_grad_(True)
+        dst = oracle.dst_of_edges(ptr)
+
+        def cpu_fb():
+            xr.grad = None
+            o = torch.zeros(n, 128).index_add_(0, dst, xr.index_select(0, idx))
+            o.backward(dy)
+
+        torch.set_num_threads(os.cpu_count() or 1)
+        out.update({"cpu_fwd_sparse_mm_ms": cpu_ms(lambda: oracle.torch_spmm_sparse(x, ptr, idx, n)),
+                    "cpu_fwd_bwd_index_add_ms": cpu_ms(cpu_fb), "cpu_cores": torch.get_num_threads()})
+    return out
 
 
-def config2(steps, flush):
+def config2(steps, flush, cpu=True):
     """GAT layer, 4 heads x 32, 128-dim input, LeakyReLU 0.2, on the configuration-1 graph; forward + backward."""
     import cxgnncomp
     import oracle
@@ -147,8 +154,8 @@ def config2(steps, flush):
         return out
 
     torch.set_num_threads(os.cpu_count() or 1)
-    ref = cpu_fb().detach()
-    c_fb = cpu_ms(cpu_fb, reps=3)
+    ref = cpu_fb().detach()  # also the parity reference below
+    c_fb = cpu_ms(cpu_fb, reps=3) if cpu else None
     fb()
     err = rel(fwd().cpu(), ref)
     err_g = rel(xg.grad.cpu(), xr.grad)
@@ -278,8 +285,10 @@ def config3(steps, flush, scale=1.0):
             "note": "CPU step excludes sampling and feature gather (batches taken from the GPU sampler)"}
 
 
-def config4(steps, flush, scale=1.0):
-    """RGCN layer, 8 relations, 1.94 M nodes / 21 M edges, 128 -> 64, fp32 (TF32 products) and bf16."""
+def config4(steps, flush, scale=1.0, cpu=True, quick=False):
+    """RGCN layer, 8 relations, 1.94 M nodes / 21 M edges, 128 -> 64: fp32 (error-compensated TF32, the default),
+    fp32 with plain TF32 products (the reference's tl.dot precision) and bf16. quick=True times the default
+    schedule only."""
     import cxgnncomp
     import cxgnncomp_backend as be
     import oracle
@@ -291,19 +300,26 @@ def config4(steps, flush, scale=1.0):
     nnz = idx.shape[0]
     rel_t = synthetic.edge_relations(nnz, 8, seed=0, device=dev)
     hbm, tens, _ = peaks()
-    out = {"config": "c4 RGCN layer (8 relations, 128 -> 64)", "nodes": n, "nnz": nnz}
-    for dtype, name in ((torch.float32, "fp32_tf32"), (torch.bfloat16, "bf16")):
+    out = {"config": "c4 RGCN layer (8 relations, 128 -> 64, total in-degree normalisation)", "nodes": n, "nnz": nnz}
+    pc, ic, rc = ptr.cpu(), idx.cpu(), rel_t.cpu()
+    rows = torch.randint(0, n, (2000,), generator=torch.Generator().manual_seed(1)).sort().values.unique()
+    for dtype, name, tf32 in ((torch.float32, "fp32", False), (torch.float32, "fp32_tf32", True),
+                              (torch.bfloat16, "bf16", False)):
         torch.manual_seed(0)
+        be.ALLOW_TF32 = tf32
         conv = cxgnncomp.MyRGCNConv(128, 64, 8).cuda().to(dtype)
         x = synthetic.node_features(n, 128, seed=0, device=dev, dtype=dtype)
         with torch.no_grad():
             t_sched = {}
-            for sched in ("e2e", "fused_gather", "fused_scatter", "transform_first"):
+            for sched in (() if quick else ("e2e", "fused_gather", "fused_scatter", "transform_first")):
                 conv.schedule = sched
                 conv(x, ptr, idx, rel_t, n)  # builds the relation buckets once, like the reference caches them
                 t_sched[sched] = gpu_ms(lambda: conv(x, ptr, idx, rel_t, n), steps, flush)
             conv.schedule = "auto"
+            conv(x, ptr, idx, rel_t, n)
             t_layer = gpu_ms(lambda: conv(x, ptr, idx, rel_t, n), steps, flush)
+            if len(conv.preprocessed) == 0:
+                conv.preprocessed = cxgnncomp.TypedLinearE2EOP.preprocess(conv.linear, rel_t)
             st, num_item, indices = conv.preprocessed[:3]
             xe = x[idx]
             t_mm = gpu_ms(lambda: be.typed_matmul_raw(xe, conv.linear.data, st, st.shape[0], nnz, src_idx=indices),
@@ -312,9 +328,8 @@ def config4(steps, flush, scale=1.0):
         elem = 2 if dtype == torch.bfloat16 else 4
         flops = 2.0 * nnz * 128 * 64
         b_mm = nnz * (128 + 64) * elem + 8 * 128 * 64 * elem + nnz * 9
+        b_fused = n * 128 * elem + n * 64 * elem + 8 * 128 * 64 * elem + nnz * 9  # gather -> matmul -> segment sum
         # parity on a row sample against float64
-        rows = torch.randint(0, n, (2000,), generator=torch.Generator().manual_seed(1)).sort().values.unique()
-        pc, ic, rc = ptr.cpu(), idx.cpu(), rel_t.cpu()
         W = conv.linear.detach().float().cpu()
         xc = x.float().cpu()
         errs = []
@@ -324,22 +339,42 @@ def config4(steps, flush, scale=1.0):
                 continue
             ref = oracle.typed_linear_f64(xc, W, rc[e0:e1], src=ic[e0:e1]).sum(0) / (e1 - e0)
             errs.append(float((y[r].float().cpu().double() - ref).abs().max() / ref.abs().max().clamp(min=1e-30)))
-        out[name] = {"layer_ms": t_layer, "layer_ms_by_schedule": t_sched, "typed_matmul_ms": t_mm, "typed_matmul_tflops": flops / t_mm / 1e9,
+        out[name] = {"layer_ms": t_layer, "layer_ms_by_schedule": t_sched, "layer_b_alg_fused_bytes": b_fused,
+                     "layer_frac_hbm_peak_fused_bytes": b_fused / t_layer / 1e6 / hbm,
+                     "typed_matmul_ms": t_mm, "typed_matmul_tflops": flops / t_mm / 1e9,
                      "typed_matmul_frac_tensor_peak": flops / t_mm / 1e9 / tens,
                      "typed_matmul_b_alg_GBps": b_mm / t_mm / 1e6, "typed_matmul_frac_hbm_peak": b_mm / t_mm / 1e6 / hbm,
                      "max_rel_err_sampled_rows": max(errs)}
         del conv, x, xe, y
         torch.cuda.empty_cache()
-    # CPU: the reference's sorted formulation on a 1/8 row sample (typed_linear.py:262-310)
-    r1 = n // 8
-    pc, ic, rc = ptr[:r1 + 1].cpu(), idx[:int(ptr[r1])].cpu(), rel_t[:int(ptr[r1])].cpu()
-    xc = torch.randn(n, 128)
-    W = torch.randn(8, 128, 64)
-    torch.set_num_threads(os.cpu_count() or 1)
-    out["cpu_sorted_formulation_ms_one_eighth_of_rows"] = cpu_ms(lambda: oracle.torch_rgcn_sorted(xc, W, pc, ic, rc, r1),
-                                                               reps=3)
-    out["cpu_cores"] = torch.get_num_threads()
+    be.ALLOW_TF32 = False
+    if cpu:
+        # CPU: the reference's sorted formulation on a 1/8 row sample (typed_linear.py:262-310)
+        r1 = n // 8
+        pc, ic, rc = ptr[:r1 + 1].cpu(), idx[:int(ptr[r1])].cpu(), rel_t[:int(ptr[r1])].cpu()
+        xc = torch.randn(n, 128)
+        W = torch.randn(8, 128, 64)
+        torch.set_num_threads(os.cpu_count() or 1)
+        out["cpu_sorted_formulation_ms_one_eighth_of_rows"] = cpu_ms(
+            lambda: oracle.torch_rgcn_sorted(xc, W, pc, ic, rc, r1), reps=3)
+        out["cpu_cores"] = torch.get_num_threads()
     return out
+
+
+def quick(steps=5):
+    """Configurations 1, 2 and 4 on the GPU only (no CPU timing): what bench.py adds to its line as "layers"."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    res = {}
+    for name, fn in (("c1", lambda: config1(steps, flush, cpu=False)), ("c2", lambda: config2(steps, flush, cpu=False)),
+                     ("c4", lambda: config4(steps, flush, cpu=False, quick=True))):
+        t0 = time.time()
+        try:
+            res[name] = fn()
+        except Exception as e:  # a layer record must not cost the headline line
+            res[name] = {"error": f"{type(e).__name__}: {e}"}
+        res[name]["wall_s"] = time.time() - t0
+        torch.cuda.empty_cache()
+    return res
 
 
 def main():

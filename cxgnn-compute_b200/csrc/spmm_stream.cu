@@ -20,7 +20,8 @@
 // Rows that lie inside one tile are therefore summed exactly like a sequential
 // loop. A row that crosses tile borders leaves one partial per tile in scratch
 // memory; a second kernel adds those partials in tile order (sequentially up to
-// 64 of them, in 8 ordered blocks beyond), so results do not depend on scheduling
+// 64 of them; beyond that in blocks of 64 consecutive partials, one warp per block,
+// whose sums are then added in block order), so results do not depend on scheduling
 // and can be reproduced on a CPU given T.
 #include <type_traits>
 
@@ -35,7 +36,7 @@ constexpr int kSThreads = kSWarps * 32;
 constexpr int kStages = 1;         // ring depth per warp (1: latency is hidden by other warps)
 constexpr int kStageBytes = 8192;  // feature bytes per stage and warp
 constexpr int kCtasPerSM = 6;
-constexpr int kSeqPartials = 64;   // longer chains are added in 8 ordered blocks
+constexpr int kSeqPartials = 64;   // longer chains are added in ordered blocks of this many partials
 constexpr int kFar = 1 << 30;      // "no row end in sight" in tile-relative positions
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -218,6 +219,7 @@ __global__ void spmm_stream_plan(StreamArgs a) {
   int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (t == 0) {
     a.hdr[kSHdrNumLong] = 0;
+    a.hdr[kSHdrNumBlocks] = 0;
     a.hdr[kSHdrError] = load_ptr(a.ptr, a.n_dst, a.ptr_bytes) > a.nnz ? kSErrEdgeCount : kSErrNone;
   }
   if (t >= a.max_tiles) return;
@@ -561,6 +563,244 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream(StreamArgs 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Lean variant of the walk for the shapes that carry the large graphs: rows of exactly 32 * CB bytes
+// (128 / 256 / 512 bytes: every lane owns CB bytes of every row), no edge values, relations, targets or
+// accumulation, 16-byte cp.async staging, one stage per warp. Same tiles, same order of additions, same
+// partials as spmm_stream (results are bit-identical); what differs is the instruction count per edge:
+// tile-relative 32-bit positions and source ids, a running shared-memory pointer instead of per-run
+// address arithmetic, no per-lane column predicates, and a full-stage copy loop without bounds tests.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int CB>
+struct FastAcc;
+
+// fp32 rows: the shared-memory words are the addends; CB / 8 packed pairs.
+template <int CB>
+struct FastAcc<float, CB> {
+  static constexpr int P = CB / 8 > 0 ? CB / 8 : 1;
+  unsigned long long p[P];
+  float s;  // CB == 4: one scalar
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < P; ++i) p[i] = 0ull;
+    s = 0.f;
+  }
+  // adds the CB bytes at shared address `addr`
+  __device__ __forceinline__ void add(uint32_t addr) {
+    if (CB == 4) {
+      s += lds_f32(addr);
+    } else if (CB == 8) {
+      unsigned long long v;
+      asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
+      asm("add.rn.f32x2 %0, %0, %1;" : "+l"(p[0]) : "l"(v));
+    } else {
+      unsigned long long v0, v1;
+      asm volatile("ld.shared.v2.b64 {%0,%1}, [%2];" : "=l"(v0), "=l"(v1) : "r"(addr));
+      asm("add.rn.f32x2 %0, %0, %1;" : "+l"(p[0]) : "l"(v0));
+      asm("add.rn.f32x2 %0, %0, %1;" : "+l"(p[P > 1 ? 1 : 0]) : "l"(v1));
+    }
+  }
+  static constexpr int EL = CB / 4;
+  __device__ __forceinline__ void get(float *f) const {
+    if (CB == 4) {
+      f[0] = s;
+    } else {
+#pragma unroll
+      for (int i = 0; i < P; ++i) asm("mov.b64 {%0,%1}, %2;" : "=f"(f[2 * i]), "=f"(f[2 * i + 1]) : "l"(p[i]));
+    }
+  }
+};
+
+// bf16 rows: every 32-bit word holds two values; low half << 16 and high half masked are the fp32 addends.
+template <int CB>
+struct FastAcc<__nv_bfloat16, CB> {
+  static constexpr int P = CB / 4;  // one packed pair per 32-bit word
+  static constexpr int EL = CB / 2;
+  unsigned long long p[P];
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < P; ++i) p[i] = 0ull;
+  }
+  __device__ __forceinline__ void add(uint32_t addr) {
+    uint32_t w[P];
+    lds_words<P>(w, addr);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      unsigned long long v;
+      asm("mov.b64 %0, {%1,%2};" : "=l"(v) : "r"(w[i] << 16), "r"(w[i] & 0xffff0000u));
+      asm("add.rn.f32x2 %0, %0, %1;" : "+l"(p[i]) : "l"(v));
+    }
+  }
+  __device__ __forceinline__ void get(float *f) const {
+#pragma unroll
+    for (int i = 0; i < P; ++i) asm("mov.b64 {%0,%1}, %2;" : "=f"(f[2 * i]), "=f"(f[2 * i + 1]) : "l"(p[i]));
+  }
+};
+
+template <typename T, int CB, typename IdxT>
+__global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(StreamArgs a) {
+  using C = Chunk<T, CB>;
+  using Acc = FastAcc<T, CB>;
+  constexpr int EL = C::kElems;
+  constexpr int W = C::kWords;
+  constexpr int RB = 32 * CB;                        // bytes per row
+  constexpr int B = kStageBytes / RB > 32 ? 32 : kStageBytes / RB;  // edges per stage
+  constexpr int CPR = RB / 16;                       // 16-byte chunks per row
+  constexpr int RPI = 32 / CPR;                      // rows per copy instruction
+  constexpr int NCOPY = B * CPR / 32;                // copy instructions per full stage
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const uint32_t sl = smem_u32(smem + static_cast<size_t>(warp) * (B * RB));
+  const uint32_t my = sl + lane * CB;                // this lane's columns of the stage's first row
+  const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
+  const uint8_t *x = reinterpret_cast<const uint8_t *>(a.x);
+  uint8_t *y = reinterpret_cast<uint8_t *>(a.y) + lane * CB;
+  const int64_t e_total = stream_edge_total(a);
+  const int64_t n_tiles = (e_total + a.tile - 1) / a.tile;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * kSWarps + warp;
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * kSWarps;
+  const bool mean = a.reduce == CXG_MEAN;
+  // copy roles of this lane: row (lane / CPR) of every group of RPI rows, bytes [16 * (lane % CPR), +16) of it
+  const int jrow = lane / CPR;
+  const uint8_t *xlane = x + (lane % CPR) * 16;
+  const uint32_t cdst = sl + lane * 16;
+
+  auto zero_row = [&](int64_t r) {
+    uint32_t z[W];
+#pragma unroll
+    for (int i = 0; i < W; ++i) z[i] = 0u;
+    stg_words_stream<W>(y + r * RB, z);
+  };
+
+  if (e_total == 0) {
+    for (int64_t r = gwarp; r < a.n_dst; r += nwarps) zero_row(r);
+    return;
+  }
+
+  for (int64_t t = gwarp; t < n_tiles; t += nwarps) {
+    const int64_t tb = t * a.tile;
+    const int tile_len = static_cast<int>(min(static_cast<int64_t>(a.tile), e_total - tb));
+    const int n_stage = (tile_len + B - 1) / B;
+    int64_t row = a.tile_row[t];
+    if (t == 0)
+      for (int64_t r = 0; r < row; ++r) zero_row(r);
+    int64_t pbase = row;
+    auto load_ends = [&]() -> int {
+      const int64_t r = pbase + lane;
+      if (r >= a.n_dst) return kFar;
+      const int64_t v = load_ptr(a.ptr, r + 1, a.ptr_bytes) - tb;
+      return v > kFar ? kFar : static_cast<int>(v);
+    };
+    int pc = load_ends();
+    int rrel = 0;
+    int rend = __shfl_sync(0xffffffffu, pc, 0);
+    const int64_t rs64 = load_ptr(a.ptr, row, a.ptr_bytes) - tb;
+    int rstart = rs64 < -kFar ? -kFar : static_cast<int>(rs64);
+    const IdxT *idx_t = idx + tb;
+
+    auto load_nid = [&](int k) -> uint32_t {
+      const int pos = k * B + lane;
+      return (lane < B && pos < tile_len) ? static_cast<uint32_t>(load_idx_stream(idx_t + pos)) : 0u;
+    };
+    auto fill = [&](int k, uint32_t nid) {
+      const int cnt = tile_len - k * B;
+      if (cnt >= B) {  // full stage: no bounds test per copy
+#pragma unroll
+        for (int c = 0; c < NCOPY; ++c) {
+          const uint32_t nj = __shfl_sync(0xffffffffu, nid, c * RPI + jrow);
+          cp_async16(cdst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NCOPY; ++c) {
+          const uint32_t nj = __shfl_sync(0xffffffffu, nid, (c * RPI + jrow) & 31);
+          if (c * RPI + jrow < cnt) cp_async16(cdst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    fill(0, load_nid(0));
+    Acc acc;
+    acc.zero();
+    float f[EL];
+
+    for (int k = 0; k < n_stage; ++k) {
+      const uint32_t nid_next = load_nid(k + 1);
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncwarp();
+      const int sbase = k * B;
+      const int send = min(sbase + B, tile_len);
+      int pos = sbase;
+      uint32_t p = my;  // shared address of this lane's bytes of edge `pos`
+      while (pos < send) {
+        const int stop = min(send, rend);
+        int n = stop - pos;
+        pos = stop;
+        for (; n >= 4; n -= 4) {
+          acc.add(p);
+          acc.add(p + RB);
+          acc.add(p + 2 * RB);
+          acc.add(p + 3 * RB);
+          p += 4 * RB;
+        }
+        if (n & 2) {
+          acc.add(p);
+          acc.add(p + RB);
+          p += 2 * RB;
+        }
+        if (n & 1) {
+          acc.add(p);
+          p += RB;
+        }
+        if (pos == rend) {
+          acc.get(f);
+          acc.zero();
+          if (rstart < 0) {
+            float *pp = a.partials + (t * 2) * (RB / static_cast<int>(sizeof(T))) + lane * EL;
+#pragma unroll
+            for (int i = 0; i < EL; ++i) pp[i] = f[i];
+          } else {
+            if (mean) {
+              const float d = static_cast<float>(rend - rstart);
+#pragma unroll
+              for (int i = 0; i < EL; ++i) f[i] = __fdiv_rn(f[i], d);
+            }
+            uint32_t w[W];
+            C::pack(w, f);
+            stg_words_stream<W>(y + row * RB, w);
+          }
+          rstart = rend;
+          for (;;) {
+            ++row;
+            if (++rrel == 32) {
+              pbase = row;
+              rrel = 0;
+              pc = load_ends();
+            }
+            rend = __shfl_sync(0xffffffffu, pc, rrel);
+            if (rend != rstart) break;
+            zero_row(row);
+          }
+        }
+      }
+      __syncwarp();
+      if (k + 1 < n_stage) fill(k + 1, nid_next);
+    }
+    int64_t tail = -1;
+    if (row < a.n_dst && rstart < tile_len && rend > tile_len) {
+      acc.get(f);
+      const int which = rstart < 0 ? 0 : 1;
+      float *pp = a.partials + (t * 2 + which) * (RB / static_cast<int>(sizeof(T))) + lane * EL;
+#pragma unroll
+      for (int i = 0; i < EL; ++i) pp[i] = f[i];
+      if (which) tail = row;
+    }
+    if (lane == 0) a.tail_row[t] = tail;
+  }
+}
+
 // VW consecutive fp32 partial columns (VW = 4 when the row width allows, else 1).
 template <int VW>
 struct PVec {
@@ -613,10 +853,22 @@ __global__ void __launch_bounds__(256) spmm_stream_fix(StreamArgs a) {
     const int64_t t_last = (re - 1) / a.tile;
     const int64_t m = t_last - t + 1;  // partials in the chain
     if (m > kSeqPartials) {
+      // left to the two long-chain kernels: claim a slot and one entry of the block table per 64 partials
+      const int nb = static_cast<int>((m + kSeqPartials - 1) / kSeqPartials);
+      int slot = 0, base = 0;
       if (lane == 0) {
-        int slot = atomicAdd(a.hdr + kSHdrNumLong, 1);
-        if (slot < a.max_long) a.long_tiles[slot] = t;
+        slot = atomicAdd(a.hdr + kSHdrNumLong, 1);
+        base = atomicAdd(a.hdr + kSHdrNumBlocks, nb);
+        if (slot < a.max_long) {
+          a.long_tiles[slot] = t;
+          a.long_base[slot] = base;
+        }
       }
+      slot = __shfl_sync(0xffffffffu, slot, 0);
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (slot < a.max_long)
+        for (int b = lane; b < nb; b += 32)
+          if (base + b < a.max_blocks) a.block_owner[base + b] = slot;
       continue;
     }
     const int64_t out = a.targets != nullptr ? a.targets[r] : r;
@@ -632,60 +884,77 @@ __global__ void __launch_bounds__(256) spmm_stream_fix(StreamArgs a) {
   }
 }
 
-// Long chains: the m partials are dealt to the 8 warps of a CTA in contiguous blocks
-// [m*w/8, m*(w+1)/8); each warp adds its block in order starting from 0, then the 8
-// block sums are added in block order.
-template <typename T, int VW>
-__global__ void __launch_bounds__(256) spmm_stream_fix_long(StreamArgs a) {
-  __shared__ float stage[8][32 * VW];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Long chains, level 1: block g of the block table = partials [64 b, min(64 b + 64, m)) of the chain that owns
+// it; one warp adds them in order and leaves the block's sum in block_sums[g].
+template <int VW>
+__global__ void __launch_bounds__(256) spmm_stream_fix_long_blocks(StreamArgs a) {
   if (a.hdr[kSHdrError] != kSErrNone) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t e_total = stream_edge_total(a);
+  const int n_blocks = min(a.hdr[kSHdrNumBlocks], a.max_blocks);
+  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int g = gwarp; g < n_blocks; g += nwarps) {
+    const int slot = a.block_owner[g];
+    const int64_t t = a.long_tiles[slot];
+    const int64_t r = a.tail_row[t];
+    if (r < 0 || r >= a.n_dst) continue;
+    const int64_t re = min(load_ptr(a.ptr, r + 1, a.ptr_bytes), e_total);
+    const int64_t m = (re - 1) / a.tile - t + 1;
+    const int64_t kb = static_cast<int64_t>(g - a.long_base[slot]) * kSeqPartials;
+    const int64_t ke = min(kb + kSeqPartials, m);
+    for (int c = lane * VW; c < a.width; c += 32 * VW) {
+      // chain element 0 is the tail partial of tile t, element k > 0 the head partial of tile t + k
+      auto at = [&](int64_t k) { return a.partials + (k == 0 ? (t * 2 + 1) : ((t + k) * 2)) * a.width + c; };
+      PVec<VW> s;
+      s.load(at(kb));
+      int64_t k = kb + 1;
+      for (; k + 8 <= ke; k += 8) {
+        PVec<VW> v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u].load(at(k + u));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s.add(v[u]);
+      }
+      for (; k < ke; ++k) {
+        PVec<VW> v;
+        v.load(at(k));
+        s.add(v);
+      }
+#pragma unroll
+      for (int u = 0; u < VW; ++u) a.block_sums[static_cast<int64_t>(g) * a.width + c + u] = s.v[u];
+    }
+  }
+}
+
+// Long chains, level 2: one warp per chain adds its block sums in block order and writes the row.
+template <typename T, int VW>
+__global__ void __launch_bounds__(256) spmm_stream_fix_long_rows(StreamArgs a) {
+  if (a.hdr[kSHdrError] != kSErrNone) return;
+  const int lane = threadIdx.x & 31;
   const int64_t e_total = stream_edge_total(a);
   const int n_long = min(a.hdr[kSHdrNumLong], a.max_long);
+  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
   T *y = reinterpret_cast<T *>(a.y);
-  for (int i = blockIdx.x; i < n_long; i += gridDim.x) {
+  for (int i = gwarp; i < n_long; i += nwarps) {
     const int64_t t = a.long_tiles[i];
     const int64_t r = a.tail_row[t];
-    if (r < 0 || r >= a.n_dst) continue;  // uniform over the CTA
+    if (r < 0 || r >= a.n_dst) continue;
     const int64_t rb = load_ptr(a.ptr, r, a.ptr_bytes), re = min(load_ptr(a.ptr, r + 1, a.ptr_bytes), e_total);
     const int64_t m = (re - 1) / a.tile - t + 1;
-    const int64_t kb = m * warp / 8, ke = m * (warp + 1) / 8;
+    const int nb = static_cast<int>((m + kSeqPartials - 1) / kSeqPartials);
+    const int base = a.long_base[i];
+    if (base + nb > a.max_blocks) continue;
     const int64_t out = a.targets != nullptr ? a.targets[r] : r;
-    for (int c0 = 0; c0 < a.width; c0 += 32 * VW) {
-      const int c = c0 + lane * VW;
-      PVec<VW> s;
-      s.zero();
-      if (c < a.width) {
-        // chain element 0 is the tail partial of tile t, element k > 0 the head partial of tile t + k
-        auto at = [&](int64_t k) { return a.partials + (k == 0 ? (t * 2 + 1) : ((t + k) * 2)) * a.width + c; };
-        int64_t k = kb;
-        for (; k + 8 <= ke; k += 8) {
-          PVec<VW> v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) v[u].load(at(k + u));
-#pragma unroll
-          for (int u = 0; u < 8; ++u) s.add(v[u]);
-        }
-        for (; k < ke; ++k) {
-          PVec<VW> v;
-          v.load(at(k));
-          s.add(v);
-        }
+    for (int c = lane * VW; c < a.width; c += 32 * VW) {
+      PVec<VW> s, v;
+      s.load(a.block_sums + static_cast<int64_t>(base) * a.width + c);
+      for (int b = 1; b < nb; ++b) {
+        v.load(a.block_sums + static_cast<int64_t>(base + b) * a.width + c);
+        s.add(v);
       }
-#pragma unroll
-      for (int u = 0; u < VW; ++u) stage[warp][lane * VW + u] = s.v[u];
-      __syncthreads();
-      if (warp == 0 && c < a.width) {
-        PVec<VW> tot;
-#pragma unroll
-        for (int u = 0; u < VW; ++u) tot.v[u] = stage[0][lane * VW + u];
-#pragma unroll
-        for (int w = 1; w < 8; ++w)
-#pragma unroll
-          for (int u = 0; u < VW; ++u) tot.v[u] += stage[w][lane * VW + u];
-        finish_row<T, VW>(a, tot, y + out * a.width + c, re - rb);
-      }
-      __syncthreads();
+      finish_row<T, VW>(a, s, y + out * a.width + c, re - rb);
     }
   }
 }
@@ -723,6 +992,32 @@ cudaError_t launch_stream1(const StreamArgs &a, int cb, int nv, int valmode, int
                            cudaStream_t st) {
   return a.mode == kModeBulk ? launch_stream2<T, IdxT, true>(a, cb, nv, valmode, grid, smem, st)
                              : launch_stream2<T, IdxT, false>(a, cb, nv, valmode, grid, smem, st);
+}
+
+template <typename T, int CB, typename IdxT>
+cudaError_t launch_fast3(const StreamArgs &a, int grid, cudaStream_t st) {
+  constexpr int RB = 32 * CB;
+  constexpr int B = kStageBytes / RB > 32 ? 32 : kStageBytes / RB;
+  const size_t smem = static_cast<size_t>(B) * RB * kSWarps;
+  auto k = spmm_stream_fast<T, CB, IdxT>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  k<<<grid, kSThreads, smem, st>>>(a);
+  return cudaSuccess;
+}
+
+template <typename T, typename IdxT>
+cudaError_t launch_fast2(const StreamArgs &a, int cb, int grid, cudaStream_t st) {
+  if (cb == 4) return launch_fast3<T, 4, IdxT>(a, grid, st);
+  if (cb == 8) return launch_fast3<T, 8, IdxT>(a, grid, st);
+  return launch_fast3<T, 16, IdxT>(a, grid, st);
+}
+
+cudaError_t launch_fast(const StreamArgs &a, int dtype, int cb, int idx_bytes, int grid, cudaStream_t st) {
+  if (dtype == CXG_F32)
+    return idx_bytes == 8 ? launch_fast2<float, int64_t>(a, cb, grid, st) : launch_fast2<float, int32_t>(a, cb, grid, st);
+  return idx_bytes == 8 ? launch_fast2<__nv_bfloat16, int64_t>(a, cb, grid, st)
+                        : launch_fast2<__nv_bfloat16, int32_t>(a, cb, grid, st);
 }
 
 }  // namespace
@@ -764,11 +1059,20 @@ int stream_layout(int64_t nnz, int64_t width, int tile, StreamLayout *L) {
   L->long_tiles = off;
   int64_t max_long = max_tiles / kSeqPartials + 1;
   off = align_up(off + max_long * sizeof(int64_t), 256);
+  L->long_base = off;
+  off = align_up(off + max_long * sizeof(int32_t), 256);
+  // a chain of m > 64 partials has ceil(m / 64) <= m / 64 + 1 blocks; chains are disjoint in tiles
+  int64_t max_blocks = max_tiles / kSeqPartials + max_long + 1;
+  L->block_owner = off;
+  off = align_up(off + max_blocks * sizeof(int32_t), 256);
+  L->block_sums = off;
+  off = align_up(off + static_cast<size_t>(max_blocks) * width * sizeof(float), 256);
   L->partials = off;
   off = align_up(off + static_cast<size_t>(max_tiles) * 2 * width * sizeof(float), 256);
   L->total = off;
   L->max_tiles = max_tiles;
   L->max_long = static_cast<int>(max_long);
+  L->max_blocks = static_cast<int>(max_blocks);
   return CXG_OK;
 }
 
@@ -795,6 +1099,10 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
   a.tile_row = reinterpret_cast<int64_t *>(ws + L.tile_row);
   a.tail_row = reinterpret_cast<int64_t *>(ws + L.tail_row);
   a.long_tiles = reinterpret_cast<int64_t *>(ws + L.long_tiles);
+  a.long_base = reinterpret_cast<int32_t *>(ws + L.long_base);
+  a.block_owner = reinterpret_cast<int32_t *>(ws + L.block_owner);
+  a.block_sums = reinterpret_cast<float *>(ws + L.block_sums);
+  a.max_blocks = L.max_blocks;
   a.partials = reinterpret_cast<float *>(ws + L.partials);
   a.max_tiles = L.max_tiles;
   a.max_long = L.max_long;
@@ -821,7 +1129,13 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
   spmm_stream_plan<<<pb, 256, 0, st>>>(a);
   const int grid = kNumSM * kCtasPerSM;
   cudaError_t e;
-  if (d->dtype == CXG_F32)
+  // the lean kernel covers full-warp rows without per-edge extras; ids are kept as 32-bit there (a feature matrix
+  // of 2^32 rows of 128 bytes would not fit the device)
+  const bool fast = row_bytes == 32 * cb && valmode == 0 && a.mode == kModeCpAsync && d->edge_rel == nullptr &&
+                    d->targets == nullptr && !a.accumulate && !(d->flags & CXG_SPMM_GENERIC_WALK);
+  if (fast) {
+    e = launch_fast(a, d->dtype, cb, d->idx_bytes, grid, st);
+  } else if (d->dtype == CXG_F32)
     e = d->idx_bytes == 8 ? launch_stream1<float, int64_t>(a, cb, nv, valmode, grid, smem, st)
                           : launch_stream1<float, int32_t>(a, cb, nv, valmode, grid, smem, st);
   else
@@ -829,24 +1143,29 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
                           : launch_stream1<__nv_bfloat16, int32_t>(a, cb, nv, valmode, grid, smem, st);
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_spmm_csr: %s", cudaGetErrorString(e));
   const bool v4 = a.width % 4 == 0;
+  const int fg = kNumSM * 8;
   if (d->dtype == CXG_F32) {
     if (v4) {
-      spmm_stream_fix<float, 4><<<kNumSM * 8, 256, 0, st>>>(a);
-      spmm_stream_fix_long<float, 4><<<kNumSM * 2, 256, 0, st>>>(a);
+      spmm_stream_fix<float, 4><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_blocks<4><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_rows<float, 4><<<kNumSM, 256, 0, st>>>(a);
     } else {
-      spmm_stream_fix<float, 1><<<kNumSM * 8, 256, 0, st>>>(a);
-      spmm_stream_fix_long<float, 1><<<kNumSM * 2, 256, 0, st>>>(a);
+      spmm_stream_fix<float, 1><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_blocks<1><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_rows<float, 1><<<kNumSM, 256, 0, st>>>(a);
     }
   } else {
     if (v4) {
-      spmm_stream_fix<__nv_bfloat16, 4><<<kNumSM * 8, 256, 0, st>>>(a);
-      spmm_stream_fix_long<__nv_bfloat16, 4><<<kNumSM * 2, 256, 0, st>>>(a);
+      spmm_stream_fix<__nv_bfloat16, 4><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_blocks<4><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_rows<__nv_bfloat16, 4><<<kNumSM, 256, 0, st>>>(a);
     } else {
-      spmm_stream_fix<__nv_bfloat16, 1><<<kNumSM * 8, 256, 0, st>>>(a);
-      spmm_stream_fix_long<__nv_bfloat16, 1><<<kNumSM * 2, 256, 0, st>>>(a);
+      spmm_stream_fix<__nv_bfloat16, 1><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_blocks<1><<<fg, 256, 0, st>>>(a);
+      spmm_stream_fix_long_rows<__nv_bfloat16, 1><<<kNumSM, 256, 0, st>>>(a);
     }
   }
-  count_launches(4);
+  count_launches(5);
   return check_launch("cxg_spmm_csr (streaming)");
 }
 

@@ -5,7 +5,7 @@
 namespace cxg {
 
 // Header words of the streaming workspace.
-enum { kSHdrNumLong = 0, kSHdrError = 63 };  // word 63 is the error word of every SpMM workspace header
+enum { kSHdrNumLong = 0, kSHdrNumBlocks = 1, kSHdrError = 63 };  // word 63 is the error word of every SpMM workspace header
 // Values of the error word.
 enum { kSErrNone = 0, kSErrTimeout = 1, kSErrEdgeCount = 2 };
 // Row fetch variants: 16-byte async copies into shared memory (default), one bulk
@@ -33,19 +33,23 @@ struct StreamArgs {
   int slot_offset;  // offset of the row slots inside a warp's shared memory
   int warp_smem;    // shared memory per warp
   int max_long;
+  int max_blocks;
   int cpr_shift;  // log2(16-byte chunks per row), -1 when not a power of two
   int mode;       // how feature rows are fetched: kModeCpAsync / kModeBulk
   int32_t *hdr;
   int64_t *tile_row;    // row that owns the first edge of each tile
   int64_t *tail_row;    // row left unfinished at the end of each tile, or -1
   int64_t *long_tiles;  // tiles whose unfinished row spans more than 64 tiles
+  int32_t *long_base;   // first entry of each such chain in the block table
+  int32_t *block_owner; // block table: the chain (slot of long_tiles) every block of 64 partials belongs to
+  float *block_sums;    // [block][width]: sum of a block's partials
   float *partials;      // [tile][2][width]: head partial, tail partial
 };
 
 struct StreamLayout {
-  size_t hdr, tile_row, tail_row, long_tiles, partials, total;
+  size_t hdr, tile_row, tail_row, long_tiles, long_base, block_owner, block_sums, partials, total;
   int64_t max_tiles;
-  int max_long;
+  int max_long, max_blocks;
 };
 
 // True when the descriptor can take the streaming path (16-byte rows up to 1 KiB, no edge mask).

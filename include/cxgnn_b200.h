@@ -56,6 +56,9 @@ extern "C" {
    CXG_ETIMEOUT, kernels return, nothing written out of bounds) can be exercised. Use it
    with a short cxg_set_wait_limit_cycles. */
 #define CXG_SPMM_TEST_STALL 8u
+/* Measurement aid: rows of 128 / 256 / 512 bytes without edge values normally take a leaner
+   instantiation of the tiled walk; this flag keeps them on the general one. Same results. */
+#define CXG_SPMM_GENERIC_WALK 16u
 
 const char *cxg_last_error_string(void);
 int cxg_abi_version(void);

@@ -96,8 +96,8 @@ ORC_API void orc_spmm_csr(const int64_t *ptr, const int64_t *idx, const void *x,
  * reference's: the edge array is cut into tiles of `tile` edges; a row inside one tile
  * is summed sequentially (identical to orc_spmm_csr); a row that crosses tile borders
  * is summed per tile (each partial starting from 0), and its m partials are then added
- * in tile order: sequentially when m <= 64, otherwise in 8 contiguous blocks
- * [m*w/8, m*(w+1)/8) that are each added from 0 and then joined in block order.
+ * in tile order: sequentially when m <= 64, otherwise in blocks of 64 consecutive
+ * partials that are each added in order and then joined in block order.
  */
 ORC_API void orc_spmm_csr_tiled(const int64_t *ptr, const int64_t *idx, const void *x, void *y,
                                 const float *edge_val, const int32_t *edge_rel, int64_t rel_stride,
@@ -137,12 +137,12 @@ ORC_API void orc_spmm_csr_tiled(const int64_t *ptr, const int64_t *idx, const vo
         for (int64_t k = 1; k < m; ++k)
           for (int c = 0; c < width; ++c) tot[c] += parts[k * width + c];
       } else {
-        for (int w = 0; w < 8; ++w) {
-          int64_t kb = m * w / 8, ke = m * (w + 1) / 8;
-          for (int c = 0; c < width; ++c) acc[c] = 0.f;
-          for (int64_t k = kb; k < ke; ++k)
+        for (int64_t kb = 0; kb < m; kb += 64) {
+          int64_t ke = kb + 64 < m ? kb + 64 : m;
+          memcpy(acc, parts + kb * width, sizeof(float) * (size_t)width);
+          for (int64_t k = kb + 1; k < ke; ++k)
             for (int c = 0; c < width; ++c) acc[c] += parts[k * width + c];
-          for (int c = 0; c < width; ++c) tot[c] = (w == 0) ? acc[c] : tot[c] + acc[c];
+          for (int c = 0; c < width; ++c) tot[c] = (kb == 0) ? acc[c] : tot[c] + acc[c];
         }
       }
       free(parts);
