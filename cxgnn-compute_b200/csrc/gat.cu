@@ -612,6 +612,89 @@ extern "C" int cxg_gat_scores_backward(const float *g_src, const float *g_dst, c
   return check_launch("cxg_gat_scores_backward");
 }
 
+namespace cxg {
+namespace {
+constexpr int kAttGradCtas = kNumSM * 2;
+
+// Stage 1 of the attention-vector gradients: CTA b owns a contiguous chunk of rows; thread (sub, col) adds
+// g[r, h(col)] * feat[r, col] over the chunk's rows r = first + sub, first + sub + nsub, ...; the nsub partial sums of
+// a column are added in sub order and written to part[b][0 | 1][col] (0: att_src, 1: att_dst).
+__global__ void __launch_bounds__(kThreads) gat_att_grad_partial(const float *feat, const float *g_src, const float *g_dst,
+                                                                 float *part, int64_t n_src, int64_t n_dst, int heads,
+                                                                 int c) {
+  __shared__ float sh[2][kThreads];
+  const int width = heads * c;
+  const int nsub = width <= kThreads ? kThreads / width : 1;
+  const int64_t per = (n_src + gridDim.x - 1) / gridDim.x;
+  const int64_t first = blockIdx.x * per, last = min(n_src, first + per);
+  for (int col0 = 0; col0 < width; col0 += kThreads) {
+    const int sub = threadIdx.x / width, col = col0 + (width <= kThreads ? threadIdx.x % width : threadIdx.x);
+    const bool on = col < width && sub < nsub;
+    const int h = on ? col / c : 0;
+    float as = 0.f, ad = 0.f;
+    if (on)
+      for (int64_t r = first + sub; r < last; r += nsub) {
+        const float f = __ldg(feat + r * width + col);
+        as = fmaf(__ldg(g_src + r * heads + h), f, as);
+        if (r < n_dst) ad = fmaf(__ldg(g_dst + r * heads + h), f, ad);
+      }
+    sh[0][threadIdx.x] = as;
+    sh[1][threadIdx.x] = ad;
+    __syncthreads();
+    if (on && sub == 0) {
+      for (int u = 1; u < nsub; ++u) {
+        as += sh[0][u * width + threadIdx.x];
+        ad += sh[1][u * width + threadIdx.x];
+      }
+      part[(static_cast<int64_t>(blockIdx.x) * 2) * width + col] = as;
+      part[(static_cast<int64_t>(blockIdx.x) * 2 + 1) * width + col] = ad;
+    }
+    __syncthreads();
+  }
+}
+
+// Stage 2: the partials of every column are added in CTA order.
+__global__ void __launch_bounds__(kThreads) gat_att_grad_final(const float *part, float *grad_att_src, float *grad_att_dst,
+                                                               int n_part, int width) {
+  const int col = blockIdx.x * kThreads + threadIdx.x;
+  if (col >= width) return;
+  float as = 0.f, ad = 0.f;
+  for (int b = 0; b < n_part; ++b) {
+    as += part[(static_cast<int64_t>(b) * 2) * width + col];
+    ad += part[(static_cast<int64_t>(b) * 2 + 1) * width + col];
+  }
+  grad_att_src[col] = as;
+  grad_att_dst[col] = ad;
+}
+}  // namespace
+}  // namespace cxg
+
+extern "C" int cxg_gat_att_grad_workspace_size(int heads, int c, size_t *bytes) {
+  CXG_REQUIRE(bytes != nullptr && heads > 0 && c > 0, CXG_EINVAL, "cxg_gat_att_grad_workspace_size: bad arguments");
+  *bytes = static_cast<size_t>(kAttGradCtas) * 2 * heads * c * sizeof(float);
+  return CXG_OK;
+}
+
+extern "C" int cxg_gat_att_grad(const float *feat, const float *g_src, const float *g_dst, float *grad_att_src,
+                                float *grad_att_dst, int64_t n_src, int64_t n_dst, int heads, int c, void *workspace,
+                                size_t workspace_bytes, void *stream) {
+  CXG_REQUIRE(n_src >= 0 && n_dst >= 0 && n_dst <= n_src && heads > 0 && c > 0, CXG_EINVAL, "cxg_gat_att_grad: bad sizes");
+  CXG_REQUIRE(grad_att_src && grad_att_dst, CXG_ENULL, "cxg_gat_att_grad: NULL output");
+  CXG_REQUIRE(n_src == 0 || (feat && g_src && (g_dst || n_dst == 0)), CXG_ENULL, "cxg_gat_att_grad: NULL argument");
+  size_t need = 0;
+  cxg_gat_att_grad_workspace_size(heads, c, &need);
+  CXG_REQUIRE(workspace != nullptr && workspace_bytes >= need, CXG_EWORKSPACE,
+              "cxg_gat_att_grad: workspace %zu bytes, need %zu", workspace_bytes, need);
+  cudaStream_t st = as_stream(stream);
+  const int width = heads * c;
+  float *part = static_cast<float *>(workspace);
+  gat_att_grad_partial<<<kAttGradCtas, kThreads, 0, st>>>(feat, g_src, g_dst, part, n_src, n_dst, heads, c);
+  gat_att_grad_final<<<(width + kThreads - 1) / kThreads, kThreads, 0, st>>>(part, grad_att_src, grad_att_dst, kAttGradCtas,
+                                                                             width);
+  count_launches(2);
+  return check_launch("cxg_gat_att_grad");
+}
+
 extern "C" int cxg_head_sum(const void *in, void *out, int64_t n_row, int heads, int feat, int dtype, void *stream) {
   CXG_REQUIRE(n_row >= 0 && heads > 0 && feat > 0 && (dtype == CXG_F32 || dtype == CXG_BF16), CXG_EINVAL,
               "cxg_head_sum: bad arguments");

@@ -363,6 +363,9 @@ class MyGATConv(torch.nn.Module):
             self.bias = None
         self.edge_softmax_schedule = "fused"
         self.fused_scores = True  # both attention scores in one kernel instead of two multiply + sum pairs
+        # edge softmax and weighted aggregation as ONE kernel where the shape allows (the reference's sequence of
+        # edge_attention + SpMMValOP otherwise, or when set to False)
+        self.fused_aggregate = True
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -402,12 +405,21 @@ class MyGATConv(torch.nn.Module):
         else:  # the reference's two multiply + sum pairs
             alpha_src = (x_src * self.att_src).sum(dim=-1).view(-1, H)
             alpha_dst = (x_src[:num_dst] * self.att_dst).sum(dim=-1).view(-1, H)
-        edge_value = self.edge_softmax(ptr=ptr, idx=idx, att_src=alpha_src.contiguous(), att_dst=alpha_dst.contiguous(),
-                                       num_edge=num_edge, relu_l=self.negative_slope)
-        if self.heads == 1:
-            out = sage_sum_forward_edge_value(x_src.contiguous(), ptr, idx, edge_value.squeeze(-1).contiguous(), num_dst)
+        if (self.fused_aggregate and self.edge_softmax_schedule == "fused"
+                and cxgnncomp_backend.gat_fused_supported(x_src)):
+            # score + LeakyReLU + softmax + weighted sum in one walk over the edges: no [E, H] tensor
+            out, _, _ = cxgnncomp_backend.gat_fused(x_src.contiguous(), alpha_src.contiguous(), alpha_dst.contiguous(),
+                                                    ptr, idx, num_dst, self.negative_slope)
+            if self.heads == 1:
+                out = out.squeeze(1)
         else:
-            out = SpMMValOP.apply(x_src.contiguous(), ptr, idx, edge_value, num_dst)
+            edge_value = self.edge_softmax(ptr=ptr, idx=idx, att_src=alpha_src.contiguous(),
+                                           att_dst=alpha_dst.contiguous(), num_edge=num_edge, relu_l=self.negative_slope)
+            if self.heads == 1:
+                out = sage_sum_forward_edge_value(x_src.contiguous(), ptr, idx, edge_value.squeeze(-1).contiguous(),
+                                                  num_dst)
+            else:
+                out = SpMMValOP.apply(x_src.contiguous(), ptr, idx, edge_value, num_dst)
         if self.concat:
             out = out.view(-1, H * C)
         elif out.dim() == 3:

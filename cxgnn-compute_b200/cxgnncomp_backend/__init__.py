@@ -557,6 +557,10 @@ _gat_scores = _sig("cxg_gat_scores", [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctype
 _gat_scores_bwd = _sig("cxg_gat_scores_backward", [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp])
 
 
+_gat_att_grad_ws = _sig("cxg_gat_att_grad_workspace_size", [ctypes.c_int, ctypes.c_int, ctypes.POINTER(_sz)])
+_gat_att_grad = _sig("cxg_gat_att_grad", [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp, _sz, _vp])
+
+
 class _GatScoresFunction(torch.autograd.Function):
     """Both attention scores of a GAT layer from the transformed features in one kernel (the reference writes
     them as two multiply + sum pairs, cxgnncomp/graph_conv.py:470-474)."""
@@ -584,10 +588,14 @@ class _GatScoresFunction(torch.autograd.Function):
             with torch.cuda.device(feat.device):
                 _check(_gat_scores_bwd(_p(g_src), _p(g_dst), _p(att_src), _p(att_dst), _p(grad_feat), n, ctx.num_dst,
                                        h, c, _stream()), "cxg_gat_scores_backward")
-        if ctx.needs_input_grad[1]:
-            grad_as = torch.einsum("nh,nhc->hc", g_src, feat).view_as(att_src)
-        if ctx.needs_input_grad[2]:
-            grad_ad = torch.einsum("nh,nhc->hc", g_dst, feat[:ctx.num_dst]).view_as(att_dst)
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            grad_as, grad_ad = torch.empty_like(att_src), torch.empty_like(att_dst)
+            need = _sz(0)
+            _check(_gat_att_grad_ws(h, c, ctypes.byref(need)), "cxg_gat_att_grad_workspace_size")
+            ws = _workspace(feat.device, need.value)
+            with torch.cuda.device(feat.device):
+                _check(_gat_att_grad(_p(feat), _p(g_src), _p(g_dst), _p(grad_as), _p(grad_ad), n, ctx.num_dst, h, c,
+                                     _p(ws), ws.numel(), _stream()), "cxg_gat_att_grad")
         return grad_feat, grad_as, grad_ad, None
 
 
@@ -758,6 +766,82 @@ def edge_attention(ptr, idx, att_dst, att_src, num_edge, relu_l):
     """softmax over each destination's edges of LeakyReLU(att_dst[d] + att_src[src]) -> [E, H]
     (binding.cpp:22-23, keyword arguments ptr, idx, att_dst, att_src, num_edge, relu_l)."""
     return _EdgeSoftmaxFunction.apply(ptr, idx, att_dst, att_src, int(num_edge), float(relu_l))
+
+
+_gatf_ws = _sig("cxg_gat_fused_workspace_size", [_i64, _i64, _int, _int, ctypes.POINTER(_sz)])
+_gatf_fwd = _sig("cxg_gat_fused_forward", [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _f,
+                                           _vp, _sz, _vp])
+_gatf_bwd = _sig("cxg_gat_fused_backward", [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                            _i64, _i64, _int, _int, _f, _vp, _sz, _vp])
+
+
+def gat_fused_supported(x_src):
+    """True when cxg_gat_fused_forward covers this [N, H, C] feature tensor (fp32, H a power of two <= 16, rows of
+    128 / 256 / 512 bytes, a lane's share of a row inside one head)."""
+    if x_src.dim() != 3 or x_src.dtype != torch.float32 or not x_src.is_cuda:
+        return False
+    h, c = x_src.shape[1], x_src.shape[2]
+    row = h * c * 4
+    return h <= 16 and (h & (h - 1)) == 0 and row in (128, 256, 512) and (c * 4) % (row // 32) == 0
+
+
+class _GatFusedFunction(torch.autograd.Function):
+    """y = softmax-weighted neighbour sum of a GAT layer in one pass (cxg_gat_fused_forward); the backward
+    recomputes the edge probabilities from the saved row maxima and sums over the transposed graph."""
+
+    @staticmethod
+    def forward(ctx, x_src, a_src, a_dst, ptr, idx, num_dst, slope):
+        _cuda(x_src, "x_src", (torch.float32,))
+        _cuda(a_src, "a_src", (torch.float32,))
+        _cuda(a_dst, "a_dst", (torch.float32,))
+        _cuda(ptr, "ptr", _INDEX_DTYPES)
+        _cuda(idx, "idx", _INDEX_DTYPES)
+        n = _num_rows(ptr, num_dst)
+        n_src, h, c = x_src.shape
+        if a_src.shape != (n_src, h) or a_dst.shape[0] < n or a_dst.shape[1] != h:
+            raise RuntimeError("gat_fused: a_src must be [n_src, H] and a_dst [num_dst, H]")
+        dev = x_src.device
+        y = torch.empty((n, h, c), dtype=torch.float32, device=dev)
+        row_max = torch.empty((n, h), dtype=torch.float32, device=dev)
+        row_sum = torch.empty((n, h), dtype=torch.float32, device=dev)
+        need = _sz(0)
+        _check(_gatf_ws(n, idx.shape[0], h, c, ctypes.byref(need)), "cxg_gat_fused_workspace_size")
+        ws = _workspace(dev, need.value)
+        with torch.cuda.device(dev):
+            _check(_gatf_fwd(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(x_src), _p(a_src), _p(a_dst),
+                             _p(y), _p(row_max), _p(row_sum), n, idx.shape[0], h, c, float(slope), _p(ws), ws.numel(),
+                             _stream()), "cxg_gat_fused_forward")
+        ctx.save_for_backward(x_src, a_src, a_dst, ptr, idx, y, row_max, row_sum)
+        ctx.n, ctx.slope = n, float(slope)
+        ctx.mark_non_differentiable(row_max, row_sum)
+        return y, row_max, row_sum
+
+    @staticmethod
+    def backward(ctx, dy, _gmax, _gsum):
+        x_src, a_src, a_dst, ptr, idx, y, row_max, row_sum = ctx.saved_tensors
+        n, (n_src, h, c) = ctx.n, x_src.shape
+        dev = x_src.device
+        dy = _cuda(dy.contiguous(), "grad_out", (torch.float32,))
+        t_ptr, t_idx, _, _ = _transposed_graph(ptr, idx, n, n_src)
+        dx = torch.empty_like(x_src)
+        d_as = torch.empty((n_src, h), dtype=torch.float32, device=dev)
+        d_ad = torch.empty((a_dst.shape[0], h), dtype=torch.float32, device=dev)
+        if a_dst.shape[0] > n:
+            d_ad[n:].zero_()
+        need = _sz(0)
+        _check(_gatf_ws(n, idx.shape[0], h, c, ctypes.byref(need)), "cxg_gat_fused_workspace_size")
+        ws = _workspace(dev, need.value)
+        with torch.cuda.device(dev):
+            _check(_gatf_bwd(_p(t_ptr), _p(t_idx), t_ptr.element_size(), t_idx.element_size(), _p(dy), _p(y), _p(x_src),
+                             _p(a_src), _p(a_dst), _p(row_max), _p(row_sum), _p(dx), _p(d_as), _p(d_ad), n_src, n,
+                             t_idx.shape[0], h, c, ctx.slope, _p(ws), ws.numel(), _stream()), "cxg_gat_fused_backward")
+        return dx, d_as, d_ad, None, None, None, None
+
+
+def gat_fused(x_src, a_src, a_dst, ptr, idx, num_dst, negative_slope):
+    """(y [num_dst, H, C], row_max [num_dst, H], row_sum [num_dst, H]): GAT aggregation of x_src [n_src, H, C] with
+    attention scores a_src [n_src, H], a_dst [num_dst, H]; differentiable in x_src, a_src, a_dst."""
+    return _GatFusedFunction.apply(x_src, a_src, a_dst, ptr, idx, int(num_dst), float(negative_slope))
 
 
 def edge_value_degree(ptr, num_dst, num_edge):

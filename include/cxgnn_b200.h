@@ -210,6 +210,34 @@ int cxg_edge_softmax_backward(const void *ptr, const void *idx, int ptr_bytes,
                               void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Fused GAT aggregation: score, LeakyReLU, edge softmax and weighted neighbour sum in one walk over the edges,
+ * without any [nnz, heads] array in memory. Replaces, for one layer, the sequence edge_attention ->
+ * sage_sum_forward_edge_value / SpMMValOP of MyGATConv.forward_many (cxgnncomp/graph_conv.py:458-496,
+ * src/cpp/src/edge_softmax.cu:3-95, src/cpp/src/aggr_kernel.cu:155-186,443-491).
+ *   forward:  y[r,h,:] = sum_e p[e,h] x[idx[e],h,:],  p = softmax over row r of leaky(a_dst[r,h] + a_src[idx[e],h]);
+ *             also row_max[r,h] and row_sum[r,h] (max and sum of exp(t - max) of the row; -1e30 / 0 for rows
+ *             without edges), which is all the backward needs to recompute p.
+ *   backward: walks the TRANSPOSED graph (t_ptr over the n_src sources, t_idx = destinations, as
+ *             cxg_csr_transpose builds it): dx [n_src, heads, c], d_a_src [n_src, heads] (both written, fixed
+ *             order) and d_a_dst [n_dst, heads] (zeroed, then added into with atomics).
+ * x [n_src, heads, c], y / dy [n_dst, heads, c] float32; heads a power of two <= 16; heads * c * 4 must be
+ * 128, 256 or 512 bytes (CXG_EUNSUPPORTED otherwise: use the separate kernels). exp is the fast __expf, like
+ * the reference's fast-math build; results agree with the three-pass formulation to fp32 rounding, not bit
+ * for bit (the running maximum changes the order of the roundings).
+ */
+int cxg_gat_fused_workspace_size(int64_t n_dst, int64_t nnz, int heads, int c, size_t *bytes);
+int cxg_gat_fused_forward(const void *ptr, const void *idx, int ptr_bytes, int idx_bytes, const float *x,
+                          const float *a_src, const float *a_dst, float *y, float *row_max, float *row_sum,
+                          int64_t n_dst, int64_t nnz, int heads, int c, float slope, void *workspace,
+                          size_t workspace_bytes, void *stream);
+int cxg_gat_fused_backward(const void *t_ptr, const void *t_idx, int ptr_bytes, int idx_bytes,
+                           const float *dy, const float *y, const float *x, const float *a_src,
+                           const float *a_dst, const float *row_max, const float *row_sum, float *dx,
+                           float *d_a_src, float *d_a_dst, int64_t n_src, int64_t n_dst, int64_t nnz,
+                           int heads, int c, float slope, void *workspace, size_t workspace_bytes,
+                           void *stream);
+
+/*
  * SDDMM on an edge list: out[e,h] = <src_feat[src[e],h,:], dst_feat[dst[e],:]>, src_feat
  * [n_src, heads, feat], out [n_edge, heads]. dst_per_head = 0: dst_feat is [n_dst, feat]
  * as in run_sddmm / sddmm_multihead (src/cpp/src/sddmm_host.cu:4-14, sddmm_kernel.cu:3-25);
@@ -260,6 +288,16 @@ int cxg_gat_scores(const float *feat, const float *att_src, const float *att_dst
 int cxg_gat_scores_backward(const float *g_src, const float *g_dst, const float *att_src,
                             const float *att_dst, float *grad_feat, int64_t n_src, int64_t n_dst,
                             int heads, int c, void *stream);
+/*
+ * Gradients of the two attention vectors of the same step (the reference leaves them to autograd through the
+ * multiply + sum pairs): grad_att_src[h, :] = sum_n g_src[n, h] feat[n, h, :] over n < n_src,
+ * grad_att_dst[h, :] = sum_n g_dst[n, h] feat[n, h, :] over n < n_dst, both [heads, c], in one pass over feat with a
+ * fixed two-level order of additions (contiguous row chunks, then the chunks in order).
+ */
+int cxg_gat_att_grad_workspace_size(int heads, int c, size_t *bytes);
+int cxg_gat_att_grad(const float *feat, const float *g_src, const float *g_dst, float *grad_att_src,
+                     float *grad_att_dst, int64_t n_src, int64_t n_dst, int heads, int c, void *workspace,
+                     size_t workspace_bytes, void *stream);
 
 /*
  * out[r, f] = sum over heads of in[r, h, f] (heads added in order into one fp32 accumulator): the head

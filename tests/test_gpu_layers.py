@@ -105,6 +105,15 @@ def test_gat_layer(cuda, heads, concat):
     conv.edge_softmax_schedule = "opwise"
     out2 = conv(x.cuda(), ptr.cuda(), idx.cuda(), 180, 180, idx.shape[0])
     assert rel_err(out2.detach().cpu(), ref.detach()) < 1e-5
+    # and so does the reference's sequence of separate kernels (edge_attention, then the weighted aggregation),
+    # forward and backward
+    conv.edge_softmax_schedule = "fused"
+    conv.fused_aggregate = False
+    xg3 = x.cuda().requires_grad_(True)
+    out3 = conv(xg3, ptr.cuda(), idx.cuda(), 180, 180, idx.shape[0])
+    assert rel_err(out3.detach().cpu(), ref.detach()) < 1e-5
+    out3.backward(go.cuda())
+    assert rel_err(xg3.grad.cpu(), xr.grad) < 1e-4
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
