@@ -7,7 +7,7 @@ compulsory bytes of one pass (every touched feature row once in, every output ro
 index stream, the row pointers) divided by the step time, inputs resident in HBM. `e2e` is the
 same metric through the `cxgnncomp_backend` call with the step's inputs copied from pinned host
 memory and its output copied back inside the timed region. `roofline` compares the SpMM call
-with the measured HBM copy bandwidth of this pool (MEASURED_PEAKS.json). `cpu_baseline` times the
+with the measured HBM copy bandwidth of the GPU (MEASURED_PEAKS.json next to this file, when present). `cpu_baseline` times the
 reference's CPU formulation (torch index_add_ / sparse.mm, all host threads) on a bounded row
 sample of the same workload.
 
@@ -48,6 +48,12 @@ WORKLOADS = {
 }
 DTYPES = {"bf16": torch.bfloat16, "f32": torch.float32}
 L2_FLUSH_BYTES = 256 << 20
+# Peer-copy bandwidth into one GPU over NVLink that the exchange is compared with: 770 GB/s per direction was
+# measured between B200s of the kind this benchmark targets (nominal 900); override with CXG_PEER_COPY_GBPS.
+PEER_COPY_GBPS = float(os.environ.get("CXG_PEER_COPY_GBPS", "770"))
+# what --exchange auto picks when the needed rows are few enough: "needed" (pack + NCCL all-to-all), "put" (one gather
+# kernel storing into the peers' buffers) or "putcopy" (pack + copy-engine copies into the peers' buffers)
+AUTO_EXCHANGE = os.environ.get("CXG_BENCH_AUTO_EXCHANGE", "put")
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tiled kernel on one GPU, from ncu
 # captures of these workloads (profiles/spmm_stream_papers.md); None where no capture exists.
 NCU_DRAM_BYTES = {"papers_like": 300.59e9, "papers_tenth": 24.67e9}
@@ -58,7 +64,7 @@ def load_peaks():
     if os.path.exists(path):
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier B200 copy-bandwidth measurement)"
 
 
 class ClockSampler:
@@ -205,15 +211,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("CXG_BENCH_WORKLOAD", "papers_like"),
                     choices=sorted(WORKLOADS))
-    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "needed"],
-                    help="multi-GPU feature exchange: one padded all-gather, or an all-to-all of only the rows each "
-                         "rank's edges name; auto takes the second when it moves under 80 %% of the rows")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "allgather", "needed", "put", "putcopy"],
+                    help="multi-GPU feature exchange: one padded all-gather; an all-to-all of only the rows each "
+                         "rank's edges name (needed); or the same rows stored into the peers' buffers over NVLink by one "
+                         "gather kernel (put) or by the copy engines (putcopy)")
     ap.add_argument("--exchange-chunks", type=int, default=int(os.environ.get("CXG_BENCH_EXCHANGE_CHUNKS", "0")),
                     help="needed-rows mode: cut every peer's rows into this many parts and send a part while the next "
                          "one is packed (0 = 4 parts on 2 GPUs, where it was measured; 1 part on more)")
-    ap.add_argument("--overlap", action="store_true",
-                    help="needed-rows mode: aggregate the own-source edges while the exchange is in flight (measured: "
-                         "no gain, the persistent aggregation kernel fills every SM and the NCCL kernel waits for it)")
+    ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
+                    help="aggregate the edges that read this rank's own rows while the exchange is in flight, then "
+                         "accumulate the rest (auto = off: at 2 GPUs the second pass over the output rows costs what "
+                         "the overlap hides, 45.1 vs 44.4 ms per step)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-layers", action="store_true",
                     help="skip the per-layer records of configurations 1, 2 and 4 (added at 1 GPU by default)")
@@ -264,17 +272,15 @@ def main():
         torch.cuda.empty_cache()
         exchange_mode = args.exchange
         remote_all = (world - 1) * part.shard_rows
-        if exchange_mode in ("auto", "needed"):
+        if exchange_mode in ("auto", "needed", "put", "putcopy"):
             ex = NeededRowsExchange(part, lptr, lidx, rank, n)
             frac = torch.tensor([ex.remote_rows() / max(remote_all, 1)], dtype=torch.float64, device=dev)
             dist.all_reduce(frac, op=dist.ReduceOp.MAX)
             if exchange_mode == "auto":
-                exchange_mode = "needed" if float(frac[0]) < 0.8 else "allgather"
-        if exchange_mode == "needed":
+                exchange_mode = AUTO_EXCHANGE if float(frac[0]) < 0.8 else "allgather"
+        if exchange_mode in ("needed", "put", "putcopy"):
             lidx = ex.lidx
             remote_rows = ex.remote_rows()
-            if args.overlap:
-                graph_own, graph_rem = ex.split_graph(lptr)
         else:
             ex = None
             lidx = part.to_gather_ids(lidx)
@@ -312,13 +318,32 @@ def main():
     b_alg_total = algorithmic_bytes(n, n, nnz, feat, elem, idx_bytes)
     b_alg_local = algorithmic_bytes(n_local, n, int(lptr[n_local]), feat, elem, idx_bytes)
 
+    putters = {}
+    if exchange_mode in ("put", "putcopy"):
+        from cxgnncomp.distributed import PeerExchange
+        put_chunks = args.exchange_chunks if args.exchange_chunks > 0 else 4
+        put_mode = "kernel" if exchange_mode == "put" else "copy"
+        try:
+            putters[x_full.data_ptr()] = PeerExchange(ex, x_full, send_buf, mode=put_mode, chunks=put_chunks)
+        except RuntimeError as e:  # raised on every rank together: no IPC between these processes
+            sys.stderr.write(f"peer mappings unavailable ({e}); using the NCCL all-to-all\n")
+            exchange_mode = "needed"
+    # Overlap: the edges whose source is one of this rank's own rows are aggregated while the remote rows travel,
+    # the rest is accumulated onto them afterwards (one more pass over the output rows)
+    overlap = ex is not None and args.overlap == "on"
     exchange_chunks = args.exchange_chunks if args.exchange_chunks > 0 else (4 if world == 2 else 1)
+    if overlap:
+        seg_graphs = ex.segment_graphs(lptr, 1)  # [own-source edges, remote-source edges]
+        comm_stream = torch.cuda.Stream()
+        chunk_events = [torch.cuda.Event()]
 
     def exchange(buf=None):
         """The feature buffer (x_full by default) receives what this rank's aggregation reads: every shard (one
         NCCL all-gather) or the rows its edges name (pack + one NCCL all-to-all)."""
         buf = x_full if buf is None else buf
-        if ex is not None:
+        if putters:
+            putters[buf.data_ptr()].exchange()
+        elif ex is not None:
             ex.exchange(buf, send_buf, chunks=exchange_chunks)
         else:
             exchange_features(buf, part, rank)
@@ -329,19 +354,28 @@ def main():
             return buf
         return ex.own(buf) if ex is not None else part.shard(buf, rank)
 
-    overlap = ex is not None and args.overlap
+    def aggregate_segments(buf, out, wait=True):
+        """Own-source edges first, then one accumulating pass over the edges that read remote rows as soon as the
+        exchange is complete (fixed order of additions)."""
+        main = torch.cuda.current_stream()
+        share = exchange_mode == "needed"  # NCCL's copy kernels need room on the SMs; copy engines do not
+        be.spmm_into(out, seg_graphs[0][0], seg_graphs[0][1], buf, n_local, share_sms=share)
+        if wait:
+            main.wait_event(chunk_events[0])
+        return be.spmm_into(out, seg_graphs[1][0], seg_graphs[1][1], buf, n_local, accumulate=True)
 
-    def step():
+    def step(buf=None, out=None):
+        buf = x_full if buf is None else buf
+        out = y if out is None else out
         if overlap:
-            # the edges that read this rank's own rows are aggregated while the remote rows are in flight,
-            # the rest is accumulated onto them afterwards
-            work = ex.exchange(x_full, send_buf, async_op=True)
-            be.spmm_into(y, graph_own[0], graph_own[1], x_full, n_local)
-            work.wait()
-            return be.spmm_into(y, graph_rem[0], graph_rem[1], x_full, n_local, accumulate=True)
+            comm_stream.wait_stream(torch.cuda.current_stream())  # the own rows of buf are in place
+            with torch.cuda.stream(comm_stream):
+                exchange(buf)
+                chunk_events[0].record(comm_stream)
+            return aggregate_segments(buf, out)
         if world > 1:
-            exchange()
-        return be.spmm_into(y, lptr, lidx, x_full, n_local)
+            exchange(buf)
+        return be.spmm_into(out, lptr, lidx, buf, n_local)
 
     def timed(fn, k):
         """k calls of fn, each between its own pair of events on the current stream, L2 flushed before."""
@@ -367,16 +401,19 @@ def main():
     # kernel-only time of the SpMM call (no exchange), for the roofline
     spmm_ms = timed(lambda: be.spmm_into(y, lptr, lidx, x_full, n_local), args.steps) / args.steps
     barrier()
+    # the segmented aggregation alone (rows already exchanged): what the step costs beyond it is exposed exchange
+    seg_ms = timed(lambda: aggregate_segments(x_full, y, wait=False), args.steps) / args.steps if overlap else spmm_ms
+    barrier()
     exch_ms = timed(exchange, args.steps) / args.steps if world > 1 else 0.0
     barrier()
     clocks = sampler.stop() if sampler else None
 
-    t = torch.tensor([ms_total, spmm_ms, exch_ms, float(remote_rows)], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, spmm_ms, exch_ms, float(remote_rows), seg_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t[0]) / args.steps
     spmm_ms = float(t[1])
-    exch_ms, remote_rows_max = float(t[2]), int(t[3])
+    exch_ms, remote_rows_max, seg_ms = float(t[2]), int(t[3]), float(t[4])
     value = b_alg_total / (ms_step * 1e-3) / 1e9
 
     # end to end: inputs from pinned host memory, result back to the host, every step
@@ -392,6 +429,8 @@ def main():
         # Double-buffered: the upload of step k+1 runs on its own stream while step k aggregates and step k-1's
         # result returns to the host (the link is full duplex), so a step costs max(upload, download), not their sum.
         xb, yb = [x_full, torch.empty_like(x_full)], [y, torch.empty_like(y)]
+        if putters:
+            putters[xb[1].data_ptr()] = PeerExchange(ex, xb[1], send_buf, mode=put_mode, chunks=put_chunks)
         s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
         ev_in = [torch.cuda.Event() for _ in range(2)]
         ev_comp = [torch.cuda.Event() for _ in range(2)]
@@ -406,9 +445,7 @@ def main():
                     ev_in[b].record(s_in)
                 s_main.wait_event(ev_in[b])
                 s_main.wait_event(ev_out[b])  # the download that last read this output buffer
-                if world > 1:
-                    exchange(xb[b])
-                be.spmm_into(yb[b], lptr, lidx, xb[b], n_local)
+                step(xb[b], yb[b])
                 ev_comp[b].record(s_main)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_comp[b])
@@ -425,6 +462,8 @@ def main():
         b_ev.record()
         b_ev.synchronize()
         e_ms = a_ev.elapsed_time(b_ev) / ksteps
+        if putters:
+            putters.pop(xb[1].data_ptr()).close()
         del xb, yb
         barrier()
         te = torch.tensor([e_ms], dtype=torch.float64, device=dev)
@@ -465,12 +504,14 @@ def main():
 
     exchange_info = None
     if world > 1:
-        # the exchange against the measured peer-copy rate of this pool (770 GB/s into each GPU)
+        # the exchange against the peer-copy rate into one GPU (PEER_COPY_GBPS)
         bytes_in = remote_rows_max * feat * elem
         exchange_info = {"mode": exchange_mode, "ms": exch_ms, "rows_into_busiest_gpu": remote_rows_max,
                          "bytes_into_busiest_gpu": bytes_in, "achieved_GBps": bytes_in / (exch_ms * 1e-3) / 1e9,
-                         "nvlink_peak_GBps": 770.0, "frac": bytes_in / (exch_ms * 1e-3) / 1e9 / 770.0,
-                         "allgather_rows_per_gpu": (world - 1) * part.shard_rows}
+                         "nvlink_peak_GBps": PEER_COPY_GBPS, "frac": bytes_in / (exch_ms * 1e-3) / 1e9 / PEER_COPY_GBPS,
+                         "allgather_rows_per_gpu": (world - 1) * part.shard_rows,
+                         "overlapped": overlap, "chunks": exchange_chunks, "aggregation_alone_ms": seg_ms,
+                         "exposed_ms": max(0.0, ms_step - seg_ms)}
     if rank == 0:
         line = {"metric": "spmm_algorithmic_hbm_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -478,8 +519,9 @@ def main():
                 "data": "synthetic",
                 "config": {"workload": args.workload, "description": desc, "nodes": n, "nnz": nnz, "feat": feat,
                            "idx_bytes": idx_bytes, "partition": f"rows by edge count over {world} GPU(s)",
-                           "exchange": exchange_mode + (" + overlap with own-source edges" if overlap else "") +
-                           (f" in {exchange_chunks} chunks" if ex is not None and exchange_chunks > 1 else ""),
+                           "exchange": exchange_mode + (f" in {exchange_chunks} chunks" if ex is not None and
+                                                        exchange_chunks > 1 else "") +
+                           (", overlapped with the aggregation of the rows already there" if overlap else ""),
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
                 "gpu_launches": int(launches), "roofline": roofline, "layers": layers, "exchange": exchange_info, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}

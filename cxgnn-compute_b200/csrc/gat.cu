@@ -614,11 +614,12 @@ extern "C" int cxg_gat_scores_backward(const float *g_src, const float *g_dst, c
 
 namespace cxg {
 namespace {
-constexpr int kAttGradCtas = kNumSM * 2;
+constexpr int kAttGradCtas = kNumSM * 8;
 
 // Stage 1 of the attention-vector gradients: CTA b owns a contiguous chunk of rows; thread (sub, col) adds
-// g[r, h(col)] * feat[r, col] over the chunk's rows r = first + sub, first + sub + nsub, ...; the nsub partial sums of
-// a column are added in sub order and written to part[b][0 | 1][col] (0: att_src, 1: att_dst).
+// g[r, h(col)] * feat[r, col] over the chunk's rows r = first + sub + j * nsub in four interleaved accumulators
+// (j mod 4) that are joined as (a0 + a1) + (a2 + a3); the nsub sums of a column are added in sub order and written
+// to part[b][0 | 1][col] (0: att_src, 1: att_dst).
 __global__ void __launch_bounds__(kThreads) gat_att_grad_partial(const float *feat, const float *g_src, const float *g_dst,
                                                                  float *part, int64_t n_src, int64_t n_dst, int heads,
                                                                  int c) {
@@ -631,40 +632,67 @@ __global__ void __launch_bounds__(kThreads) gat_att_grad_partial(const float *fe
     const int sub = threadIdx.x / width, col = col0 + (width <= kThreads ? threadIdx.x % width : threadIdx.x);
     const bool on = col < width && sub < nsub;
     const int h = on ? col / c : 0;
-    float as = 0.f, ad = 0.f;
-    if (on)
-      for (int64_t r = first + sub; r < last; r += nsub) {
-        const float f = __ldg(feat + r * width + col);
-        as = fmaf(__ldg(g_src + r * heads + h), f, as);
-        if (r < n_dst) ad = fmaf(__ldg(g_dst + r * heads + h), f, ad);
+    float as[4] = {0.f, 0.f, 0.f, 0.f}, ad[4] = {0.f, 0.f, 0.f, 0.f};
+    if (on) {
+      int64_t r = first + sub;
+      for (; r + 3 * nsub < last; r += 4 * nsub) {
+        float f[4], gs[4], gd[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t ru = r + u * nsub;
+          f[u] = __ldg(feat + ru * width + col);
+          gs[u] = __ldg(g_src + ru * heads + h);
+          gd[u] = ru < n_dst ? __ldg(g_dst + ru * heads + h) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          as[u] = fmaf(gs[u], f[u], as[u]);
+          ad[u] = fmaf(gd[u], f[u], ad[u]);
+        }
       }
-    sh[0][threadIdx.x] = as;
-    sh[1][threadIdx.x] = ad;
+      for (int u = 0; r < last; r += nsub, ++u) {
+        const float f = __ldg(feat + r * width + col);
+        as[u] = fmaf(__ldg(g_src + r * heads + h), f, as[u]);
+        if (r < n_dst) ad[u] = fmaf(__ldg(g_dst + r * heads + h), f, ad[u]);
+      }
+    }
+    float a_s = (as[0] + as[1]) + (as[2] + as[3]), a_d = (ad[0] + ad[1]) + (ad[2] + ad[3]);
+    sh[0][threadIdx.x] = a_s;
+    sh[1][threadIdx.x] = a_d;
     __syncthreads();
     if (on && sub == 0) {
       for (int u = 1; u < nsub; ++u) {
-        as += sh[0][u * width + threadIdx.x];
-        ad += sh[1][u * width + threadIdx.x];
+        a_s += sh[0][u * width + threadIdx.x];
+        a_d += sh[1][u * width + threadIdx.x];
       }
-      part[(static_cast<int64_t>(blockIdx.x) * 2) * width + col] = as;
-      part[(static_cast<int64_t>(blockIdx.x) * 2 + 1) * width + col] = ad;
+      part[(static_cast<int64_t>(blockIdx.x) * 2) * width + col] = a_s;
+      part[(static_cast<int64_t>(blockIdx.x) * 2 + 1) * width + col] = a_d;
     }
     __syncthreads();
   }
 }
 
-// Stage 2: the partials of every column are added in CTA order.
+// Stage 2: one warp per column; lane l adds the partials of CTAs l, l + 32, ... in order, the 32 lane sums are
+// joined by a shuffle tree.
 __global__ void __launch_bounds__(kThreads) gat_att_grad_final(const float *part, float *grad_att_src, float *grad_att_dst,
                                                                int n_part, int width) {
-  const int col = blockIdx.x * kThreads + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int col = (blockIdx.x * kThreads + threadIdx.x) >> 5;
   if (col >= width) return;
   float as = 0.f, ad = 0.f;
-  for (int b = 0; b < n_part; ++b) {
+  for (int b = lane; b < n_part; b += 32) {
     as += part[(static_cast<int64_t>(b) * 2) * width + col];
     ad += part[(static_cast<int64_t>(b) * 2 + 1) * width + col];
   }
-  grad_att_src[col] = as;
-  grad_att_dst[col] = ad;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    as += __shfl_down_sync(0xffffffffu, as, o);
+    ad += __shfl_down_sync(0xffffffffu, ad, o);
+  }
+  if (lane == 0) {
+    grad_att_src[col] = as;
+    grad_att_dst[col] = ad;
+  }
 }
 }  // namespace
 }  // namespace cxg
@@ -689,8 +717,8 @@ extern "C" int cxg_gat_att_grad(const float *feat, const float *g_src, const flo
   const int width = heads * c;
   float *part = static_cast<float *>(workspace);
   gat_att_grad_partial<<<kAttGradCtas, kThreads, 0, st>>>(feat, g_src, g_dst, part, n_src, n_dst, heads, c);
-  gat_att_grad_final<<<(width + kThreads - 1) / kThreads, kThreads, 0, st>>>(part, grad_att_src, grad_att_dst, kAttGradCtas,
-                                                                             width);
+  gat_att_grad_final<<<(width * 32 + kThreads - 1) / kThreads, kThreads, 0, st>>>(part, grad_att_src, grad_att_dst,
+                                                                                  kAttGradCtas, width);
   count_launches(2);
   return check_launch("cxg_gat_att_grad");
 }

@@ -565,8 +565,8 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream(StreamArgs 
 
 // ---------------------------------------------------------------------------------------------
 // Lean variant of the walk for the shapes that carry the large graphs: rows of exactly 32 * CB bytes
-// (128 / 256 / 512 bytes: every lane owns CB bytes of every row), no edge values, relations, targets or
-// accumulation, 16-byte cp.async staging, one stage per warp. Same tiles, same order of additions, same
+// (128 / 256 / 512 bytes: every lane owns CB bytes of every row), no edge values, relations or targets,
+// 16-byte cp.async staging, one stage per warp. Same tiles, same order of additions, same
 // partials as spmm_stream (results are bit-identical); what differs is the instruction count per edge:
 // tile-relative 32-bit positions and source ids, a running shared-memory pointer instead of per-run
 // address arithmetic, no per-lane column predicates, and a full-stage copy loop without bounds tests.
@@ -637,7 +637,7 @@ struct FastAcc<__nv_bfloat16, CB> {
   }
 };
 
-template <typename T, int CB, typename IdxT>
+template <typename T, int CB, typename IdxT, bool ACC>
 __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(StreamArgs a) {
   using C = Chunk<T, CB>;
   using Acc = FastAcc<T, CB>;
@@ -667,6 +667,7 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(Stream
   const uint32_t cdst = sl + lane * 16;
 
   auto zero_row = [&](int64_t r) {
+    if (ACC) return;  // y[r] += 0
     uint32_t z[W];
 #pragma unroll
     for (int i = 0; i < W; ++i) z[i] = 0u;
@@ -768,6 +769,13 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(Stream
               for (int i = 0; i < EL; ++i) f[i] = __fdiv_rn(f[i], d);
             }
             uint32_t w[W];
+            if (ACC) {  // y[row] += result (added after the division, as the general kernel does)
+              float old[EL];
+              ldg_words<W>(w, y + row * RB);
+              C::unpack(old, w);
+#pragma unroll
+              for (int i = 0; i < EL; ++i) f[i] += old[i];
+            }
             C::pack(w, f);
             stg_words_stream<W>(y + row * RB, w);
           }
@@ -999,7 +1007,7 @@ cudaError_t launch_fast3(const StreamArgs &a, int grid, cudaStream_t st) {
   constexpr int RB = 32 * CB;
   constexpr int B = kStageBytes / RB > 32 ? 32 : kStageBytes / RB;
   const size_t smem = static_cast<size_t>(B) * RB * kSWarps;
-  auto k = spmm_stream_fast<T, CB, IdxT>;
+  auto k = a.accumulate ? spmm_stream_fast<T, CB, IdxT, true> : spmm_stream_fast<T, CB, IdxT, false>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   k<<<grid, kSThreads, smem, st>>>(a);
@@ -1127,12 +1135,14 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
 
   unsigned pb = static_cast<unsigned>((L.max_tiles + 255) / 256);
   spmm_stream_plan<<<pb, 256, 0, st>>>(a);
-  const int grid = kNumSM * kCtasPerSM;
+  // CXG_SPMM_SHARE_SMS: four persistent CTAs per SM instead of six, so that a kernel of another stream (a
+  // collective's copy kernel) finds registers and shared memory on every SM while this one runs
+  const int grid = kNumSM * ((d->flags & CXG_SPMM_SHARE_SMS) ? 4 : kCtasPerSM);
   cudaError_t e;
   // the lean kernel covers full-warp rows without per-edge extras; ids are kept as 32-bit there (a feature matrix
   // of 2^32 rows of 128 bytes would not fit the device)
   const bool fast = row_bytes == 32 * cb && valmode == 0 && a.mode == kModeCpAsync && d->edge_rel == nullptr &&
-                    d->targets == nullptr && !a.accumulate && !(d->flags & CXG_SPMM_GENERIC_WALK);
+                    d->targets == nullptr && !(d->flags & CXG_SPMM_GENERIC_WALK);
   if (fast) {
     e = launch_fast(a, d->dtype, cb, d->idx_bytes, grid, st);
   } else if (d->dtype == CXG_F32)

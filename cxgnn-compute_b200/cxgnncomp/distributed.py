@@ -206,6 +206,57 @@ class NeededRowsExchange:
         ptr_rem = lptr.long() - ptr_own
         return (ptr_own, self.lidx[:nnz][own].contiguous()), (ptr_rem, self.lidx[:nnz][~own].contiguous())
 
+    def segment_graphs(self, lptr, chunks):
+        """The local CSR cut by WHEN the source row of an edge is available in a chunked exchange: element 0 holds the
+        edges that read this rank's own rows (no exchange needed), element 1 + c those that read the rows arriving
+        with chunk c (part c of every peer's rows, as `_chunk_plan` cuts them). Every element keeps all local rows,
+        so element k > 0 can be accumulated onto the sum of the elements before it; the order of the additions
+        into an output row is then own edges, chunk 0, chunk 1, ..., each in CSR order."""
+        plan = self._chunk_plan(chunks)
+        nnz = int(lptr[-1])
+        dev = lptr.device
+        seg_of_row = torch.zeros(self.buffer_rows(), dtype=torch.int8, device=dev)
+        for c in range(chunks):
+            for (ra, rb) in plan["recv_parts"][c]:
+                if rb > ra:
+                    seg_of_row[self.n_own + ra:self.n_own + rb] = 1 + c
+        seg = seg_of_row[self.lidx[:nnz].long()]
+        lptr_l = lptr.long()
+        graphs = []
+        for k in range(chunks + 1):
+            mine = seg == k
+            run = torch.zeros(nnz + 1, dtype=torch.int64, device=dev)
+            torch.cumsum(mine, 0, out=run[1:])
+            graphs.append((run[lptr_l], self.lidx[:nnz][mine].contiguous()))
+            del run, mine
+        return graphs
+
+    def exchange_pipelined(self, x_buf, send_buf, chunks, comm_stream, events, pack=None):
+        """The chunked exchange issued on `comm_stream`: chunk c is packed and sent / received there and
+        `events[c]` is recorded when its rows have landed in x_buf, so that another stream can start the work that
+        reads them (segment 1 + c of `segment_graphs`) while later chunks are still in flight. The caller makes
+        comm_stream wait for whatever produced x_buf's own rows before calling."""
+        x_own = x_buf[:self.n_own]
+        if pack is None:
+            import cxgnncomp_backend
+            pack = cxgnncomp_backend.gather_rows
+        plan = self._chunk_plan(chunks)
+        with torch.cuda.stream(comm_stream):
+            for c in range(chunks):
+                lo, hi = plan["send_chunk"][c]
+                pack(x_own, plan["send_rows"][lo:hi], send_buf[lo:hi])
+                ops = []
+                for q in range(self.part.world):
+                    (sa, sb), (ra, rb) = plan["send_parts"][c][q], plan["recv_parts"][c][q]
+                    if sb > sa:
+                        ops.append(dist.P2POp(dist.isend, send_buf[sa:sb], q, group=self.group))
+                    if rb > ra:
+                        ops.append(dist.P2POp(dist.irecv, x_buf[self.n_own + ra:self.n_own + rb], q, group=self.group))
+                if ops:
+                    for w in dist.batch_isend_irecv(ops):
+                        w.wait()
+                events[c].record(comm_stream)
+
     def exchange_backward(self, dx_buf, recv_buf=None, unpack=None):
         """Backward of `exchange`: dx_buf [buffer_rows, F] holds this rank's partial gradients for its own rows and
         for the remote rows it read. The remote part travels back to the owners (the forward all-to-all with the
@@ -290,3 +341,112 @@ class NeededRowsExchange:
             self._plans = {}
         self._plans[chunks] = plan
         return plan
+
+
+class PeerExchange:
+    """The needed-rows exchange without a collective kernel, over peer mappings of the other ranks' feature
+    buffers (CUDA IPC, every mapping opened by the GPU that writes through it: cxg_ipc_open). Two forms:
+
+      mode "kernel": ONE gather kernel per rank stores the rows every peer asked for straight into the peers'
+                     buffers (cxg_put_rows: pack and transfer fused, plain stores over NVLink);
+      mode "copy":   the rows are packed into the send buffer (cxg_gather_rows, in `chunks` parts) and each peer's
+                     part is copied into that peer's buffer by the copy engines (cxg_copy_async), one side stream
+                     per peer; no SM takes part in the transfer.
+
+    Ordering: a tiny all-reduce before the transfer (no rank still reads the buffer that is overwritten) and one
+    after it (every sender's stores have completed); both are stream-ordered, the host never waits. `close()`
+    releases the mappings (all ranks call it)."""
+
+    def __init__(self, ex, x_buf, send_buf=None, group=None, mode="kernel", chunks=1):
+        import cxgnncomp_backend as be
+        self.ex, self.group, self.x_buf, self.send_buf = ex, group, x_buf, send_buf
+        self.mode, self.chunks = mode, max(1, int(chunks))
+        world, rank = ex.part.world, ex.rank
+        dev = x_buf.device
+        self.row_bytes = x_buf.shape[1] * x_buf.element_size()
+        # Every rank takes part in every collective below even when a step of its own fails; the failure is agreed
+        # on afterwards, so that all ranks raise together and the caller can fall back to another exchange.
+        error = None
+        try:
+            exported = be.ipc_export(x_buf)
+        except RuntimeError as e:
+            exported, error = (None, 0), e
+        meta = [None] * world
+        dist.all_gather_object(meta, (exported[0], exported[1], ex.n_own, list(ex.recv_counts)), group=group)
+        self._bases, self.dst = [], []
+        for q in range(world):
+            if q == rank or ex.send_counts[q] == 0:
+                self.dst.append(0)
+                continue
+            h_q, off_q, n_own_q, recv_q = meta[q]
+            assert recv_q[rank] == ex.send_counts[q], "peer expects another number of rows"
+            base = 0
+            if error is None and h_q is not None:
+                try:
+                    base = be.ipc_open(h_q, dev)
+                    self._bases.append(base)
+                except RuntimeError as e:
+                    error = e
+            elif error is None:
+                error = RuntimeError(f"rank {q} could not export its buffer")
+            first = n_own_q + sum(recv_q[:rank])  # q's own rows, then the rows of the owners before me
+            self.dst.append(base + off_q + first * self.row_bytes if base else 0)
+        ok = torch.tensor([0.0 if error is not None else 1.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if float(ok[0]) == 0.0:
+            for b in self._bases:
+                be.ipc_close(b, dev)
+            self._bases = []
+            raise RuntimeError(f"peer mappings are not available on every rank ({error})")
+        seg = [0]
+        for q in range(world):
+            seg.append(seg[-1] + ex.send_counts[q])
+        self.seg_start = seg
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._streams = [torch.cuda.Stream(device=dev) if d else None for d in self.dst]
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+
+    def close(self):
+        import cxgnncomp_backend as be
+        torch.cuda.synchronize(self.x_buf.device)
+        dist.barrier(group=self.group)
+        for b in self._bases:
+            be.ipc_close(b, self.x_buf.device)
+        self._bases = []
+
+    def fence(self):
+        """Stream-ordered rendezvous of all ranks."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def exchange(self):
+        """Fills the remote part of every rank's buffer; returns when the work is queued on the current stream."""
+        import cxgnncomp_backend as be
+        ex = self.ex
+        x_own = ex.own(self.x_buf)
+        self.fence()
+        if self.mode == "kernel":
+            be.put_rows(x_own, ex.send_rows, self.dst, self.seg_start)
+        else:
+            main = torch.cuda.current_stream()
+            order = [(ex.rank + 1 + i) % ex.part.world for i in range(ex.part.world - 1)]  # another peer first per rank
+            for c in range(self.chunks):
+                for q in order:
+                    if not self.dst[q]:
+                        continue
+                    k = ex.send_counts[q]
+                    lo, hi = self.seg_start[q] + c * k // self.chunks, self.seg_start[q] + (c + 1) * k // self.chunks
+                    if hi == lo:
+                        continue
+                    be.gather_rows(x_own, ex.send_rows[lo:hi], self.send_buf[lo:hi])
+                    done = torch.cuda.Event()
+                    done.record(main)
+                    st = self._streams[q]
+                    st.wait_event(done)
+                    with torch.cuda.stream(st):
+                        be.copy_async(self.dst[q] + (lo - self.seg_start[q]) * self.row_bytes, self.send_buf[lo:hi])
+            for st in self._streams:
+                if st is not None:
+                    main.wait_stream(st)
+        self.fence()
+        return self.x_buf

@@ -106,6 +106,8 @@ SPLIT_EDGES = 0
 # OR-ed into cxg_spmm_desc.flags; CXG_SPMM_BULK_ROWS (4) selects the bulk-copy (TMA) row fetch.
 CXG_SPMM_BULK_ROWS = 4
 CXG_SPMM_TEST_STALL = 8  # test hook, see include/cxgnn_b200.h
+CXG_SPMM_GENERIC_WALK = 16
+CXG_SPMM_SHARE_SMS = 32
 CXG_TMM_TEST_STALL = 4
 EXTRA_SPMM_FLAGS = int(os.environ.get("CXG_SPMM_FLAGS", "0"))
 
@@ -130,7 +132,7 @@ def _dtype_code(t):
 
 
 def _make_desc(ptr, idx, x, y, num_node, *, heads=1, feat=None, edge_val=None, edge_mask=None,
-               edge_rel=None, rel_stride=0, targets=None, reduce=CXG_SUM, accumulate=False):
+               edge_rel=None, rel_stride=0, targets=None, reduce=CXG_SUM, accumulate=False, flags=0):
     _cuda(ptr, "ptr", _INDEX_DTYPES)
     _cuda(idx, "idx", _INDEX_DTYPES)
     d = SpmmDesc()
@@ -151,7 +153,7 @@ def _make_desc(ptr, idx, x, y, num_node, *, heads=1, feat=None, edge_val=None, e
     d.ptr_bytes = ptr.element_size()
     d.idx_bytes = idx.element_size()
     d.reduce = reduce
-    d.flags = (CXG_SPMM_ACCUMULATE if accumulate else 0) | EXTRA_SPMM_FLAGS
+    d.flags = (CXG_SPMM_ACCUMULATE if accumulate else 0) | EXTRA_SPMM_FLAGS | int(flags)
     d.split_edges = SPLIT_EDGES
     return d
 
@@ -204,7 +206,7 @@ def _run_spmm(desc, device):
 
 
 def _spmm_forward(x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, out=None, accumulate=False,
-                  edge_mask=None, edge_rel=None, rel_stride=0, targets=None):
+                  edge_mask=None, edge_rel=None, rel_stride=0, targets=None, flags=0):
     """y = A x for the first `num_node` rows; x is [N_s, F] or [N_s, H, F]."""
     _cuda(x, "x", _FEAT_DTYPES)
     n = _num_rows(ptr, num_node)
@@ -224,7 +226,7 @@ def _spmm_forward(x, ptr, idx, num_node, *, edge_val=None, reduce=CXG_SUM, out=N
         out = torch.empty(shape, dtype=x.dtype, device=x.device)
     desc = _make_desc(ptr, idx, x, out, n, heads=heads, feat=feat, edge_val=edge_val, edge_mask=edge_mask,
                       edge_rel=edge_rel, rel_stride=rel_stride, targets=targets, reduce=reduce,
-                      accumulate=accumulate)
+                      accumulate=accumulate, flags=flags)
     _run_spmm(desc, x.device)
     return out
 
@@ -398,13 +400,15 @@ def run_spmm_configurable(ptr, idx, vin, num_node, grid_x=0, grid_y=0, block_x=0
     return _spmm_forward(vin, ptr, idx, num_node)
 
 
-def spmm_into(out, ptr, idx, vin, num_node, reduce="sum", accumulate=False):
+def spmm_into(out, ptr, idx, vin, num_node, reduce="sum", accumulate=False, share_sms=False):
     """SpMM into a caller-owned [num_node, F] (or [num_node, H, F]) tensor: out = A vin, or out += A vin with
     accumulate=True. Not in the reference (its outputs are always fresh tensors); for loops that keep their
-    buffers, e.g. double-buffered pipelines, and for accumulating several source blocks into one output."""
+    buffers, e.g. double-buffered pipelines, and for accumulating several source blocks into one output.
+    share_sms=True leaves room on every SM for a kernel of another stream (an overlapping collective)."""
     _cuda(out, "out", (vin.dtype,))
     return _spmm_forward(vin, ptr, idx, num_node, out=out, accumulate=accumulate,
-                         reduce=CXG_MEAN if reduce == "mean" else CXG_SUM)
+                         reduce=CXG_MEAN if reduce == "mean" else CXG_SUM,
+                         flags=CXG_SPMM_SHARE_SMS if share_sms else 0)
 
 
 def run_spmm_configurable_int32(ptr, idx, vin, num_node, *tuner_args):
@@ -452,6 +456,58 @@ def gather_rows(x, rows, out=None):
         _check(_gather_rows(_p(x), _p(rows), _p(out), rows.shape[0], x.shape[1] * x.element_size(), _stream()),
                "cxg_gather_rows")
     return out
+
+
+_ipc_export = _sig("cxg_ipc_export", [_vp, _vp, ctypes.POINTER(_i64)])
+_ipc_open = _sig("cxg_ipc_open", [_vp, ctypes.POINTER(_vp)])
+_ipc_close = _sig("cxg_ipc_close", [_vp])
+_copy_async = _sig("cxg_copy_async", [_vp, _vp, _i64, _vp])
+_put_rows = _sig("cxg_put_rows", [_vp, _vp, _vp, _vp, ctypes.c_int, _i64, _vp])
+
+
+def ipc_export(t):
+    """(64-byte CUDA IPC handle of the allocation behind the CUDA tensor t, offset of t's first byte in it)."""
+    _cuda(t, "tensor")
+    buf = (ctypes.c_ubyte * 64)()
+    off = _i64(0)
+    with torch.cuda.device(t.device):
+        _check(_ipc_export(_p(t), buf, ctypes.byref(off)), "cxg_ipc_export")
+    return bytes(buf), int(off.value)
+
+
+def ipc_open(handle, device):
+    """Maps the allocation named by `handle` (from another process) into `device`'s context; returns its base address."""
+    base = _vp(0)
+    with torch.cuda.device(device):
+        _check(_ipc_open((ctypes.c_ubyte * 64).from_buffer_copy(handle), ctypes.byref(base)), "cxg_ipc_open")
+    return int(base.value)
+
+
+def ipc_close(base, device):
+    with torch.cuda.device(device):
+        _check(_ipc_close(_vp(base)), "cxg_ipc_close")
+
+
+def copy_async(dst_ptr, src, nbytes=None):
+    """Device-to-device copy (copy engines) of the contiguous CUDA tensor `src` to the device address dst_ptr, queued
+    on the current stream of src's device."""
+    _cuda(src, "src")
+    nbytes = src.numel() * src.element_size() if nbytes is None else int(nbytes)
+    with torch.cuda.device(src.device):
+        _check(_copy_async(_vp(dst_ptr), _p(src), nbytes, _stream()), "cxg_copy_async")
+
+
+def put_rows(x, rows, peer_ptrs, seg_start):
+    """Row i of `rows` (int64 positions into the 2-D x) is stored at peer_ptrs[q] + (i - seg_start[q]) * row bytes for
+    the q with seg_start[q] <= i < seg_start[q + 1]; peer_ptrs[q] is an address inside a mapping from ipc_open (None
+    or 0 where nothing is sent). One kernel, plain stores over NVLink. See cxg_put_rows."""
+    _cuda(x, "x")
+    _cuda(rows, "rows", (torch.int64,))
+    n_peer = len(peer_ptrs)
+    bases = (ctypes.c_void_p * n_peer)(*[None if not v else int(v) for v in peer_ptrs])
+    segs = (ctypes.c_int64 * (n_peer + 1))(*[int(v) for v in seg_start])
+    with torch.cuda.device(x.device):
+        _check(_put_rows(_p(x), _p(rows), bases, segs, n_peer, x.shape[1] * x.element_size(), _stream()), "cxg_put_rows")
 
 
 _sample = _sig("cxg_sample_neighbors", [_vp, _vp, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.c_int, _vp, _vp,

@@ -59,6 +59,10 @@ extern "C" {
 /* Measurement aid: rows of 128 / 256 / 512 bytes without edge values normally take a leaner
    instantiation of the tiled walk; this flag keeps them on the general one. Same results. */
 #define CXG_SPMM_GENERIC_WALK 16u
+/* The tiled kernel normally keeps six persistent CTAs on every SM; with this flag it keeps four, so
+   that a kernel launched from another stream meanwhile (the copy kernel of a collective that overlaps
+   this aggregation) finds room on every SM instead of waiting for this kernel to end. Same results. */
+#define CXG_SPMM_SHARE_SMS 32u
 
 const char *cxg_last_error_string(void);
 int cxg_abi_version(void);
@@ -352,6 +356,31 @@ int cxg_rgcn_direct(const void *ptr, const void *idx, int ptr_bytes, int idx_byt
  */
 int cxg_gather_rows(const void *in, const int64_t *rows, void *out, int64_t n_rows,
                     int64_t row_bytes, void *stream);
+
+/*
+ * Peer mappings for the exchange between the GPUs of one node (one process per GPU). cxg_ipc_export gives the
+ * 64-byte CUDA IPC handle of the allocation that holds `ptr` and ptr's offset inside it; the other process calls
+ * cxg_ipc_open WITH ITS OWN GPU CURRENT and receives the base of a mapping of that allocation in its own context
+ * (lazy peer access over NVLink; the mapping is probed with a small copy before it is handed out), to be released
+ * with cxg_ipc_close. An allocation can be opened once per process. cxg_copy_async is a device-to-device
+ * cudaMemcpyAsync (copy engines) for moving packed rows into such a mapping.
+ *
+ * cxg_put_rows fuses the pack step with the transfer: row i of the list goes to peer q = the segment
+ * [seg_start[q], seg_start[q+1]) that holds i, at peer_base[q] + (i - seg_start[q]) * row_bytes, where peer_base[q]
+ * points into a mapping obtained from cxg_ipc_open (already offset to the first row q expects from this rank).
+ * Plain 16-byte stores over NVLink, all peers written concurrently; no send buffer, no collective kernel.
+ * peer_base_host and seg_start_host (n_peer and n_peer + 1 entries) are HOST arrays. The caller orders the step
+ * across ranks (nobody may still read the destination; the receiver may read it once every sender's kernel has
+ * completed). Replaces the pack + NCCL send / receive pair of the reference's "densify" exchange
+ * (test/1-kernels/test_mgpu_model.py:227-331). n_peer <= 16, row_bytes a multiple of 16.
+ */
+int cxg_ipc_export(const void *ptr, unsigned char *handle64, int64_t *offset_bytes);
+int cxg_ipc_open(const unsigned char *handle64, void **base);
+int cxg_ipc_close(void *base);
+int cxg_copy_async(void *dst, const void *src, int64_t bytes, void *stream);
+int cxg_put_rows(const void *in, const int64_t *rows, void *const *peer_base_host,
+                 const int64_t *seg_start_host, int n_peer, int64_t row_bytes, void *stream);
+
 
 /*
  * Neighbour sampling for mini-batches in the CSR_Layer format (the step the reference takes from its

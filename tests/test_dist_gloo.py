@@ -72,6 +72,17 @@ def _worker(rank, world, port, out_dir):
     assert bool((i_own < ex.n_own).all()) and bool((i_rem >= ex.n_own).all())
     y_two = oracle.spmm_f64(p_own, i_own, x_buf) + oracle.spmm_f64(p_rem, i_rem, x_buf)
     assert float((y_two - oracle.spmm_f64(lptr, ex.lidx, x_buf)).abs().max()) < 1e-12
+    # the local graph cut by arrival time in a 3-chunk exchange: the pieces partition the edges, each reads only its
+    # own part of the buffer, and accumulating them in order reproduces the aggregation
+    graphs = ex.segment_graphs(lptr, 3)
+    assert len(graphs) == 4 and sum(int(g[0][-1]) for g in graphs) == int(lptr[-1])
+    assert torch.equal(sum(g[0] for g in graphs), lptr) and bool((graphs[0][1] < ex.n_own).all())
+    plan3 = ex._chunk_plan(3)
+    for c in range(3):
+        rows_c = torch.cat([torch.arange(ra, rb) for (ra, rb) in plan3["recv_parts"][c]]) + ex.n_own
+        assert bool(torch.isin(graphs[1 + c][1], rows_c).all())
+    y_seg = sum(oracle.spmm_f64(g[0], g[1], x_buf) for g in graphs)
+    assert float((y_seg - oracle.spmm_f64(lptr, ex.lidx, x_buf)).abs().max()) < 1e-12
     # backward: partial gradients for every row this rank read go back to their owners and are summed there
     dy = synthetic.node_features(3000, 16, seed=2)[r0:r1]
     dx_buf = oracle.spmm_bwd_f64(lptr, ex.lidx, dy, (ex.buffer_rows(), 16))[0]

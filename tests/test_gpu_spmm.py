@@ -396,3 +396,14 @@ def test_spmm_into_overwrites_and_accumulates(cuda):
     mean = torch.empty_like(out)
     be.spmm_into(mean, p, i, xg, 300, reduce="mean")
     assert torch.equal(mean, be._spmm_forward(xg, p, i, 300, reduce=be.CXG_MEAN))
+    # the lean and the general instantiation of the tiled walk give the same bits, also when accumulating, and
+    # so does the grid that leaves room on the SMs
+    for dtype in (torch.float32, torch.bfloat16):
+        xd = xg.to(dtype)
+        y0 = randn((300, 64), 97).to(dtype).cuda()
+        for acc in (False, True):
+            lean, shared, general = y0.clone(), y0.clone(), y0.clone()
+            be.spmm_into(lean, p, i, xd, 300, accumulate=acc)
+            be.spmm_into(shared, p, i, xd, 300, accumulate=acc, share_sms=True)
+            be._spmm_forward(xd, p, i, 300, out=general, accumulate=acc, flags=be.CXG_SPMM_GENERIC_WALK)
+            assert torch.equal(lean, general) and torch.equal(shared, general)
