@@ -1,6 +1,7 @@
 """Per-configuration measurements of the aggregation path (configurations 1, 2 and 4; `bench.py` covers 5).
 
-    python bench_layers.py [--configs c1,c2,c4] [--steps K]
+    python bench_layers.py [--configs c1,c2,c3,c4] [--steps K]
+    python -m torch.distributed.run --nproc-per-node P ... bench_layers.py      (configuration 3, one replica per GPU)
 
 Prints one JSON line per configuration: GPU time per pass (CUDA events, 256 MiB L2 flush between passes),
 algorithmic bytes / flops and the fraction of the measured HBM (or tensor) peak, the reference's CPU
@@ -291,6 +292,56 @@ def config3(steps, flush, scale=1.0):
             "note": "CPU step excludes sampling and feature gather (batches taken from the GPU sampler)"}
 
 
+def config3_replicas(scale=1.0):
+    """Configuration 3 as the reference's MultiModel runs it (cxgnncomp/trainer.py:14-59,307-344): one model
+    replica, one sampler stream (seed 1000 + rank) and one epoch loop per GPU, no gradient exchange. Launched under
+    torchrun with one rank per GPU; every rank trains one epoch of its own stream, the epoch time is the maximum over
+    the ranks (device events) and the throughput is ranks x batches / that time. Rank 0 returns the record."""
+    import torch.distributed as dist
+    import cxgnncomp
+    from cxgnncomp import synthetic
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    n, e_und = synthetic.CONFIG_SHAPES["products_like"]
+    n, e_und = int(n * scale), int(e_und * scale)
+    ptr, idx = synthetic.powerlaw_graph(n, e_und, seed=0, device=dev)  # every GPU holds the whole graph
+    x = synthetic.node_features(n, 100, seed=0, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    y = torch.randint(0, 47, (n,), device=dev, generator=g)
+    train = torch.randperm(n, device=dev, generator=g)[:int(0.08 * n)]
+    bs = 1024
+    torch.manual_seed(1000 + rank)
+    model = cxgnncomp.SAGE(100, 256, 47, 3).cuda()
+    opt = torch.optim.Adam(model.parameters(), lr=0.003, fused=True)
+    sampler = cxgnncomp.NeighborSampler(ptr, idx, [15, 10, 5])
+    nb = cxgnncomp.num_batches(train.shape[0], bs)
+    cxgnncomp.train_epoch(model, opt, sampler, x, y, train, bs, epoch=1000 + rank, max_batches=10)  # warm-up
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    losses = cxgnncomp.train_epoch(model, opt, sampler, x, y, train, bs, epoch=2000 + rank)
+    b.record()
+    b.synchronize()
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    rec = {"config": "c3 GraphSAGE mini-batch training, one replica and one batch stream per GPU, no gradient exchange",
+           "n_gpus": world, "nodes": n, "nnz": int(idx.shape[0]), "fanouts_from_seeds": [15, 10, 5], "batch_size": bs,
+           "train_fraction": 0.08, "batches_per_epoch_per_gpu": nb, "epoch_ms_max_over_ranks": ms,
+           "batches_per_s_all_gpus": world * nb / (ms * 1e-3), "ms_per_batch_per_gpu": ms / nb,
+           "loss_first_last_rank0": [float(losses[0]), float(losses[-1])]}
+    if world > 1:
+        dist.barrier()
+    return rec if rank == 0 else None
+
+
 def config4(steps, flush, scale=1.0, cpu=True, quick=False):
     """RGCN layer, 8 relations, 1.94 M nodes / 21 M edges, 128 -> 64: fp32 (error-compensated TF32, the default),
     fp32 with plain TF32 products (the reference's tl.dot precision) and bf16. quick=True times the default
@@ -391,6 +442,12 @@ def main():
     ap.add_argument("--c3-scale", type=float, default=1.0, help="shrink configuration 3 (nodes and edges) by this factor")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "needs a CUDA device"
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.configs == "c3r":
+        # torchrun: the only multi-GPU layer record is configuration 3 as independent replicas
+        rec = config3_replicas(args.c3_scale)
+        if rec is not None:
+            print(json.dumps(rec), flush=True)
+        return
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     table = {"c1": config1, "c2": config2, "c3": config3, "c4": config4}
     for c in args.configs.split(","):

@@ -36,6 +36,14 @@
 // the stage). To keep several stages in flight with stages twice as large, the K dimension is cut into blocks:
 // the pipeline unit is (tile, K-block) and all blocks of a tile accumulate into one accumulator buffer.
 //
+// Dense mode (CXG_TMM_ALL_RELATIONS): C[r * m_valid + i, :] = A[i, :] . W[r] for every row i and EVERY relation r, the
+// "transform all nodes with every relation's weight" step of the transform-first RGCN schedule
+// (TypedLinearS2DMMAggrOP, cxgnncomp/typed_linear.py:191-221, which the reference runs as num_rel torch.mm calls).
+// No index arrays: a CTA owns P consecutive relations (as many as fit: their weights side by side are one B operand
+// of P * N columns, P * N <= 256) and the row tiles of one group; W is copied once per CTA, a tile of A is
+// multiplied by all P weights with one set of MMAs, and the num_rel / P CTAs of a group walk the same tiles at the
+// same time, so a tile of A comes from HBM once and from L2 for the other relation sets.
+//
 // Every wait is bounded: a role that waits longer than about a second raises a CTA-wide abort
 // flag and an error status; all roles then leave their loops, the copies in flight are waited
 // for, the tensor memory is released and the kernel returns.
@@ -73,6 +81,8 @@ struct TmmArgs {
   int tmem_cols;  // columns of ONE accumulator buffer (two are allocated)
   int stages;     // shared-memory stages of A
   int kb;         // K-block: columns of A per pipeline unit (= k unless the stage would not fit several times)
+  int dense;       // dense mode: relations per CTA (0 = off); n is then dense * ncols (see below)
+  int ncols;       // columns of C per relation (= n outside dense mode)
   int test_stall;  // test hook: the producers never hand over the first tile, so the waits for it run out
   long long wait_cycles;  // limit of one barrier wait
   int32_t *status;  // [0] error flag
@@ -257,7 +267,13 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
 
   const T *A = static_cast<const T *>(a.a);
   const int64_t n_tiles = (a.m + kTileM - 1) / kTileM;
-  const int64_t tile_lo = n_tiles * blockIdx.x / gridDim.x, tile_hi = n_tiles * (blockIdx.x + 1) / gridDim.x;
+  const bool dense = a.dense != 0;
+  const int rel_sets = dense ? a.num_rel / a.dense : 1;                   // CTAs per group of row tiles
+  const int64_t dense_rel = dense ? (blockIdx.x % rel_sets) * a.dense : 0;  // first relation of this CTA in dense mode
+  const int64_t part = dense ? blockIdx.x / rel_sets : blockIdx.x, parts = dense ? gridDim.x / rel_sets : gridDim.x;
+  const int64_t tile_lo = n_tiles * part / parts, tile_hi = n_tiles * (part + 1) / parts;
+  // relation of a tile: the position array's, or the CTA's own in dense mode
+  auto rel_of = [&](int64_t tile) -> int64_t { return tile < tile_hi ? (dense ? dense_rel : a.rel[tile * kTileM]) : -1; };
 
   if (warp > kMmaWarp && warp < kFirstConvWarp) {
     // ================= producers: gather A (and W on a relation change) =================
@@ -271,7 +287,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
     // the relation and the row indices of a tile are fetched one tile ahead, off the critical path
     auto fetch = [&](int64_t tile, int64_t &r, int64_t (&ia)[kSlots]) {
       const int64_t m0 = tile * kTileM;
-      r = tile < tile_hi ? a.rel[m0] : -1;
+      r = rel_of(tile);
 #pragma unroll
       for (int gi = 0; gi < kSlots; ++gi) {
         const int64_t pos = m0 + pw * kRowsPerProdWarp + gi * kRpi + rsub;  // warp pw owns kRowsPerProdWarp rows
@@ -293,7 +309,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
         for (int64_t j = (it > S ? it - S : 0); j < it && alive; ++j)
           alive = wait_bar(&bars.empty[j % S], static_cast<uint32_t>((j / S) & 1), abort_flag, a.status, a.wait_cycles);
         if (!alive) break;
-        const int64_t w_elems = static_cast<int64_t>(a.n) * a.k;
+        const int64_t w_elems = static_cast<int64_t>(a.ncols) * a.k;  // one relation's weight (dense: P of them in a row)
         const uint32_t b0 = smem_addr(smem_b);
         for (int part = 0; part < (X3 ? 2 : 1); ++part) {  // hi, then lo
           const T *wr = Wt + (part * static_cast<int64_t>(a.num_rel) + r) * w_elems;
@@ -335,7 +351,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
     int64_t it = 0;
     bool alive = true;
     for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
-      const int64_t r = a.rel[tile * kTileM];
+      const int64_t r = rel_of(tile);
       if (r < 0 || r >= a.num_rel) continue;
       for (int kb = 0; kb < nkb && alive; ++kb) {
         const int s = static_cast<int>(it % S);
@@ -367,10 +383,10 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
       const int steps = chunks_blk / 2;  // two chunks (32 bytes) of K per instruction
       int64_t it = 0, tile_it = 0;
       bool alive = true;
-      int64_t r_next = tile_lo < tile_hi ? a.rel[tile_lo * kTileM] : -1;
+      int64_t r_next = rel_of(tile_lo);
       for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
         const int64_t r = r_next;
-        r_next = tile + 1 < tile_hi ? a.rel[(tile + 1) * kTileM] : -1;
+        r_next = rel_of(tile + 1);
         if (r < 0 || r >= a.num_rel) continue;
         const int buf = static_cast<int>(tile_it & 1);
         const uint32_t d = tmem_d + buf * a.tmem_cols;
@@ -423,11 +439,12 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
     // relation, source and destination index of this thread's row, fetched one tile ahead
     auto fetch = [&](int64_t tile, int64_t &r, int64_t &sv, int64_t &dv) {
       const int64_t m0 = tile * kTileM, pos = m0 + warp * 32 + lane;
-      r = tile < tile_hi ? a.rel[m0] : -1;
+      r = rel_of(tile);
       sv = -1, dv = -1;
       if (tile < tile_hi && pos < a.m) {
         sv = a.src != nullptr ? a.src[pos] : pos;
         dv = a.dst != nullptr ? a.dst[pos] : -2;  // -2: no destination index
+        if (dense) dv = dense_rel * a.m_valid + pos;  // row of the [num_rel * m_valid, ncols] table, first relation
       }
     };
     int64_t r_next, sv_next, dv_next;
@@ -455,6 +472,9 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(&bars.acc_empty[buf]);
         }
+        // dense mode: columns [j * ncols, (j + 1) * ncols) of the accumulator are relation dense_rel + j
+        const int64_t rel_shift = dense ? static_cast<int64_t>(c0 / a.ncols) * a.m_valid : 0;
+        const int cc = dense ? c0 % a.ncols : c0;
         if (oc >= 0 && a.atomic) {
           float *o = static_cast<float *>(a.c) + oc * a.n + c0;
 #pragma unroll
@@ -483,7 +503,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
           }
           const bool odd = lane & 1;
           const int64_t oc_a = __shfl_sync(0xffffffffu, oc, lane & ~1), oc_b = __shfl_sync(0xffffffffu, oc, lane | 1);
-          T *row_a = C + oc_a * a.n + c0, *row_b = C + oc_b * a.n + c0;
+          T *row_a = C + (oc_a + rel_shift) * a.ncols + cc, *row_b = C + (oc_b + rel_shift) * a.ncols + cc;
           constexpr int QE = 16 / sizeof(T);  // elements per quad
 #pragma unroll
           for (int h = 0; h < NQ / 2; ++h) {
@@ -535,11 +555,17 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
                                 int precision, int flags, void *workspace, size_t workspace_bytes, void *stream) {
   const int seq_output = (flags & CXG_TMM_SEQ_OUTPUT) ? 1 : 0;
   const int atomic = (flags & CXG_TMM_ATOMIC_F32) ? 1 : 0;
+  const int dense = (flags & CXG_TMM_ALL_RELATIONS) ? 1 : 0;
   CXG_REQUIRE(m >= 0 && m_valid >= 0 && k > 0 && n > 0 && num_rel > 0, CXG_EINVAL, "cxg_typed_matmul: bad sizes");
   CXG_REQUIRE(dtype == CXG_F32 || dtype == CXG_BF16, CXG_EINVAL, "cxg_typed_matmul: dtype %d", dtype);
   CXG_REQUIRE(precision >= 0 && precision <= 2, CXG_EINVAL, "cxg_typed_matmul: precision %d", precision);
   if (m == 0) return CXG_OK;
-  CXG_REQUIRE(a && w && c && rel, CXG_ENULL, "cxg_typed_matmul: NULL argument");
+  CXG_REQUIRE(a && w && c && (rel || dense), CXG_ENULL, "cxg_typed_matmul: NULL argument");
+  if (dense) {
+    CXG_REQUIRE(precision != 0 && !atomic && src_idx == nullptr && dst_idx == nullptr && m == m_valid, CXG_EUNSUPPORTED,
+                "cxg_typed_matmul: CXG_TMM_ALL_RELATIONS takes no index arrays, m == m_valid, a tensor-core precision");
+    CXG_REQUIRE(num_rel <= kNumSM, CXG_ELIMIT, "cxg_typed_matmul: %d relations, at most %d in dense mode", num_rel, kNumSM);
+  }
   cudaStream_t st = as_stream(stream);
   const int follows = (src_idx != nullptr && dst_idx == nullptr && !seq_output) ? 1 : 0;
   if (precision == 0) {  // exact fp32 accumulation of every product, no tensor cores
@@ -548,8 +574,24 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
                              st);
   }
   const bool x3 = precision == 2 && dtype == CXG_F32;  // bf16 inputs have nothing to compensate
+  const int ncols = n;  // columns of C per relation
+  int rel_per_cta = 0;
+  if (dense) {
+    // as many relations side by side as divide num_rel, fit 256 accumulator columns and leave shared memory for at
+    // least three stages of A next to their weights
+    const size_t elem_b = dtype == CXG_F32 ? 4 : 2;
+    for (int p = 1; p <= num_rel; ++p) {
+      if (num_rel % p != 0 || p * ncols > 256) continue;
+      const size_t wb = static_cast<size_t>(p) * ncols * k * elem_b * (x3 ? 2 : 1);
+      const size_t stage = static_cast<size_t>(kTileM) * (k < 32 ? k : 32) * elem_b * (x3 ? 2 : 1);
+      if (wb + 3 * stage <= static_cast<size_t>(kSmemBudget)) rel_per_cta = p;
+    }
+    CXG_REQUIRE(rel_per_cta > 0, CXG_EUNSUPPORTED, "cxg_typed_matmul: K = %d, N = %d is too large for the dense mode", k, n);
+    n = rel_per_cta * ncols;
+  }
   if (x3 && static_cast<size_t>(n) * k * 8 + static_cast<size_t>(kTileM) * 8 * 8 > static_cast<size_t>(kSmemBudget)) {
     // both TF32 terms of W[rel] do not fit in shared memory next to one stage: the exact kernel keeps the accuracy
+    CXG_REQUIRE(!dense, CXG_EUNSUPPORTED, "cxg_typed_matmul: K = %d, N = %d is too large for the dense fp32 mode", k, n);
     CXG_REQUIRE(!atomic || dtype == CXG_F32, CXG_EUNSUPPORTED, "cxg_typed_matmul: exact mode adds atomically in fp32 only");
     return typed_rows_launch(a, w, c, rel, 8, src_idx, dst_idx, m, m_valid, k, n, num_rel, dtype, atomic ? 2 : 0, follows,
                              st);
@@ -566,7 +608,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   // multiple of one instruction's K (32 bytes)
   auto stage_bytes = [&](int kb) { return static_cast<size_t>(kTileM) * kb * elem * (x3 ? 2 : 1); };
   int kb = k;
-  const int want = x3 ? 4 : 1;
+  const int want = x3 ? 4 : (dense ? 3 : 1);
   while (b_bytes + want * stage_bytes(kb) > static_cast<size_t>(kSmemBudget) && kb % (4 * epc) == 0) kb /= 2;
   if (const char *env = getenv("CXG_TMM_KBLOCK")) {  // tuning aid: force the K-block (must divide K, multiple of 32 bytes)
     const int v = atoi(env);
@@ -582,7 +624,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
                   (n * elem) % 16 == 0,
               CXG_EINVAL, "cxg_typed_matmul: A, C and their rows must be 16-byte aligned");
   size_t need = 0;
-  cxg_typed_matmul_workspace_size(num_rel, k, n, dtype, &need);
+  cxg_typed_matmul_workspace_size(num_rel, k, ncols, dtype, &need);
   CXG_REQUIRE(workspace != nullptr && workspace_bytes >= need, CXG_EWORKSPACE,
               "cxg_typed_matmul: workspace %zu bytes, need %zu", workspace_bytes, need);
   CXG_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, CXG_EINVAL, "cxg_typed_matmul: workspace alignment");
@@ -591,6 +633,8 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   t.a = a, t.c = c, t.rel = rel, t.src = src_idx, t.dst = dst_idx;
   t.m = m, t.m_valid = m_valid, t.k = k, t.n = n, t.num_rel = num_rel, t.out_follows_src = follows;
   t.atomic = atomic;
+  t.dense = rel_per_cta;
+  t.ncols = ncols;
   t.test_stall = (flags & CXG_TMM_TEST_STALL) ? 1 : 0;
   t.wait_cycles = wait_limit_cycles();
   t.status = reinterpret_cast<int32_t *>(workspace);
@@ -606,6 +650,12 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   // one persistent CTA per SM (its shared-memory ring fills the SM), contiguous tile ranges
   int64_t grid = kNumSM;
   if (grid > n_tiles) grid = n_tiles;
+  if (dense) {  // num_rel / rel_per_cta CTAs per group of row tiles
+    const int sets = num_rel / rel_per_cta;
+    int64_t groups = kNumSM / sets;
+    if (groups > n_tiles) groups = n_tiles;
+    grid = groups * sets;
+  }
   // rows that are gathered several times each go through L1, rows read once bypass it
   const bool ca = src_idx != nullptr && m_valid * 2 <= m;
   cudaError_t e = cudaSuccess;
@@ -616,7 +666,8 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   if (dtype == CXG_F32) {
     float *wt_f = static_cast<float *>(wt);
     transpose_w<float><<<kNumSM, 256, 0, st>>>(static_cast<const float *>(w), wt_f,
-                                               x3 ? wt_f + static_cast<size_t>(num_rel) * k * n : nullptr, num_rel, k, n);
+                                               x3 ? wt_f + static_cast<size_t>(num_rel) * k * ncols : nullptr, num_rel, k,
+                                               ncols);
     constexpr int kW = kEpiWarps + 1 + 8;
     if (x3) {
       if (ca) launch(typed_mm_tc<float, true, 8, true>, kW + kConvWarps); else launch(typed_mm_tc<float, false, 8, true>, kW + kConvWarps);
@@ -625,7 +676,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
     }
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),
-                                                       static_cast<__nv_bfloat16 *>(wt), nullptr, num_rel, k, n);
+                                                       static_cast<__nv_bfloat16 *>(wt), nullptr, num_rel, k, ncols);
     constexpr int kW = kEpiWarps + 1 + 4;
     if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4, false>, kW); else launch(typed_mm_tc<__nv_bfloat16, false, 4, false>, kW);
   }

@@ -250,6 +250,25 @@ class RGCNFusedOP(torch.autograd.Function):
         return grad_x, grad_w, None, None, None, None, None, None, None, None, None
 
 
+class _AggrRelValFunction(torch.autograd.Function):
+    """aggr_rel with one fp32 value per edge: out[d] = sum_e val[e] * table[etype[e] * N + idx[e]] (the relational
+    aggregation of rel_spmm.cu:8-70 with the per-relation degree normalisation folded into the edge values)."""
+
+    @staticmethod
+    def forward(ctx, table, ptr, idx, etype, val, num_node, num_rel):
+        ctx.save_for_backward(table, ptr, idx, etype, val)
+        ctx.num_node, ctx.num_rel = num_node, num_rel
+        return cxgnncomp_backend._spmm_forward(table, ptr, idx, num_node, edge_val=val, edge_rel=etype,
+                                               rel_stride=table.shape[0] // num_rel)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        table, ptr, idx, etype, val = ctx.saved_tensors
+        dx, _ = cxgnncomp_backend._spmm_backward(grad_out, table, ptr, idx, ctx.num_node, edge_val=val, edge_rel=etype,
+                                                 rel_stride=table.shape[0] // ctx.num_rel)
+        return dx.to(table.dtype), None, None, None, None, None, None
+
+
 class MyRGCNConv(torch.nn.Module):
     """RGCN layer: y[d] = (1 / deg d) * sum over edges of x[src] W[rel] (graph_conv.py:329-378). `norm`
     selects the reference's total in-degree ("total", default) or the per-(destination, relation) degree
@@ -277,6 +296,8 @@ class MyRGCNConv(torch.nn.Module):
         self.reset_parameters()
         self.preprocessed = []
         self._types32 = None
+        self._inv_rel_count = None
+        self._deg_cache = None
 
     def reset_parameters(self):
         glorot(self.linear)
@@ -286,7 +307,10 @@ class MyRGCNConv(torch.nn.Module):
         if idx.shape[0] > 1e8:
             return RGCNOP.apply(x, self.linear, ptr, idx, edge_types, num_node)
         num_edge = edge_types.shape[0]
-        deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(x.dtype)
+        key = (ptr.data_ptr(), ptr._version, num_node, x.dtype)
+        if self._deg_cache is None or self._deg_cache[0] != key:  # per graph, not per call
+            self._deg_cache = (key, (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(x.dtype), ptr)
+        deg = self._deg_cache[1]
         schedule = self.schedule
         if schedule == "auto":
             # values moved per call: per-edge gather of `in` + write of `out`, against one pass over x, the
@@ -295,20 +319,34 @@ class MyRGCNConv(torch.nn.Module):
             fused = num_edge * (k + o)
             table = n_src * k + self.num_rel * n_src * o + num_edge * o
             schedule = "transform_first" if table < fused else "fused_gather"
-        if self.norm == "total" and schedule == "transform_first":
-            if x.dtype == torch.float32 and cxgnncomp_backend.ALLOW_TF32:
+        if schedule == "transform_first":
+            if cxgnncomp_backend.typed_matmul_all_relations_supported(x, self.linear):
+                # every node times every relation's weight in one launch of the tensor-core kernel
+                xw = cxgnncomp_backend.transform_all_relations(x, self.linear)  # [R, N_src, out]
+            elif x.dtype == torch.float32 and cxgnncomp_backend.ALLOW_TF32:
                 old = torch.backends.cuda.matmul.allow_tf32
                 torch.backends.cuda.matmul.allow_tf32 = True
                 try:
-                    xw = torch.matmul(x.unsqueeze(0), self.linear)  # [R, N_src, out]
+                    xw = torch.matmul(x.unsqueeze(0), self.linear)
                 finally:
                     torch.backends.cuda.matmul.allow_tf32 = old
             else:
                 xw = torch.matmul(x.unsqueeze(0), self.linear)
             if self._types32 is None or self._types32[0] is not edge_types:
                 self._types32 = (edge_types, edge_types.int())  # aggr_rel takes int32 relation ids
-            out = cxgnncomp_backend.aggr_rel(xw.reshape(-1, xw.shape[-1]), ptr, idx, self._types32[1], num_node,
-                                             self.num_rel)
+                self._inv_rel_count = None
+            table = xw.reshape(-1, xw.shape[-1])
+            if self.norm == "relation":
+                # 1 / (edges of this relation into this destination) as the edge value of the relational aggregation
+                if self._inv_rel_count is None:
+                    dst = torch.repeat_interleave(torch.arange(num_node, device=x.device),
+                                                  ptr[1:num_node + 1] - ptr[:num_node])
+                    key = dst * self.num_rel + edge_types[:dst.shape[0]]
+                    cnt = torch.bincount(key, minlength=num_node * self.num_rel)
+                    self._inv_rel_count = (1.0 / cnt[key].float()).contiguous()
+                return _AggrRelValFunction.apply(table, ptr, idx, self._types32[1], self._inv_rel_count, num_node,
+                                                 self.num_rel)
+            out = cxgnncomp_backend.aggr_rel(table, ptr, idx, self._types32[1], num_node, self.num_rel)
             return out / deg.unsqueeze(-1)
         if len(self.preprocessed) == 0:  # relation buckets, built on the first call like the reference caches them
             self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)

@@ -213,3 +213,71 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
         _check(_tmm(_p(a), _p(b), _p(c), _p(rel), _p(src_idx), _p(dst_idx), int(m_positions), int(m_valid), k, n, num_rel,
                     dtype, precision, flags, _p(ws), ws.numel(), _stream()), "cxg_typed_matmul")
     return c
+
+
+def typed_matmul_all_relations(x, w, allow_tf32=None):
+    """[R, N, out] = x [N, K] multiplied by every relation's weight w [R, K, out] in one launch of the tensor-core
+    kernel (cxg_typed_matmul with CXG_TMM_ALL_RELATIONS): the first half of TypedLinearS2DMMAggrOP
+    (cxgnncomp/typed_linear.py:191-221), which the reference runs as num_rel torch.mm calls. No autograd."""
+    _cuda(x, "x", (torch.float32, torch.bfloat16))
+    _cuda(w, "w", (x.dtype,))
+    num_rel, k, n = w.shape
+    if x.dim() != 2 or x.shape[1] != k:
+        raise RuntimeError("incompatible dimensions")
+    m = x.shape[0]
+    c = torch.empty((num_rel, m, n), dtype=x.dtype, device=x.device)
+    dtype = CXG_F32 if x.dtype == torch.float32 else CXG_BF16
+    if allow_tf32 is None:
+        allow_tf32 = sys.modules[__package__].ALLOW_TF32
+    precision = 1 if (allow_tf32 or dtype == CXG_BF16) else 2
+    need = _sz(0)
+    _check(_tmm_ws(num_rel, k, n, dtype, ctypes.byref(need)), "cxg_typed_matmul_workspace_size")
+    ws = _workspace(x.device, need.value, "typed_matmul")
+    with torch.cuda.device(x.device):
+        _check(_tmm(_p(x), _p(w), _p(c), None, None, None, m, m, k, n, num_rel, dtype, precision, 8, _p(ws), ws.numel(),
+                    _stream()), "cxg_typed_matmul")
+    return c
+
+
+def typed_matmul_all_relations_supported(x, w):
+    """Shapes the dense tensor-core mode covers (K a multiple of 16 / 8, N a multiple of 16 up to 256, both TF32
+    terms of a weight matrix within shared memory for fp32)."""
+    if x.dtype not in (torch.float32, torch.bfloat16) or w.dtype != x.dtype or not x.is_cuda:
+        return False
+    num_rel, k, n = w.shape
+    elem = x.element_size()
+    if k % (32 // elem) != 0 or n % 16 != 0 or n > 256 or num_rel > 148:
+        return False
+    split = 2 if elem == 4 else 1  # fp32: both TF32 terms of every operand
+    return n * k * elem * split + 3 * 128 * min(k, 32) * elem * split <= 226 * 1024
+
+
+class _TransformAllFunction(torch.autograd.Function):
+    """xw[r] = x @ w[r] for every relation (forward: one tensor-core launch); backward through the dense formulas
+    dx = sum_r g[r] @ w[r]^T and dw[r] = x^T @ g[r] as batched matrix products."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return typed_matmul_all_relations(x.contiguous(), w.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        dx = dw = None
+        tf32 = sys.modules[__package__].ALLOW_TF32
+        old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = bool(tf32)
+        try:
+            if ctx.needs_input_grad[0]:
+                dx = torch.matmul(g, w.transpose(1, 2)).sum(0)
+            if ctx.needs_input_grad[1]:
+                dw = torch.matmul(x.t().unsqueeze(0), g)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = old
+        return dx, dw
+
+
+def transform_all_relations(x, w):
+    """Differentiable typed_matmul_all_relations."""
+    return _TransformAllFunction.apply(x, w)

@@ -454,6 +454,11 @@ int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
  */
 #define CXG_TMM_SEQ_OUTPUT 1
 #define CXG_TMM_ATOMIC_F32 2
+/* Dense mode: C[r * m + i, :] = A[i, :] . W[r] for every row i < m and EVERY relation r (C is [num_rel * m, n]):
+   the "transform every node with every relation's weight" step of TypedLinearS2DMMAggrOP
+   (cxgnncomp/typed_linear.py:191-221) as one launch. rel, src_idx, dst_idx must be NULL, m_valid == m,
+   precision 1 or 2. */
+#define CXG_TMM_ALL_RELATIONS 8
 /* Test hook: the first tile of every CTA is never handed to the tensor-core role, so the bounded
    waits for it run out (status CXG_ETIMEOUT, all roles leave, tensor memory is released). Use it
    with a short cxg_set_wait_limit_cycles. */

@@ -118,7 +118,8 @@ def test_gat_layer(cuda, heads, concat):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("norm,schedule", [("total", "e2e"), ("total", "fused_gather"), ("total", "fused_scatter"),
-                                           ("total", "transform_first"), ("total", "auto"), ("relation", "e2e")])
+                                           ("total", "transform_first"), ("total", "auto"), ("relation", "e2e"),
+                                           ("relation", "transform_first"), ("relation", "auto")])
 def test_rgcn_layer(cuda, dtype, tol, norm, schedule):
     """Configuration 4 in small: 8 relations, 128 -> 64, edges bucketed by relation, typed matmul on the tensor
     cores (TF32 for fp32 inputs, as the reference's tl.dot), segment sum, degree normalisation."""

@@ -118,6 +118,30 @@ def test_typed_matmul_tensor_cores(cuda, dtype, k, n, tol, thres):
     assert rel_err(ce.float().cpu(), want) < (1e-5 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("num_rel,n_rows,k,n", [(8, 5000, 128, 64), (3, 130, 64, 32), (5, 40000, 64, 64), (1, 257, 32, 16)])
+def test_typed_matmul_all_relations(cuda, dtype, tol, num_rel, n_rows, k, n):
+    """Dense mode: every row times every relation's weight in one launch, [R, N, out] (the reference runs num_rel
+    torch.mm calls, typed_linear.py:195-201); forward against float64, gradients against autograd."""
+    import cxgnncomp_backend as be
+    x = randn((n_rows, k), 21).to(dtype)
+    w = (randn((num_rel, k, n), 22) * 0.2).to(dtype)
+    assert be.typed_matmul_all_relations_supported(x.cuda(), w.cuda())
+    xg, wg = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    got = be.transform_all_relations(xg, wg)
+    want = torch.matmul(x.double().unsqueeze(0), w.double())
+    assert got.shape == (num_rel, n_rows, n)
+    assert rel_err(got.detach().float().cpu(), want) < tol
+    if dtype == torch.float32:
+        plain = be.typed_matmul_all_relations(x.cuda(), w.cuda(), allow_tf32=True)
+        assert rel_err(plain.cpu(), want) < 2e-3
+        go = randn(want.shape, 23)
+        got.backward(go.cuda())
+        xr, wr = x.double().requires_grad_(True), w.double().requires_grad_(True)
+        torch.matmul(xr.unsqueeze(0), wr).backward(go.double())
+        assert rel_err(xg.grad.cpu(), xr.grad) < 1e-5 and rel_err(wg.grad.cpu(), wr.grad) < 1e-5
+
+
 def test_typed_matmul_index_variants(cuda):
     """No index, sequential output, and separate source / destination indices (the four kernels of
     triton_typed_matmul.py:145-749)."""
