@@ -26,26 +26,37 @@ __global__ void __launch_bounds__(kThreads) gather_rows_kernel(const V *in, cons
 
 // out_q[i - seg_start[q], :] = in[rows[i], :] for the peer q whose segment [seg_start[q], seg_start[q+1]) holds i:
 // the pack step of the needed-rows exchange writing straight into the receivers' feature buffers (plain 16-byte
-// stores through peer-mapped pointers over NVLink), so no send buffer and no separate transfer are needed. Blocks
-// stride over all rows, so every peer is written to at the same time.
+// stores through peer-mapped pointers over NVLink), so no send buffer and no separate transfer are needed.
 constexpr int kMaxPeers = 16;
 struct PutArgs {
   void *base[kMaxPeers];        // where the first row for peer q goes (a mapping of q's memory in this context)
   int64_t seg_start[kMaxPeers + 1];
+  int order[kMaxPeers];         // peers that receive rows, rotated so that senders start at different receivers
   int n_peer;
 };
 
+// Work is dealt in chunks of kPutChunk rows that rotate over the peers (chunk c belongs to peer order[c % n_act],
+// rows [c / n_act * kPutChunk, +kPutChunk) of that peer's segment), so at every moment this GPU writes to all
+// peers and, with every sender doing the same from a different starting peer, every receiver is written to by
+// all senders at once instead of one receiver at a time.
+constexpr int kPutChunk = 64;
+
 __global__ void __launch_bounds__(kThreads) put_rows_kernel(const uint4 *in, const int64_t *rows, PutArgs a, int vecs_per_row,
-                                                            int group) {
+                                                            int group, int n_act, int64_t chunks_per_peer) {
   const int lane = threadIdx.x % group;
-  const int64_t n_rows = a.seg_start[a.n_peer];
-  const int64_t groups = static_cast<int64_t>(gridDim.x) * (kThreads / group);
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(kThreads / group) + threadIdx.x / group; i < n_rows; i += groups) {
-    int q = 0;
-    while (q + 1 < a.n_peer && i >= a.seg_start[q + 1]) ++q;
+  const int gpb = kThreads / group;  // row groups per block
+  const int64_t total = chunks_per_peer * n_act * (kPutChunk / 1);
+  // flat index t = (chunk, row in chunk); groups stride over it
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(gpb) + threadIdx.x / group; t < total;
+       t += static_cast<int64_t>(gridDim.x) * gpb) {
+    const int64_t c = t / kPutChunk;
+    const int q = a.order[c % n_act];
+    const int64_t j = (c / n_act) * kPutChunk + (t % kPutChunk);  // row inside peer q's segment
+    const int64_t i = a.seg_start[q] + j;
+    if (i >= a.seg_start[q + 1]) continue;
     const uint4 *src = in + __ldg(rows + i) * vecs_per_row;
-    uint4 *dst = static_cast<uint4 *>(a.base[q]) + (i - a.seg_start[q]) * vecs_per_row;
-    for (int c = lane; c < vecs_per_row; c += group) dst[c] = __ldg(src + c);
+    uint4 *dst = static_cast<uint4 *>(a.base[q]) + j * vecs_per_row;
+    for (int v = lane; v < vecs_per_row; v += group) dst[v] = __ldg(src + v);
   }
 }
 
@@ -153,9 +164,25 @@ extern "C" int cxg_put_rows(const void *in, const int64_t *rows, void *const *pe
   const int vecs = static_cast<int>(row_bytes / 16);
   int group = 1;
   while (group < vecs && group < 32) group <<= 1;
-  const int64_t want = (n_rows + kThreads / group - 1) / (kThreads / group);
+  // receivers in rotated order: the first one after this rank (the rank whose own segment is empty), and so on
+  int self = 0;
+  for (int q = 0; q < n_peer; ++q)
+    if (a.seg_start[q + 1] == a.seg_start[q]) self = q;  // with several empty segments any of them will do
+  int n_act = 0;
+  int64_t max_cnt = 0;
+  for (int k = 1; k <= n_peer; ++k) {
+    const int q = (self + k) % n_peer;
+    const int64_t cnt = a.seg_start[q + 1] - a.seg_start[q];
+    if (cnt == 0) continue;
+    a.order[n_act++] = q;
+    if (cnt > max_cnt) max_cnt = cnt;
+  }
+  const int64_t chunks_per_peer = (max_cnt + kPutChunk - 1) / kPutChunk;
+  const int64_t total = chunks_per_peer * n_act * kPutChunk;
+  const int64_t want = (total + kThreads / group - 1) / (kThreads / group);
   const unsigned grid = static_cast<unsigned>(want < kNumSM * 16 ? want : kNumSM * 16);
-  put_rows_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(static_cast<const uint4 *>(in), rows, a, vecs, group);
+  put_rows_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(static_cast<const uint4 *>(in), rows, a, vecs, group, n_act,
+                                                            chunks_per_peer);
   count_launches(1);
   return check_launch("cxg_put_rows");
 }

@@ -32,7 +32,7 @@
 // accumulates A_hi.W_lo + A_lo.W_hi + A_hi.W_hi into the same tensor-memory accumulator, which restores fp32
 // accuracy (about 1e-6) while the tensor pipe, idle most of the time on this memory-bound op, absorbs the two
 // extra instructions. W is split once by the transposing pre-pass; a tile of A is split in shared memory by
-// four converter warps between the producers and the MMA thread (raw -> hi in place, lo into the second half of
+// converter warps between the producers and the MMA thread (raw -> hi in place, lo into the second half of
 // the stage). To keep several stages in flight with stages twice as large, the K dimension is cut into blocks:
 // the pipeline unit is (tile, K-block) and all blocks of a tile accumulate into one accumulator buffer.
 //
@@ -62,7 +62,10 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kEpiWarps = 4;
 constexpr int kMaxProdWarps = 8;  // producer warps: 8 for 4-byte elements, 4 for 2-byte ones (measured)
-constexpr int kConvWarps = 4;     // converter warps of the error-compensated fp32 mode
+#ifndef CXG_TMM_CONV_WARPS
+#define CXG_TMM_CONV_WARPS 8
+#endif
+constexpr int kConvWarps = CXG_TMM_CONV_WARPS;  // converter warps of the error-compensated fp32 mode
 constexpr int kMmaWarp = kEpiWarps;                              // warp 4
 constexpr int kMaxStages = 6;
 constexpr int kRpi = 8, kCpi = 32 / kRpi;  // rows / chunks per warp copy instruction

@@ -40,6 +40,8 @@ def test_static_scratch_matches_workspace_entry_point(cuda):
     assert _call_static(be, p, i, xg, got, 500) == 0
     torch.cuda.synchronize()
     assert torch.equal(got, want)  # same kernels, same order: no tolerance needed
+    import oracle
+    assert torch.equal(got.cpu(), oracle.spmm(ptr, idx, x, tile=64))  # and the CPU oracle's bits (64-edge tiles here)
     # second call straight after, other graph, other dtype, mean: the array still holds the first call's data
     ptr2, idx2 = random_csr(300, 300, 7, seed=103, hub=4000)
     x2 = randn((300, 64), 104, dtype=torch.bfloat16)
