@@ -23,6 +23,8 @@
 // 64 of them; beyond that in blocks of 64 consecutive partials, one warp per block,
 // whose sums are then added in block order), so results do not depend on scheduling
 // and can be reproduced on a CPU given T.
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "common.cuh"
@@ -637,22 +639,26 @@ struct FastAcc<__nv_bfloat16, CB> {
   }
 };
 
-template <typename T, int CB, typename IdxT, bool ACC>
-__global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(StreamArgs a) {
+// NS = stages in flight per warp: 2 (two stages of 4 KiB, the default) or 1 (the whole 8 KiB as one stage).
+#ifndef CXG_FAST_CTAS
+#define CXG_FAST_CTAS 7  // resident CTAs per SM of the lean walk (72 registers, 7 x 32 KiB of shared memory)
+#endif
+template <typename T, int CB, typename IdxT, bool ACC, int NS>
+__global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(StreamArgs a) {
   using C = Chunk<T, CB>;
   using Acc = FastAcc<T, CB>;
   constexpr int EL = C::kElems;
   constexpr int W = C::kWords;
   constexpr int RB = 32 * CB;                        // bytes per row
-  constexpr int B = kStageBytes / RB > 32 ? 32 : kStageBytes / RB;  // edges per stage
+  constexpr int B = (kStageBytes / NS) / RB > 32 ? 32 : (kStageBytes / NS) / RB;  // edges per stage
   constexpr int CPR = RB / 16;                       // 16-byte chunks per row
   constexpr int RPI = 32 / CPR;                      // rows per copy instruction
   constexpr int NCOPY = B * CPR / 32;                // copy instructions per full stage
   extern __shared__ __align__(128) uint8_t smem[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const uint32_t sl = smem_u32(smem + static_cast<size_t>(warp) * (B * RB));
-  const uint32_t my = sl + lane * CB;                // this lane's columns of the stage's first row
+  const uint32_t sl = smem_u32(smem + static_cast<size_t>(warp) * (NS * B * RB));  // NS stage slots of B rows
+  const uint32_t my = sl + lane * CB;                // this lane's columns of the first slot's first row
   const IdxT *idx = reinterpret_cast<const IdxT *>(a.idx);
   const uint8_t *x = reinterpret_cast<const uint8_t *>(a.x);
   uint8_t *y = reinterpret_cast<uint8_t *>(a.y) + lane * CB;
@@ -704,37 +710,41 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(Stream
       const int pos = k * B + lane;
       return (lane < B && pos < tile_len) ? static_cast<uint32_t>(load_idx_stream(idx_t + pos)) : 0u;
     };
+    // stage k goes to slot k % NS; exactly one group is committed per call (an empty one past the last stage), so
+    // "all but the newest NS - 1 groups complete" means stage k has landed
     auto fill = [&](int k, uint32_t nid) {
       const int cnt = tile_len - k * B;
+      const uint32_t dst = cdst + (NS == 1 ? 0 : (k & (NS - 1)) * (B * RB));
       if (cnt >= B) {  // full stage: no bounds test per copy
 #pragma unroll
         for (int c = 0; c < NCOPY; ++c) {
           const uint32_t nj = __shfl_sync(0xffffffffu, nid, c * RPI + jrow);
-          cp_async16(cdst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
+          cp_async16(dst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
         }
-      } else {
+      } else if (cnt > 0) {
 #pragma unroll
         for (int c = 0; c < NCOPY; ++c) {
           const uint32_t nj = __shfl_sync(0xffffffffu, nid, (c * RPI + jrow) & 31);
-          if (c * RPI + jrow < cnt) cp_async16(cdst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
+          if (c * RPI + jrow < cnt) cp_async16(dst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     fill(0, load_nid(0));
+    if (NS == 2) fill(1, load_nid(1));
     Acc acc;
     acc.zero();
     float f[EL];
 
     for (int k = 0; k < n_stage; ++k) {
-      const uint32_t nid_next = load_nid(k + 1);
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      const uint32_t nid_next = load_nid(k + NS);
+      asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
       __syncwarp();
       const int sbase = k * B;
       const int send = min(sbase + B, tile_len);
       int pos = sbase;
-      uint32_t p = my;  // shared address of this lane's bytes of edge `pos`
+      uint32_t p = my + (NS == 1 ? 0 : (k & (NS - 1)) * (B * RB));  // shared address of this lane's bytes of edge `pos`
       while (pos < send) {
         const int stop = min(send, rend);
         int n = stop - pos;
@@ -794,8 +804,12 @@ __global__ void __launch_bounds__(kSThreads, kCtasPerSM) spmm_stream_fast(Stream
         }
       }
       __syncwarp();
-      if (k + 1 < n_stage) fill(k + 1, nid_next);
+      if (NS == 2)
+        fill(k + 2, nid_next);  // also past the last stage: an empty group keeps the group count in step
+      else if (k + 1 < n_stage)
+        fill(k + 1, nid_next);
     }
+    if (NS == 2) asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups are left
     int64_t tail = -1;
     if (row < a.n_dst && rstart < tile_len && rend > tile_len) {
       acc.get(f);
@@ -1005,9 +1019,14 @@ cudaError_t launch_stream1(const StreamArgs &a, int cb, int nv, int valmode, int
 template <typename T, int CB, typename IdxT>
 cudaError_t launch_fast3(const StreamArgs &a, int grid, cudaStream_t st) {
   constexpr int RB = 32 * CB;
-  constexpr int B = kStageBytes / RB > 32 ? 32 : kStageBytes / RB;
-  const size_t smem = static_cast<size_t>(B) * RB * kSWarps;
-  auto k = a.accumulate ? spmm_stream_fast<T, CB, IdxT, true> : spmm_stream_fast<T, CB, IdxT, false>;
+  // two half-size stages in flight per warp (measured 2-3 % faster than one 8 KiB stage on every graph size)
+  bool two = kStageBytes / 2 / RB >= 4;
+  if (const char *env = getenv("CXG_SPMM_STAGES")) two = atoi(env) == 2 && kStageBytes / 2 / RB >= 4;  // tuning aid
+  const int rows = two ? 2 * ((kStageBytes / 2) / RB > 32 ? 32 : (kStageBytes / 2) / RB)
+                       : (kStageBytes / RB > 32 ? 32 : kStageBytes / RB);
+  const size_t smem = static_cast<size_t>(rows) * RB * kSWarps;
+  auto k = a.accumulate ? (two ? spmm_stream_fast<T, CB, IdxT, true, 2> : spmm_stream_fast<T, CB, IdxT, true, 1>)
+                        : (two ? spmm_stream_fast<T, CB, IdxT, false, 2> : spmm_stream_fast<T, CB, IdxT, false, 1>);
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   k<<<grid, kSThreads, smem, st>>>(a);
@@ -1137,13 +1156,18 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
   spmm_stream_plan<<<pb, 256, 0, st>>>(a);
   // CXG_SPMM_SHARE_SMS: four persistent CTAs per SM instead of six, so that a kernel of another stream (a
   // collective's copy kernel) finds registers and shared memory on every SM while this one runs
-  const int grid = kNumSM * ((d->flags & CXG_SPMM_SHARE_SMS) ? 4 : kCtasPerSM);
+  int grid = kNumSM * ((d->flags & CXG_SPMM_SHARE_SMS) ? 4 : kCtasPerSM);
   cudaError_t e;
   // the lean kernel covers full-warp rows without per-edge extras; ids are kept as 32-bit there (a feature matrix
   // of 2^32 rows of 128 bytes would not fit the device)
   const bool fast = row_bytes == 32 * cb && valmode == 0 && a.mode == kModeCpAsync && d->edge_rel == nullptr &&
                     d->targets == nullptr && !(d->flags & CXG_SPMM_GENERIC_WALK);
   if (fast) {
+    if (!(d->flags & CXG_SPMM_SHARE_SMS)) {
+      int ctas = CXG_FAST_CTAS;
+      if (const char *env = getenv("CXG_SPMM_FAST_CTAS")) ctas = atoi(env) > 0 ? atoi(env) : ctas;  // tuning aid
+      grid = kNumSM * ctas;
+    }
     e = launch_fast(a, d->dtype, cb, d->idx_bytes, grid, st);
   } else if (d->dtype == CXG_F32)
     e = d->idx_bytes == 8 ? launch_stream1<float, int64_t>(a, cb, nv, valmode, grid, smem, st)

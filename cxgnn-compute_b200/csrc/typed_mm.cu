@@ -63,7 +63,7 @@ constexpr int kTileM = 128;
 constexpr int kEpiWarps = 4;
 constexpr int kMaxProdWarps = 8;  // producer warps: 8 for 4-byte elements, 4 for 2-byte ones (measured)
 #ifndef CXG_TMM_CONV_WARPS
-#define CXG_TMM_CONV_WARPS 8
+#define CXG_TMM_CONV_WARPS 4
 #endif
 constexpr int kConvWarps = CXG_TMM_CONV_WARPS;  // converter warps of the error-compensated fp32 mode
 constexpr int kMmaWarp = kEpiWarps;                              // warp 4

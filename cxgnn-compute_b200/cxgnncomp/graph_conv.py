@@ -346,8 +346,8 @@ class MyRGCNConv(torch.nn.Module):
                     self._inv_rel_count = (1.0 / cnt[key].float()).contiguous()
                 return _AggrRelValFunction.apply(table, ptr, idx, self._types32[1], self._inv_rel_count, num_node,
                                                  self.num_rel)
-            out = cxgnncomp_backend.aggr_rel(table, ptr, idx, self._types32[1], num_node, self.num_rel)
-            return out / deg.unsqueeze(-1)
+            # aggregation and division by the in-degree in one kernel
+            return cxgnncomp_backend.aggr_rel_mean(table, ptr, idx, self._types32[1], num_node, self.num_rel)
         if len(self.preprocessed) == 0:  # relation buckets, built on the first call like the reference caches them
             self.preprocessed = TypedLinearE2EOP.preprocess(self.linear, edge_types)
         if self.norm == "total" and schedule != "e2e":

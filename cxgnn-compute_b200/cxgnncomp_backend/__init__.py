@@ -736,28 +736,36 @@ def target_aggr_backward(grad_in, ptr, idx, targets, grad_out, num_node):
 
 
 class _AggrRelFunction(torch.autograd.Function):
-    """AggrRelFunction (src/cpp/src/rel_spmm.cu:37-135)."""
+    """AggrRelFunction (src/cpp/src/rel_spmm.cu:37-135); `reduce` = CXG_MEAN divides every row by its edge count in
+    the same kernel (the degree normalisation of MyRGCNConv, cxgnncomp/graph_conv.py:370-375)."""
 
     @staticmethod
-    def forward(ctx, x, ptr, idx, etype, num_node, num_rel):
+    def forward(ctx, x, ptr, idx, etype, num_node, num_rel, reduce):
         ctx.save_for_backward(x, ptr, idx, etype)
-        ctx.num_node, ctx.num_rel = num_node, num_rel
+        ctx.num_node, ctx.num_rel, ctx.reduce = num_node, num_rel, reduce
         stride = x.shape[0] // num_rel
-        return _spmm_forward(x, ptr, idx, num_node, edge_rel=etype, rel_stride=stride)
+        return _spmm_forward(x, ptr, idx, num_node, edge_rel=etype, rel_stride=stride, reduce=reduce)
 
     @staticmethod
     def backward(ctx, grad_out):
         x, ptr, idx, etype = ctx.saved_tensors
         stride = x.shape[0] // ctx.num_rel
-        dx, _ = _spmm_backward(grad_out, x, ptr, idx, ctx.num_node, edge_rel=etype, rel_stride=stride)
-        return dx.to(x.dtype), None, None, None, None, None
+        dx, _ = _spmm_backward(grad_out, x, ptr, idx, ctx.num_node, edge_rel=etype, rel_stride=stride, reduce=ctx.reduce)
+        return dx.to(x.dtype), None, None, None, None, None, None
 
 
 def aggr_rel(x, ptr, idx, etype, num_node, num_rel):
     """out[r] = sum_e x[etype[e] * N + idx[e]] with x = [num_rel * N, F] already transformed per
     relation; etype is int32 (binding.cpp:45, rel_spmm.cu:8-70)."""
     _cuda(etype, "etype", (torch.int32,))
-    return _AggrRelFunction.apply(x, ptr, idx, etype, num_node, num_rel)
+    return _AggrRelFunction.apply(x, ptr, idx, etype, num_node, num_rel, CXG_SUM)
+
+
+def aggr_rel_mean(x, ptr, idx, etype, num_node, num_rel):
+    """aggr_rel divided by the number of edges of every destination (0 for destinations without edges), in one
+    kernel: the aggregation + total-degree normalisation of the RGCN layer (cxgnncomp/graph_conv.py:370-375)."""
+    _cuda(etype, "etype", (torch.int32,))
+    return _AggrRelFunction.apply(x, ptr, idx, etype, num_node, num_rel, CXG_MEAN)
 
 
 # --------------------------------------------------------------------------------------
