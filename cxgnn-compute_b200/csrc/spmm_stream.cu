@@ -23,8 +23,6 @@
 // 64 of them; beyond that in blocks of 64 consecutive partials, one warp per block,
 // whose sums are then added in block order), so results do not depend on scheduling
 // and can be reproduced on a CPU given T.
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "common.cuh"
@@ -641,7 +639,7 @@ struct FastAcc<__nv_bfloat16, CB> {
 
 // NS = stages in flight per warp: 2 (two stages of 4 KiB, the default) or 1 (the whole 8 KiB as one stage).
 #ifndef CXG_FAST_CTAS
-#define CXG_FAST_CTAS 7  // resident CTAs per SM of the lean walk (72 registers, 7 x 32 KiB of shared memory)
+#define CXG_FAST_CTAS kCtasPerSM  // resident CTAs per SM of the lean walk (7 measured 25 % slower: more warps, more L2 misses)
 #endif
 template <typename T, int CB, typename IdxT, bool ACC, int NS>
 __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(StreamArgs a) {
@@ -1020,8 +1018,7 @@ template <typename T, int CB, typename IdxT>
 cudaError_t launch_fast3(const StreamArgs &a, int grid, cudaStream_t st) {
   constexpr int RB = 32 * CB;
   // two half-size stages in flight per warp (measured 2-3 % faster than one 8 KiB stage on every graph size)
-  bool two = kStageBytes / 2 / RB >= 4;
-  if (const char *env = getenv("CXG_SPMM_STAGES")) two = atoi(env) == 2 && kStageBytes / 2 / RB >= 4;  // tuning aid
+  const bool two = kStageBytes / 2 / RB >= 4;
   const int rows = two ? 2 * ((kStageBytes / 2) / RB > 32 ? 32 : (kStageBytes / 2) / RB)
                        : (kStageBytes / RB > 32 ? 32 : kStageBytes / RB);
   const size_t smem = static_cast<size_t>(rows) * RB * kSWarps;
@@ -1164,9 +1161,7 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
                     d->targets == nullptr && !(d->flags & CXG_SPMM_GENERIC_WALK);
   if (fast) {
     if (!(d->flags & CXG_SPMM_SHARE_SMS)) {
-      int ctas = CXG_FAST_CTAS;
-      if (const char *env = getenv("CXG_SPMM_FAST_CTAS")) ctas = atoi(env) > 0 ? atoi(env) : ctas;  // tuning aid
-      grid = kNumSM * ctas;
+      grid = kNumSM * CXG_FAST_CTAS;
     }
     e = launch_fast(a, d->dtype, cb, d->idx_bytes, grid, st);
   } else if (d->dtype == CXG_F32)

@@ -47,8 +47,6 @@
 // Every wait is bounded: a role that waits longer than about a second raises a CTA-wide abort
 // flag and an error status; all roles then leave their loops, the copies in flight are waited
 // for, the tensor memory is released and the kernel returns.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace cxg {
@@ -613,10 +611,6 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   int kb = k;
   const int want = x3 ? 4 : (dense ? 3 : 1);
   while (b_bytes + want * stage_bytes(kb) > static_cast<size_t>(kSmemBudget) && kb % (4 * epc) == 0) kb /= 2;
-  if (const char *env = getenv("CXG_TMM_KBLOCK")) {  // tuning aid: force the K-block (must divide K, multiple of 32 bytes)
-    const int v = atoi(env);
-    if (v > 0 && k % v == 0 && v % (2 * epc) == 0) kb = v;
-  }
   const size_t a_bytes = stage_bytes(kb);
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
               "cxg_typed_matmul: one stage of %zu bytes plus W of %zu bytes exceeds shared memory", a_bytes, b_bytes);

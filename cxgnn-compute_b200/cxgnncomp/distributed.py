@@ -268,11 +268,29 @@ class NeededRowsExchange:
             recv_buf = torch.empty((self.send_rows.shape[0], dx_buf.shape[1]), dtype=dx_buf.dtype, device=dx_buf.device)
         dist.all_to_all_single(recv_buf, dx_buf[self.n_own:].contiguous(), self.send_counts, self.recv_counts,
                                group=self.group)
-        if unpack is None:
-            dx_own.index_add_(0, self.send_rows, recv_buf)
-        else:
+        if unpack is not None:
             unpack(dx_own, self.send_rows, recv_buf)
+        elif dx_own.is_cuda and dx_own.dtype in (torch.float32, torch.bfloat16):
+            # every own row gathers the received rows that belong to it, in the order they arrived (sender by
+            # sender): an accumulating aggregation over the transposed request list, no atomics, same bits every run
+            t_ptr, t_idx = self._unpack_graph()
+            import cxgnncomp_backend
+            cxgnncomp_backend.spmm_into(dx_own, t_ptr, t_idx, recv_buf, self.n_own, accumulate=True)
+        else:
+            dx_own.index_add_(0, self.send_rows, recv_buf)
         return dx_own
+
+    def _unpack_graph(self):
+        """CSR over this rank's own rows listing, for every row, the positions of the receive buffer that hold a
+        partial gradient for it (the transpose of send_rows, built once per plan on the device)."""
+        cached = getattr(self, "_unpack", None)
+        if cached is None:
+            import cxgnncomp_backend
+            n_recv = self.send_rows.shape[0]
+            ptr = torch.arange(n_recv + 1, dtype=torch.int64, device=self.send_rows.device)
+            t_ptr, t_idx, _, _ = cxgnncomp_backend.csr_transpose(ptr, self.send_rows, n_recv, self.n_own, want_eid=False)
+            cached = self._unpack = (t_ptr, t_idx)
+        return cached
 
     def exchange(self, x_buf, send_buf=None, pack=None, async_op=False, chunks=1):
         """x_buf [buffer_rows, F] with this rank's shard already in x_buf[:n_own]; fills the remote part.
