@@ -519,8 +519,8 @@ def main():
                 "data": "synthetic",
                 "config": {"workload": args.workload, "description": desc, "nodes": n, "nnz": nnz, "feat": feat,
                            "idx_bytes": idx_bytes, "partition": f"rows by edge count over {world} GPU(s)",
-                           "exchange": exchange_mode + (f" in {exchange_chunks} chunks" if ex is not None and
-                                                        exchange_chunks > 1 else "") +
+                           "exchange": exchange_mode + (f" in {exchange_chunks} chunks" if exchange_mode in ("needed", "putcopy")
+                                                        and exchange_chunks > 1 else "") +
                            (", overlapped with the aggregation of the rows already there" if overlap else ""),
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
