@@ -223,6 +223,9 @@ def main():
                          "accumulate the rest (auto = off: at 2 GPUs the second pass over the output rows costs what "
                          "the overlap hides, 45.1 vs 44.4 ms per step)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--backward", action="store_true",
+                    help="also time the backward of the step (dX = A^T dY over the transposed local graph, then the "
+                         "return of the remote rows' partial gradients to their owners) and add it as \"backward\"")
     ap.add_argument("--no-layers", action="store_true",
                     help="skip the per-layer records of configurations 1, 2 and 4 (added at 1 GPU by default)")
     ap.add_argument("--no-cpu", action="store_true")
@@ -245,7 +248,7 @@ def main():
     import torch.distributed as dist
     import cxgnncomp_backend as be
     from cxgnncomp import synthetic
-    from cxgnncomp.distributed import NeededRowsExchange, RowPartition, exchange_features
+    from cxgnncomp.distributed import NeededRowsExchange, RowPartition, exchange_features, reduce_gradients
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local_rank)
@@ -479,6 +482,55 @@ def main():
                        "of step k and download of step k-1 overlap")}
         del hx, hy
 
+    # backward of the step (not part of the headline): every rank aggregates the upstream gradient of its rows over
+    # its transposed local graph into a gradient in the layout of the feature buffer, then the partial gradients of
+    # remote rows go back to their owners (needed-rows plans: all-to-all + an accumulating aggregation over the
+    # transposed request list; all-gather layout: one reduce-scatter)
+    backward = None
+    if args.backward:
+        n_src = x_full.shape[0]
+        a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_ev.record()
+        t_ptr, t_idx, _, _ = be.csr_transpose(lptr, lidx, n_local, n_src, want_eid=False)
+        b_ev.record()
+        b_ev.synchronize()
+        transpose_ms = a_ev.elapsed_time(b_ev)
+        dx = torch.empty((n_src, feat), dtype=dtype, device=dev)
+
+        def local_backward():
+            return be.spmm_into(dx, t_ptr, t_idx, y, n_src)
+
+        def return_gradients():
+            if world == 1:
+                return dx
+            if ex is not None:
+                return ex.exchange_backward(dx, send_buf)
+            return reduce_gradients(dx, part, rank)
+
+        def backward_step():
+            local_backward()
+            return return_gradients()
+
+        for _ in range(2):
+            backward_step()
+        barrier()
+        t_b = [timed(backward_step, args.steps) / args.steps]
+        barrier()
+        t_b.append(timed(local_backward, args.steps) / args.steps)
+        barrier()
+        t_b.append(timed(return_gradients, args.steps) / args.steps)
+        barrier()
+        tb = torch.tensor(t_b + [transpose_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+        backward = {"ms_per_step": float(tb[0]), "transposed_aggregation_ms": float(tb[1]),
+                    "gradient_return_ms": float(tb[2]), "transpose_once_ms": float(tb[3]),
+                    "return": "none" if world == 1 else ("all-to-all + accumulating aggregation" if ex is not None
+                                                         else "reduce-scatter"),
+                    "note": "max over ranks; the transposed graph is built once per graph and kept"}
+        del dx, t_ptr, t_idx
+        torch.cuda.empty_cache()
+
     peak, peak_src = load_peaks()
     achieved = b_alg_local / (spmm_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -524,7 +576,7 @@ def main():
                            (", overlapped with the aggregation of the rows already there" if overlap else ""),
                            "l2": "256 MiB written between timed steps; inputs exceed L2"},
                 "gflops": 2.0 * nnz * feat / (ms_step * 1e-3) / 1e9, "frac_of_hbm_peak": value / peak / world,
-                "gpu_launches": int(launches), "roofline": roofline, "layers": layers, "exchange": exchange_info, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
+                "gpu_launches": int(launches), "roofline": roofline, "layers": layers, "exchange": exchange_info, "backward": backward, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks}
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:

@@ -641,7 +641,12 @@ struct FastAcc<__nv_bfloat16, CB> {
 #ifndef CXG_FAST_CTAS
 #define CXG_FAST_CTAS kCtasPerSM  // resident CTAs per SM of the lean walk (7 measured 25 % slower: more warps, more L2 misses)
 #endif
-template <typename T, int CB, typename IdxT, bool ACC, int NS>
+// IDXS: the tile's source ids are not loaded by the lanes but staged by the bulk-copy unit (TMA): one
+// `cp.async.bulk` of 512 bytes (128 int32 / 64 int64 ids) per chunk into a two-slot ring per warp, completion on an
+// mbarrier, the next chunk (of this tile or of the warp's next tile) requested when a chunk is first read. The
+// copy lanes then take the id of their row from shared memory instead of a shuffle. The waits are bounded like
+// those of the bulk-row variant.
+template <typename T, int CB, typename IdxT, bool ACC, int NS, bool IDXS>
 __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(StreamArgs a) {
   using C = Chunk<T, CB>;
   using Acc = FastAcc<T, CB>;
@@ -669,6 +674,20 @@ __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(Str
   const int jrow = lane / CPR;
   const uint8_t *xlane = x + (lane % CPR) * 16;
   const uint32_t cdst = sl + lane * 16;
+  // id ring (IDXS): two slots of kIdxChunkBytes per warp behind the row slots of all warps, then two barriers per warp
+  constexpr int CH = kIdxChunkBytes / static_cast<int>(sizeof(IdxT));  // ids per chunk; a multiple of B
+  const uint32_t ibuf = smem_u32(smem + static_cast<size_t>(kSWarps) * (NS * B * RB) + warp * (2 * kIdxChunkBytes));
+  const uint32_t ibar = smem_u32(smem + static_cast<size_t>(kSWarps) * (NS * B * RB + 2 * kIdxChunkBytes) + warp * 16);
+  uint32_t g_issue = 0, g_wait = 0;  // chunks requested / consumed by this warp so far (slot = number & 1)
+  bool dead = false;
+  if (IDXS) {
+    if (lane == 0) {
+      mbar_init(ibar, 1);
+      mbar_init(ibar + 8, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+  }
 
   auto zero_row = [&](int64_t r) {
     if (ACC) return;  // y[r] += 0
@@ -683,10 +702,34 @@ __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(Str
     return;
   }
 
+  // requests chunk c of tile t2 into slot g_issue & 1; every lane of the warp has finished reading that slot (the
+  // caller passed a __syncwarp since). The part that is a multiple of 16 bytes goes through the copy unit, the
+  // last few ids of the graph's last tile (fewer than 16 bytes) through the lanes.
+  auto request_chunk = [&](int64_t t2, int c) {
+    const int64_t e0 = t2 * a.tile + static_cast<int64_t>(c) * CH;
+    const int64_t left = min(static_cast<int64_t>(a.tile) - static_cast<int64_t>(c) * CH, e_total - e0);
+    const int len = static_cast<int>(min(static_cast<int64_t>(CH), left));
+    const uint32_t bulk = (static_cast<uint32_t>(len) * static_cast<uint32_t>(sizeof(IdxT))) & ~15u;
+    const uint32_t slot = ibuf + (g_issue & 1u) * kIdxChunkBytes;
+    const uint32_t bar = ibar + (g_issue & 1u) * 8;
+    if (lane == 0) {
+      mbar_expect_tx(bar, bulk + ((a.test_stall && g_issue == 0) ? 16u : 0u));
+      if (bulk) bulk_g2s(slot, idx + e0, bulk, bar);
+    }
+    const int done = static_cast<int>(bulk / sizeof(IdxT));
+    if (lane < len - done) {
+      const uint32_t v = static_cast<uint32_t>(load_idx_stream(idx + e0 + done + lane));
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot + (done + lane) * static_cast<uint32_t>(sizeof(IdxT))), "r"(v) : "memory");
+    }
+    ++g_issue;
+  };
+  if (IDXS && gwarp < n_tiles) request_chunk(gwarp, 0);
+
   for (int64_t t = gwarp; t < n_tiles; t += nwarps) {
     const int64_t tb = t * a.tile;
     const int tile_len = static_cast<int>(min(static_cast<int64_t>(a.tile), e_total - tb));
     const int n_stage = (tile_len + B - 1) / B;
+    const int n_chunk = (tile_len + CH - 1) / CH;
     int64_t row = a.tile_row[t];
     if (t == 0)
       for (int64_t r = 0; r < row; ++r) zero_row(r);
@@ -705,6 +748,7 @@ __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(Str
     const IdxT *idx_t = idx + tb;
 
     auto load_nid = [&](int k) -> uint32_t {
+      if (IDXS) return 0u;
       const int pos = k * B + lane;
       return (lane < B && pos < tile_len) ? static_cast<uint32_t>(load_idx_stream(idx_t + pos)) : 0u;
     };
@@ -713,16 +757,55 @@ __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(Str
     auto fill = [&](int k, uint32_t nid) {
       const int cnt = tile_len - k * B;
       const uint32_t dst = cdst + (NS == 1 ? 0 : (k & (NS - 1)) * (B * RB));
-      if (cnt >= B) {  // full stage: no bounds test per copy
+      uint32_t ids = 0;  // IDXS: shared address of the id of this lane's row of the stage's first copy group
+      if (IDXS && cnt > 0 && !dead) {
+        const int in_chunk = (k * B) % CH;
+        if (in_chunk == 0) {  // first stage of a chunk: wait for it, then request the one after it
+          const uint32_t bar = ibar + (g_wait & 1u) * 8;
+          const uint32_t parity = (g_wait >> 1) & 1u;
+          if (!mbar_try_wait(bar, parity)) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar, parity)) {
+              if (clock64() - t0 > a.wait_cycles) {
+                dead = true;
+                break;
+              }
+            }
+          }
+          dead = __any_sync(0xffffffffu, dead);  // also orders the lanes' own id stores and the reads of the other slot
+          ++g_wait;
+          if (!dead) {
+            const int c = (k * B) / CH;
+            if (c + 1 < n_chunk)
+              request_chunk(t, c + 1);
+            else if (t + nwarps < n_tiles)
+              request_chunk(t + nwarps, 0);
+          }
+        }
+        ids = ibuf + ((g_wait - 1) & 1u) * kIdxChunkBytes + (in_chunk + jrow) * static_cast<uint32_t>(sizeof(IdxT));
+      }
+      if (IDXS && dead) {
+        // the stage's copies are not issued; the group below stays empty
+      } else if (cnt >= B) {  // full stage: no bounds test per copy
 #pragma unroll
         for (int c = 0; c < NCOPY; ++c) {
-          const uint32_t nj = __shfl_sync(0xffffffffu, nid, c * RPI + jrow);
+          uint32_t nj;
+          if (IDXS)
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(nj) : "r"(ids + c * RPI * static_cast<uint32_t>(sizeof(IdxT))));
+          else
+            nj = __shfl_sync(0xffffffffu, nid, c * RPI + jrow);
           cp_async16(dst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
         }
       } else if (cnt > 0) {
 #pragma unroll
         for (int c = 0; c < NCOPY; ++c) {
-          const uint32_t nj = __shfl_sync(0xffffffffu, nid, (c * RPI + jrow) & 31);
+          uint32_t nj = 0;
+          if (IDXS) {
+            if (c * RPI + jrow < cnt)
+              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(nj) : "r"(ids + c * RPI * static_cast<uint32_t>(sizeof(IdxT))));
+          } else {
+            nj = __shfl_sync(0xffffffffu, nid, (c * RPI + jrow) & 31);
+          }
           if (c * RPI + jrow < cnt) cp_async16(dst + c * 512, xlane + static_cast<uint64_t>(nj) * RB);
         }
       }
@@ -736,6 +819,7 @@ __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(Str
     float f[EL];
 
     for (int k = 0; k < n_stage; ++k) {
+      if (IDXS && dead) break;
       const uint32_t nid_next = load_nid(k + NS);
       asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
       __syncwarp();
@@ -808,6 +892,13 @@ __global__ void __launch_bounds__(kSThreads, CXG_FAST_CTAS) spmm_stream_fast(Str
         fill(k + 1, nid_next);
     }
     if (NS == 2) asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups are left
+    if (IDXS && dead) {
+      // An id chunk did not arrive within the limit. The row copies of this warp have been waited for above and no
+      // other chunk is requested; the tile's tail_row keeps the -1 of the plan kernel and the fix-up kernels do
+      // nothing once the error word is set.
+      if (lane == 0) atomicExch(a.hdr + kSHdrError, kSErrTimeout);
+      break;
+    }
     int64_t tail = -1;
     if (row < a.n_dst && rstart < tile_len && rend > tile_len) {
       acc.get(f);
@@ -1021,9 +1112,12 @@ cudaError_t launch_fast3(const StreamArgs &a, int grid, cudaStream_t st) {
   const bool two = kStageBytes / 2 / RB >= 4;
   const int rows = two ? 2 * ((kStageBytes / 2) / RB > 32 ? 32 : (kStageBytes / 2) / RB)
                        : (kStageBytes / RB > 32 ? 32 : kStageBytes / RB);
-  const size_t smem = static_cast<size_t>(rows) * RB * kSWarps;
-  auto k = a.accumulate ? (two ? spmm_stream_fast<T, CB, IdxT, true, 2> : spmm_stream_fast<T, CB, IdxT, true, 1>)
-                        : (two ? spmm_stream_fast<T, CB, IdxT, false, 2> : spmm_stream_fast<T, CB, IdxT, false, 1>);
+  const bool idxs = two && a.tma_index;
+  const size_t smem = static_cast<size_t>(rows) * RB * kSWarps + (idxs ? kSWarps * (2 * kIdxChunkBytes + 16) : 0);
+  auto k = idxs ? (a.accumulate ? spmm_stream_fast<T, CB, IdxT, true, 2, true> : spmm_stream_fast<T, CB, IdxT, false, 2, true>)
+           : a.accumulate
+               ? (two ? spmm_stream_fast<T, CB, IdxT, true, 2, false> : spmm_stream_fast<T, CB, IdxT, true, 1, false>)
+               : (two ? spmm_stream_fast<T, CB, IdxT, false, 2, false> : spmm_stream_fast<T, CB, IdxT, false, 1, false>);
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   k<<<grid, kSThreads, smem, st>>>(a);
@@ -1108,6 +1202,7 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
   a.n_dst = d->n_dst, a.nnz = d->nnz, a.rel_stride = d->rel_stride;
   a.wait_cycles = wait_limit_cycles();
   a.test_stall = (d->flags & CXG_SPMM_TEST_STALL) ? 1 : 0;
+  a.tma_index = 0;
   a.feat = d->feat, a.heads = d->heads, a.width = d->feat * d->heads;
   a.ptr_bytes = d->ptr_bytes, a.reduce = d->reduce;
   a.accumulate = (d->flags & CXG_SPMM_ACCUMULATE) ? 1 : 0;
@@ -1163,6 +1258,8 @@ int stream_launch(const cxg_spmm_desc *d, void *workspace, size_t workspace_byte
     if (!(d->flags & CXG_SPMM_SHARE_SMS)) {
       grid = kNumSM * CXG_FAST_CTAS;
     }
+    // the bulk copies of the id ring need 16-byte aligned sources: tiles are multiples of 32 ids, so the base decides
+    a.tma_index = (d->flags & CXG_SPMM_TMA_INDEX) && reinterpret_cast<uintptr_t>(d->idx) % 16 == 0 && a.tile % 32 == 0;
     e = launch_fast(a, d->dtype, cb, d->idx_bytes, grid, st);
   } else if (d->dtype == CXG_F32)
     e = d->idx_bytes == 8 ? launch_stream1<float, int64_t>(a, cb, nv, valmode, grid, smem, st)

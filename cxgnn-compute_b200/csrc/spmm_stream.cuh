@@ -11,6 +11,8 @@ enum { kSErrNone = 0, kSErrTimeout = 1, kSErrEdgeCount = 2 };
 // Row fetch variants: 16-byte async copies into shared memory (default), one bulk
 // async copy per row into shared memory.
 enum { kModeCpAsync = 0, kModeBulk = 1 };
+// Bytes of one chunk of the id ring of the lean walk (two chunks per warp).
+constexpr int kIdxChunkBytes = 512;
 
 struct StreamArgs {
   const void *ptr;
@@ -36,6 +38,7 @@ struct StreamArgs {
   int max_blocks;
   int cpr_shift;  // log2(16-byte chunks per row), -1 when not a power of two
   int mode;       // how feature rows are fetched: kModeCpAsync / kModeBulk
+  int tma_index;  // lean walk: source ids staged by bulk copies into a ring in shared memory
   int32_t *hdr;
   int64_t *tile_row;    // row that owns the first edge of each tile
   int64_t *tail_row;    // row left unfinished at the end of each tile, or -1

@@ -22,9 +22,12 @@
 //   * one thread issues K/16 (bf16) or K/8 (tf32) `tcgen05.mma` instructions per tile with M = 128,
 //     N = n, accumulating fp32 in one of two tensor-memory buffers, and commits them to the
 //     barrier that frees the stage and to the one that hands the accumulator to the epilogue;
-//   * 4 epilogue warps read their 32 accumulator lanes with `tcgen05.ld`, convert, and write (or
-//     atomically add) the rows of C at their scattered destinations while the next tile's MMAs
-//     run into the other buffer.
+//   * 8 epilogue warps (4 in the error-compensated mode, where converter warps take the other four places)
+//     read their 32 accumulator lanes with `tcgen05.ld` - two groups of four warps, each group one half of the
+//     columns, 64 (fp32: 32) columns per round trip to tensor memory - convert, and write (or atomically add)
+//     the rows of C at their scattered destinations while the next tile's MMAs run into the other buffer.
+//     (With four warps and one round trip per 16 columns the epilogue bounded the kernel: 0.28 us per 16
+//     columns of a tile, 5.5 us per 256-column tile of the dense mode.)
 //
 // fp32 inputs have two tensor-core modes. Plain TF32 (precision 1) feeds the fp32 words to `kind::tf32` as they
 // are, like the reference's tl.dot: products carry 10 mantissa bits (about 6e-4 relative on these shapes). The
@@ -208,6 +211,15 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int by
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
+// 16 consecutive 32-bit columns of this warp's 32 accumulator lanes; completion is awaited by the caller
+__device__ __forceinline__ void tmem_ld16(uint32_t *v, uint32_t taddr) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
+
 __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -215,13 +227,17 @@ __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
 // PW producer warps; each copies 128 / PW rows of a tile, kSlots of them per thread. X3: error-compensated
 // fp32 (three TF32 products per term), with kConvWarps converter warps behind the producers.
 template <typename T, bool CA, int PW, bool X3>
-__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 0)), 1) typed_mm_tc(TmmArgs a) {
+__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : kEpiWarps)), 1) typed_mm_tc(TmmArgs a) {
   constexpr int kProdWarps = PW;
   constexpr int kRowsPerProdWarp = kTileM / kProdWarps;
   constexpr int kSlots = kRowsPerProdWarp / kRpi;
   constexpr bool TF32 = sizeof(T) == 4;
   constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
   constexpr int kFirstConvWarp = kMmaWarp + 1 + PW;
+  // Without converter warps a second group of four epilogue warps sits in their place: the two groups share a
+  // tile's accumulator by columns (a warp reads the tensor-memory lanes 32 * (warp % 4) .. + 31, whatever its group).
+  constexpr bool E2 = !X3;
+  constexpr int kEpiAll = E2 ? 2 * kEpiWarps : kEpiWarps;
   static_assert(!X3 || TF32, "the error-compensated mode is for fp32 inputs");
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) Barriers bars;
@@ -257,7 +273,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
     }
     for (int b = 0; b < 2; ++b) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars.acc_full[b])) : "memory");
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc_empty[b])), "r"(32 * kEpiWarps) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc_empty[b])), "r"(32 * kEpiAll) : "memory");
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -433,13 +449,19 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
     }
     __syncwarp();
   } else {
-    // ================= epilogue: warp w owns accumulator lanes 32w .. 32w+31 = tile rows =================
+    // ================= epilogue: a warp owns accumulator lanes 32 * (warp % 4) .. + 31 = tile rows =================
     T *C = static_cast<T *>(a.c);
+    const int quarter = warp & 3;
+    const int grp = (E2 && warp >= kFirstConvWarp) ? 1 : 0;
+    // columns of this group: the first or the second half of the accumulator, in units of 16
+    const int n_half = E2 ? ((a.n / 16 + 1) / 2) * 16 : a.n;
+    const int c_lo = grp ? n_half : 0, c_hi = grp ? a.n : n_half;
+    const int rel_lo = dense ? c_lo / a.ncols : 0, cc_lo = dense ? c_lo % a.ncols : c_lo;
     int64_t it = 0;
     bool alive = true;
     // relation, source and destination index of this thread's row, fetched one tile ahead
     auto fetch = [&](int64_t tile, int64_t &r, int64_t &sv, int64_t &dv) {
-      const int64_t m0 = tile * kTileM, pos = m0 + warp * 32 + lane;
+      const int64_t m0 = tile * kTileM, pos = m0 + quarter * 32 + lane;
       r = rel_of(tile);
       sv = -1, dv = -1;
       if (tile < tile_hi && pos < a.m) {
@@ -455,71 +477,102 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
       fetch(tile + 1, r_next, sv_next, dv_next);
       if (r < 0 || r >= a.num_rel) continue;
       int64_t oc = -1;
-      if (sv >= 0 && sv < a.m_valid) oc = dv != -2 ? dv : (a.out_follows_src ? sv : tile * kTileM + warp * 32 + lane);
+      if (sv >= 0 && sv < a.m_valid) oc = dv != -2 ? dv : (a.out_follows_src ? sv : tile * kTileM + quarter * 32 + lane);
       const int buf = static_cast<int>(it & 1);
       alive = wait_bar(&bars.acc_full[buf], static_cast<uint32_t>((it >> 1) & 1), abort_flag, a.status, a.wait_cycles);
       if (!alive) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t taddr = tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + buf * a.tmem_cols;
-      for (int c0 = 0; c0 < a.n; c0 += 16) {
-        uint32_t v[16];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-            : "r"(taddr + c0));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 16 >= a.n) {  // the accumulator buffer is in registers: give it back to the MMA thread
+      const uint32_t taddr = tmem_d + (static_cast<uint32_t>(quarter * 32) << 16) + buf * a.tmem_cols;
+      if (a.atomic) {
+        if (c_lo >= c_hi) {  // nothing for this group (n = 16): only hand the buffer back
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(&bars.acc_empty[buf]);
         }
-        // dense mode: columns [j * ncols, (j + 1) * ncols) of the accumulator are relation dense_rel + j
-        const int64_t rel_shift = dense ? static_cast<int64_t>(c0 / a.ncols) * a.m_valid : 0;
-        const int cc = dense ? c0 % a.ncols : c0;
-        if (oc >= 0 && a.atomic) {
-          float *o = static_cast<float *>(a.c) + oc * a.n + c0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4 * q), "f"(__uint_as_float(v[4 * q])),
-                         "f"(__uint_as_float(v[4 * q + 1])), "f"(__uint_as_float(v[4 * q + 2])),
-                         "f"(__uint_as_float(v[4 * q + 3]))
-                         : "memory");
-        } else if (!a.atomic) {
-          // pack the 16 columns into 16-byte quads of the output type, then trade quads with the
-          // neighbouring lane so that two adjacent lanes write the two halves of one 32-byte sector
-          constexpr int NQ = TF32 ? 4 : 2;
-          uint4 q[NQ];
-          if (TF32) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) q[j % NQ] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
-            uint32_t p[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-              p[j] = *reinterpret_cast<uint32_t *>(&t);
-            }
-            q[0] = make_uint4(p[0], p[1], p[2], p[3]);
-            q[1] = make_uint4(p[4], p[5], p[6], p[7]);
+        for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(v, taddr + c0);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (c0 + 16 >= c_hi) {  // the accumulator buffer is in registers: give it back to the MMA thread
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&bars.acc_empty[buf]);
           }
-          const bool odd = lane & 1;
-          const int64_t oc_a = __shfl_sync(0xffffffffu, oc, lane & ~1), oc_b = __shfl_sync(0xffffffffu, oc, lane | 1);
-          T *row_a = C + (oc_a + rel_shift) * a.ncols + cc, *row_b = C + (oc_b + rel_shift) * a.ncols + cc;
-          constexpr int QE = 16 / sizeof(T);  // elements per quad
+          if (oc >= 0) {
+            float *o = static_cast<float *>(a.c) + oc * a.n + c0;
 #pragma unroll
-          for (int h = 0; h < NQ / 2; ++h) {
-            const uint4 keep = odd ? q[2 * h + 1] : q[2 * h], send = odd ? q[2 * h] : q[2 * h + 1];
-            uint4 got;
-            got.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
-            got.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
-            got.z = __shfl_xor_sync(0xffffffffu, send.z, 1);
-            got.w = __shfl_xor_sync(0xffffffffu, send.w, 1);
-            const int col = (2 * h + (odd ? 1 : 0)) * QE;
-            // row of the even lane: its own quad 2h, and its quad 2h+1 written by the odd lane. (One store
-            // instruction for both lanes, so that the two halves leave as one sector.)
-            const uint4 va = odd ? got : keep, vb = odd ? keep : got;
-            if (oc_a >= 0) st_global_v4(row_a + col, va);
-            if (oc_b >= 0) st_global_v4(row_b + col, vb);
+            for (int q = 0; q < 4; ++q)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4 * q), "f"(__uint_as_float(v[4 * q])),
+                           "f"(__uint_as_float(v[4 * q + 1])), "f"(__uint_as_float(v[4 * q + 2])),
+                           "f"(__uint_as_float(v[4 * q + 3]))
+                           : "memory");
+          }
+        }
+      } else {
+        // Store epilogue. The accumulator is read in groups of 64 (32) columns (four (two) loads in flight, one wait),
+        // so that a tile of n columns costs n / 64 round trips to tensor memory instead of n / 16. Two adjacent
+        // lanes trade 16-byte quads so that one store instruction of the pair writes one whole 32-byte sector.
+        const bool odd = lane & 1;
+        const int64_t oc_a = __shfl_sync(0xffffffffu, oc, lane & ~1), oc_b = __shfl_sync(0xffffffffu, oc, lane | 1);
+        // dense mode: columns [j * ncols, (j + 1) * ncols) of the accumulator are relation dense_rel + j, whose rows
+        // start j * m_valid rows further down the table; cc = column inside the relation's row
+        const int64_t rel_step = dense ? a.m_valid * a.ncols : 0;
+        T *row_a = C + oc_a * a.ncols + rel_lo * rel_step, *row_b = C + oc_b * a.ncols + rel_lo * rel_step;
+        int cc = cc_lo;
+        constexpr int GU = TF32 ? 2 : 4;  // loads of 16 columns per round trip (fp32 kernels have fewer registers per thread)
+        if (c_lo >= c_hi) {  // nothing for this group (n = 16): only hand the buffer back
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&bars.acc_empty[buf]);
+        }
+        for (int g0 = c_lo; g0 < c_hi; g0 += 16 * GU) {
+          uint32_t v[16 * GU];
+#pragma unroll
+          for (int u = 0; u < GU; ++u)
+            if (g0 + 16 * u < c_hi) tmem_ld16(v + 16 * u, taddr + g0 + 16 * u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (g0 + 16 * GU >= c_hi) {  // the accumulator buffer is in registers: give it back to the MMA thread
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&bars.acc_empty[buf]);
+          }
+#pragma unroll
+          for (int u = 0; u < GU; ++u) {
+            if (g0 + 16 * u >= c_hi) break;
+            constexpr int NQ = TF32 ? 4 : 2;
+            uint4 q[NQ];
+            if (TF32) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                q[j % NQ] = make_uint4(v[16 * u + 4 * j], v[16 * u + 4 * j + 1], v[16 * u + 4 * j + 2], v[16 * u + 4 * j + 3]);
+            } else {
+              uint32_t p[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[16 * u + 2 * j]), __uint_as_float(v[16 * u + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t *>(&t);
+              }
+              q[0] = make_uint4(p[0], p[1], p[2], p[3]);
+              q[1] = make_uint4(p[4], p[5], p[6], p[7]);
+            }
+            constexpr int QE = 16 / sizeof(T);  // elements per quad
+#pragma unroll
+            for (int h = 0; h < NQ / 2; ++h) {
+              const uint4 keep = odd ? q[2 * h + 1] : q[2 * h], send = odd ? q[2 * h] : q[2 * h + 1];
+              uint4 got;
+              got.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
+              got.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
+              got.z = __shfl_xor_sync(0xffffffffu, send.z, 1);
+              got.w = __shfl_xor_sync(0xffffffffu, send.w, 1);
+              const int col = cc + (2 * h + (odd ? 1 : 0)) * QE;
+              // row of the even lane: its own quad 2h, and its quad 2h+1 written by the odd lane. (One store
+              // instruction for both lanes, so that the two halves leave as one sector.)
+              const uint4 va = odd ? got : keep, vb = odd ? keep : got;
+              if (oc_a >= 0) st_global_v4(row_a + col, va);
+              if (oc_b >= 0) st_global_v4(row_b + col, vb);
+            }
+            cc += 16;
+            if (dense && cc == a.ncols) {  // next relation of this CTA
+              cc = 0;
+              row_a += rel_step;
+              row_b += rel_step;
+            }
           }
         }
       }
@@ -669,13 +722,13 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
     if (x3) {
       if (ca) launch(typed_mm_tc<float, true, 8, true>, kW + kConvWarps); else launch(typed_mm_tc<float, false, 8, true>, kW + kConvWarps);
     } else {
-      if (ca) launch(typed_mm_tc<float, true, 8, false>, kW); else launch(typed_mm_tc<float, false, 8, false>, kW);
+      if (ca) launch(typed_mm_tc<float, true, 8, false>, kW + kEpiWarps); else launch(typed_mm_tc<float, false, 8, false>, kW + kEpiWarps);
     }
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),
                                                        static_cast<__nv_bfloat16 *>(wt), nullptr, num_rel, k, ncols);
     constexpr int kW = kEpiWarps + 1 + 4;
-    if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4, false>, kW); else launch(typed_mm_tc<__nv_bfloat16, false, 4, false>, kW);
+    if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4, false>, kW + kEpiWarps); else launch(typed_mm_tc<__nv_bfloat16, false, 4, false>, kW + kEpiWarps);
   }
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_typed_matmul: %s", cudaGetErrorString(e));
   count_launches(2);

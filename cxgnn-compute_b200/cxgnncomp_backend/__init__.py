@@ -107,6 +107,7 @@ SPLIT_EDGES = 0
 CXG_SPMM_BULK_ROWS = 4
 CXG_SPMM_TEST_STALL = 8  # test hook, see include/cxgnn_b200.h
 CXG_SPMM_GENERIC_WALK = 16
+CXG_SPMM_TMA_INDEX = 64  # source ids staged by bulk copies into a ring in shared memory (lean walk)
 CXG_SPMM_SHARE_SMS = 32
 CXG_TMM_TEST_STALL = 4
 EXTRA_SPMM_FLAGS = int(os.environ.get("CXG_SPMM_FLAGS", "0"))
@@ -735,22 +736,45 @@ def target_aggr_backward(grad_in, ptr, idx, targets, grad_out, num_node):
     _spmm_backward(grad_in, None, ptr, idx, num_node, grad_x=grad_out, targets=targets, x_shape=grad_out.shape)
 
 
+_cidx_cache = []  # (idx, etype, versions, stride, combined), most recent last
+
+
+def _combined_index(idx, etype, stride, num_rel):
+    """etype[e] * stride + idx[e]: the row of the [num_rel * stride, F] table that edge e reads. Built once per
+    (idx, etype) pair and kept (cache of 8), so that the relational aggregation is a plain aggregation over the
+    table and takes the lean walk and the transposed-graph backward; int32 when the table has fewer than 2^31 rows."""
+    ver = (idx._version, etype._version)
+    for it in _cidx_cache:
+        if it[0] is idx and it[1] is etype and it[2] == ver and it[3] == stride:
+            return it[4]
+    n = min(idx.shape[0], etype.shape[0])
+    c = etype[:n].to(torch.int64) * stride + idx[:n].to(torch.int64)
+    if stride * num_rel < 2 ** 31:
+        c = c.to(torch.int32)
+    _cidx_cache.append((idx, etype, ver, stride, c))
+    if len(_cidx_cache) > 8:
+        _cidx_cache.pop(0)
+    return c
+
+
 class _AggrRelFunction(torch.autograd.Function):
     """AggrRelFunction (src/cpp/src/rel_spmm.cu:37-135); `reduce` = CXG_MEAN divides every row by its edge count in
-    the same kernel (the degree normalisation of MyRGCNConv, cxgnncomp/graph_conv.py:370-375)."""
+    the same kernel (the degree normalisation of MyRGCNConv, cxgnncomp/graph_conv.py:370-375). Edges are walked in
+    CSR order with the row of the table computed per edge, which is the aggregation of the table over the combined
+    index etype * N + idx: same additions in the same order as the reference's kernel."""
 
     @staticmethod
     def forward(ctx, x, ptr, idx, etype, num_node, num_rel, reduce):
-        ctx.save_for_backward(x, ptr, idx, etype)
-        ctx.num_node, ctx.num_rel, ctx.reduce = num_node, num_rel, reduce
         stride = x.shape[0] // num_rel
-        return _spmm_forward(x, ptr, idx, num_node, edge_rel=etype, rel_stride=stride, reduce=reduce)
+        cidx = _combined_index(idx, etype, stride, num_rel)
+        ctx.save_for_backward(x, ptr, cidx)
+        ctx.num_node, ctx.reduce = num_node, reduce
+        return _spmm_forward(x, ptr, cidx, num_node, reduce=reduce)
 
     @staticmethod
     def backward(ctx, grad_out):
-        x, ptr, idx, etype = ctx.saved_tensors
-        stride = x.shape[0] // ctx.num_rel
-        dx, _ = _spmm_backward(grad_out, x, ptr, idx, ctx.num_node, edge_rel=etype, rel_stride=stride, reduce=ctx.reduce)
+        x, ptr, cidx = ctx.saved_tensors
+        dx, _ = _spmm_backward(grad_out, x, ptr, cidx, ctx.num_node, reduce=ctx.reduce)
         return dx.to(x.dtype), None, None, None, None, None, None
 
 

@@ -63,6 +63,13 @@ extern "C" {
    that a kernel launched from another stream meanwhile (the copy kernel of a collective that overlaps
    this aggregation) finds room on every SM instead of waiting for this kernel to end. Same results. */
 #define CXG_SPMM_SHARE_SMS 32u
+/* Index-stream variant of the lean walk (rows of 128 / 256 / 512 bytes): the source ids of a tile are staged
+   into shared memory by the bulk-copy unit (one 512-byte `cp.async.bulk` per 128 int32 / 64 int64 ids, two
+   chunks per warp, the next one requested while the current one is read, completion on an mbarrier with a
+   bounded wait) instead of being loaded by the lanes one stage ahead. Needs a 16-byte aligned `idx`; ignored
+   otherwise and on the general walk. Same results bit for bit. CXG_SPMM_TEST_STALL makes every warp's first
+   chunk announce 16 bytes that never arrive. */
+#define CXG_SPMM_TMA_INDEX 64u
 
 const char *cxg_last_error_string(void);
 int cxg_abi_version(void);

@@ -127,6 +127,37 @@ def test_tiles_and_long_rows(cuda, tile, dtype):
     assert torch.equal(gm, oracle.spmm(ptr, idx, x, mean=True, tile=tile))
 
 
+@pytest.mark.parametrize("tile", [32, 64, 256, 512])
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64])
+def test_index_ring_variant(cuda, tile, idx_dtype):
+    """CXG_SPMM_TMA_INDEX: source ids staged by bulk copies (two 512-byte chunks per warp) give the oracle's bits
+    for every row width of the lean walk, edge counts that are not multiples of 16 bytes, tiles of one and of
+    several chunks, id arrays that start 16 bytes into an allocation, and id arrays whose start is not 16-byte
+    aligned (those take the per-lane loads)."""
+    import cxgnncomp_backend as be
+    be.SPLIT_EDGES = tile
+    for seed in range(4):
+        ptr, idx = random_csr(500, 400, 9, seed=100 + seed, hub=3000 + seed)
+        for dtype, feat in ((torch.float32, 32), (torch.float32, 64), (torch.float32, 128),
+                            (torch.bfloat16, 64), (torch.bfloat16, 128), (torch.bfloat16, 256)):
+            x = randn((400, feat), 7 + seed, dtype=dtype)
+            p, xg = ptr.cuda(), x.cuda()
+            want = oracle.spmm(ptr, idx, x, tile=tile)
+            pad = torch.zeros(idx.shape[0] + 4, dtype=idx_dtype, device="cuda")
+            for off in (0, 4 if idx_dtype == torch.int32 else 2, 1):
+                i = pad[off:off + idx.shape[0]]
+                i.copy_(idx)
+                got = be._spmm_forward(xg, p, i, 500, flags=be.CXG_SPMM_TMA_INDEX)
+                assert torch.equal(got.cpu(), want), (seed, dtype, feat, off)
+            acc = got.clone()
+            be._spmm_forward(xg, p, i, 500, out=acc, accumulate=True, flags=be.CXG_SPMM_TMA_INDEX)
+            plain = got.clone()
+            be._spmm_forward(xg, p, i, 500, out=plain, accumulate=True)
+            assert torch.equal(acc, plain)
+        gm = be._spmm_forward(xg, p, i, 500, reduce=be.CXG_MEAN, flags=be.CXG_SPMM_TMA_INDEX)
+        assert torch.equal(gm.cpu(), oracle.spmm(ptr, idx, x, mean=True, tile=tile))
+
+
 @pytest.mark.parametrize("split", [8, 32, 100])
 def test_row_per_group_path_split_rows(cuda, split):
     """Widths outside the streaming path (here 4 KiB rows): long rows are cut into segments whose

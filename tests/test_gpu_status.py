@@ -83,6 +83,30 @@ def test_spmm_bounded_wait_runs_out(cuda):
         assert torch.equal(y.cpu(), oracle.spmm(ptr, idx, x, tile=64))
 
 
+def test_spmm_index_ring_wait_runs_out(cuda):
+    """The id ring of the lean walk (CXG_SPMM_TMA_INDEX): every warp's first chunk announces bytes that never
+    arrive; the warps give up after the limit, the call reports CXG_ETIMEOUT and the next call is right."""
+    import cxgnncomp_backend as be
+    ptr, idx = random_csr(300, 300, 8, seed=95, hub=700)
+    x = randn((300, 64), 96)
+    for idx_dtype in (torch.int32, torch.int64):
+        p, i, xg = ptr.cuda(), idx.cuda().to(idx_dtype), x.cuda()
+        y = torch.full((300, 64), 3.0, device="cuda")
+        desc = be._make_desc(p, i, xg, y, 300, heads=1, feat=64)
+        desc.split_edges = 256
+        desc.flags = be.CXG_SPMM_TMA_INDEX | be.CXG_SPMM_TEST_STALL
+        be.set_wait_limit_cycles(200_000)  # ~0.1 ms
+        try:
+            rc, status, guard_ok = _raw_spmm(be, desc, _need(be, desc))
+        finally:
+            be.set_wait_limit_cycles(0)
+        assert rc == 0 and status == CXG_ETIMEOUT and guard_ok
+        desc.flags = be.CXG_SPMM_TMA_INDEX
+        rc, status, guard_ok = _raw_spmm(be, desc, _need(be, desc))
+        assert rc == 0 and status == 0 and guard_ok
+        assert torch.equal(y.cpu(), oracle.spmm(ptr, idx, x, tile=256))
+
+
 def test_typed_matmul_bounded_wait_runs_out(cuda):
     import cxgnncomp_backend as be
     R, E, K, N = 3, 2000, 64, 32
