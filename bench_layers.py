@@ -440,6 +440,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--c4-scale", type=float, default=1.0, help="shrink configuration 4 (nodes and edges) by this factor")
     ap.add_argument("--c3-scale", type=float, default=1.0, help="shrink configuration 3 (nodes and edges) by this factor")
+    ap.add_argument("--c4-default-only", action="store_true",
+                    help="configuration 4: time the default schedule and the typed matmul only, no CPU timing "
+                         "(a short launch list for profiler captures)")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "needs a CUDA device"
     if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.configs == "c3r":
@@ -451,7 +454,9 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     table = {"c1": config1, "c2": config2, "c3": config3, "c4": config4}
     for c in args.configs.split(","):
-        if c in ("c3", "c4"):
+        if c == "c4" and args.c4_default_only:
+            res = config4(args.steps, flush, args.c4_scale, cpu=False, quick=True)
+        elif c in ("c3", "c4"):
             res = table[c](args.steps, flush, args.c4_scale if c == "c4" else args.c3_scale)
         else:
             res = table[c](args.steps, flush)

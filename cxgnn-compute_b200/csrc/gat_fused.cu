@@ -24,8 +24,10 @@
 //                 dp = <dy[r,h,:], x[s,h,:]>                                          (per-head SDDMM)
 //                 dt = p (dp - D[r,h]) * (t > 0 ? 1 : slope)
 //                 dx[s,h,:] += p dy[r,h,:];   d a_src[s,h] += dt      (registers, fixed order)
-//                 d a_dst[r,h] += dt                                  (vector atomic, as the
-//                                                 reference's grad_src atomics: order not fixed)
+//                 d a_dst[r,h] += dt: with the forward position of every transposed edge at hand (t_eid of
+//                 the transpose) dt is stored at that position of a [nnz, H] scratch array and every
+//                 destination then adds its edges' values in a fixed order (same bits on every run); without
+//                 it, one atomic add per edge and head (order not fixed, as the reference's grad_src atomics).
 //
 // Shapes covered: fp32 features, heads a power of two <= 16, a feature row (heads * c floats) of exactly
 // 128, 256 or 512 bytes (every lane owns 4, 8 or 16 bytes of it, inside one head). Everything else stays on
@@ -42,6 +44,7 @@ constexpr int kGStageBytes = 8192;
 constexpr int kGFar = 1 << 30;
 constexpr float kNegBig = -1e30f;  // "no edge yet": exp(kNegBig - t) is 0 for every finite t
 constexpr int kFixSeq = 32;        // chains of more partials are joined by a whole CTA
+constexpr int kLongRowEdges = 2048;  // ordered d a_dst: destinations with more edges are summed piecewise by CTAs
 
 struct GatArgs {
   const void *ptr;       // graph that is walked: CSR (forward) or transposed CSR (backward)
@@ -55,7 +58,9 @@ struct GatArgs {
   float *row_max;        // forward [n_dst, H]
   float *row_sum;        // forward [n_dst, H]
   float *d_r_small;      // backward: d a_src [n_src, H]
-  float *d_g_small;      // backward: d a_dst [n_dst, H], added into atomically
+  float *d_g_small;      // backward: d a_dst [n_dst, H], added into atomically (when d_edge is NULL)
+  const void *eid;       // backward, ordered mode: forward edge of every transposed edge (width of idx)
+  float *d_edge;         // backward, ordered mode: [nnz, H] score gradient of every edge at its forward position
   int64_t n_rows, nnz, max_tiles;
   int heads, hshift, c, ptr_bytes, idx_bytes, tile;
   float slope;
@@ -146,7 +151,10 @@ __device__ __forceinline__ int64_t edge_total(const GatArgs &a) {
 
 __global__ void gat_plan(GatArgs a) {
   const int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-  if (t == 0) a.hdr[0] = 0;  // number of long chains
+  if (t == 0) {
+    a.hdr[0] = 0;  // number of long chains
+    a.hdr[1] = 0;  // number of long destinations (ordered d a_dst)
+  }
   if (t >= a.max_tiles) return;
   a.tail_row[t] = -1;
   const int64_t e_total = edge_total(a);
@@ -279,9 +287,18 @@ __global__ void __launch_bounds__(kGThreads, kGCtasPerSM) gat_walk(GatArgs a) {
     begin_row(row);
     uint32_t nid_cur = load_nid(0);
     fill(0, nid_cur);
+    // ordered d a_dst: the forward position of every transposed edge, fetched like the ids
+    const IdxT *eid_t = reinterpret_cast<const IdxT *>(a.eid) + tb;
+    const bool ordered = BWD && a.d_edge != nullptr;
+    auto load_eid = [&](int k) -> uint32_t {
+      const int pos = k * B + lane;
+      return (ordered && lane < B && pos < tile_len) ? static_cast<uint32_t>(__ldg(eid_t + pos)) : 0u;
+    };
+    uint32_t eid_cur = load_eid(0);
 
     for (int k = 0; k < n_stage; ++k) {
       const uint32_t nid_next = load_nid(k + 1);
+      const uint32_t eid_next = load_eid(k + 1);
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncwarp();
       const int sbase = k * B;
@@ -314,8 +331,13 @@ __global__ void __launch_bounds__(kGThreads, kGCtasPerSM) gat_walk(GatArgs a) {
             s += dt;
 #pragma unroll
             for (int i = 0; i < EL; ++i) acc[i] = fmaf(w, f[i], acc[i]);
-            const uint32_t dst_node = __shfl_sync(0xffffffffu, nid_cur, pos - sbase);
-            if (head_lead) red_add_f32(a.d_g_small + static_cast<uint64_t>(dst_node) * H + h, dt);
+            if (ordered) {  // left at the edge's forward position; the destinations add theirs up afterwards
+              const uint32_t fe = __shfl_sync(0xffffffffu, eid_cur, pos - sbase);
+              if (head_lead) a.d_edge[static_cast<uint64_t>(fe) * H + h] = dt;
+            } else {
+              const uint32_t dst_node = __shfl_sync(0xffffffffu, nid_cur, pos - sbase);
+              if (head_lead) red_add_f32(a.d_g_small + static_cast<uint64_t>(dst_node) * H + h, dt);
+            }
           }
           p += RB;
           pv += small_bytes;
@@ -361,6 +383,7 @@ __global__ void __launch_bounds__(kGThreads, kGCtasPerSM) gat_walk(GatArgs a) {
       __syncwarp();
       if (k + 1 < n_stage) fill(k + 1, nid_next);
       nid_cur = nid_next;
+      eid_cur = eid_next;
     }
     int64_t tail = -1;
     if (row < a.n_rows && rstart < tile_len && rend > tile_len) {
@@ -534,8 +557,101 @@ __global__ void __launch_bounds__(256) gat_bwd_prepare(const float *dy, const fl
   }
 }
 
+// Ordered d a_dst. The backward walk has left the score gradient of every edge at the edge's forward position
+// (d_edge [nnz, H]); a destination's gradient is the sum over its edges, added in an order that depends on the
+// graph only: lane (slot, head) of a warp takes every (32 / H)-th edge of the row (four running sums, joined in
+// a fixed order), then the slots are joined by a butterfly. Destinations with more than kLongRowEdges edges are
+// listed for the two kernels below.
+__device__ __forceinline__ float strided_sum(const float *v, int64_t lo, int64_t hi, int64_t step) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int64_t e = lo;
+  for (; e + 3 * step < hi; e += 4 * step) {
+    s0 += __ldg(v + e);
+    s1 += __ldg(v + e + step);
+    s2 += __ldg(v + e + 2 * step);
+    s3 += __ldg(v + e + 3 * step);
+  }
+  for (; e < hi; e += step) s0 += __ldg(v + e);
+  return (s0 + s1) + (s2 + s3);
+}
+
+__global__ void __launch_bounds__(256) gat_dst_sum_rows(const void *ptr, int ptr_bytes, const float *d_edge, float *d_a_dst,
+                                                        int64_t n_dst, int64_t nnz, int heads, int hshift, int32_t *hdr,
+                                                        int64_t *long_rows, int max_long) {
+  const int lane = threadIdx.x & 31;
+  const int head = lane & (heads - 1), slot = lane >> hshift;
+  const int64_t gwarp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t r = gwarp; r < n_dst; r += nwarps) {
+    const int64_t e0 = min(load_ptr(ptr, r, ptr_bytes), nnz), e1 = min(load_ptr(ptr, r + 1, ptr_bytes), nnz);
+    if (e1 - e0 > kLongRowEdges) {
+      if (lane == 0) {
+        const int s = atomicAdd(hdr + 1, 1);  // the list's order does not enter any sum
+        if (s < max_long) long_rows[s] = r;
+      }
+      continue;
+    }
+    // value (e, head) sits at d_edge[e * heads + head]: this lane walks e = e0 + slot, e0 + slot + 32 / heads, ...
+    float acc = strided_sum(d_edge + head, (e0 + slot) * heads, e1 * heads, 32);
+    for (int o = heads; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane < heads) d_a_dst[r * heads + head] = acc;
+  }
+}
+
+// Long destinations, first level: the edge array is cut into pieces of kPieceEdges consecutive edges; every piece of
+// a listed row is summed by one CTA (thread (slot, head) takes every (256 / H)-th edge, then a fixed tree in shared
+// memory) into piece_sums. A piece holds at most one listed row's first edges and at most one listed row's later
+// edges, hence two slots per piece. The CTAs share a row's pieces round-robin.
+constexpr int kPieceEdges = 1024;
+__global__ void __launch_bounds__(256) gat_dst_sum_pieces(const void *ptr, int ptr_bytes, const float *d_edge,
+                                                          float *piece_sums, int64_t nnz, int heads, int hshift,
+                                                          const int32_t *hdr, const int64_t *long_rows, int max_long) {
+  __shared__ float red[256];
+  const int tid = threadIdx.x;
+  const int head = tid & (heads - 1), slot = tid >> hshift;
+  const int n_long = min(hdr[1], max_long);
+  const int G = gridDim.x;
+  for (int i = 0; i < n_long; ++i) {
+    const int64_t r = long_rows[i];
+    const int64_t e0 = min(load_ptr(ptr, r, ptr_bytes), nnz), e1 = min(load_ptr(ptr, r + 1, ptr_bytes), nnz);
+    const int64_t p0 = e0 / kPieceEdges, p1 = (e1 - 1) / kPieceEdges;
+    const int first = (static_cast<int>(blockIdx.x) + G - (i % G)) % G;
+    for (int64_t p = p0 + first; p <= p1; p += G) {
+      const int64_t lo = max(e0, p * kPieceEdges), hi = min(e1, (p + 1) * kPieceEdges);
+      red[tid] = strided_sum(d_edge + head, (lo + slot) * heads, hi * heads, 256);
+      __syncthreads();
+      for (int o = 128; o >= heads; o >>= 1) {
+        if (tid < o) red[tid] += red[tid + o];
+        __syncthreads();
+      }
+      if (tid < heads) piece_sums[(2 * p + (p == p0 ? 1 : 0)) * heads + tid] = red[tid];
+      __syncthreads();
+    }
+  }
+}
+
+// Second level: one warp per listed destination adds the sums of its pieces, lane (slot, head) every (32 / H)-th
+// piece in ascending order, then the butterfly.
+__global__ void __launch_bounds__(256) gat_dst_sum_long(const void *ptr, int ptr_bytes, const float *piece_sums,
+                                                        float *d_a_dst, int64_t nnz, int heads, int hshift,
+                                                        const int32_t *hdr, const int64_t *long_rows, int max_long) {
+  const int lane = threadIdx.x & 31;
+  const int head = lane & (heads - 1), slot = lane >> hshift, nslot = 32 >> hshift;
+  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int n_long = min(hdr[1], max_long);
+  for (int i = gwarp; i < n_long; i += nwarps) {
+    const int64_t r = long_rows[i];
+    const int64_t e0 = min(load_ptr(ptr, r, ptr_bytes), nnz), e1 = min(load_ptr(ptr, r + 1, ptr_bytes), nnz);
+    const int64_t p0 = e0 / kPieceEdges, p1 = (e1 - 1) / kPieceEdges;
+    float acc = 0.f;
+    for (int64_t p = p0 + slot; p <= p1; p += nslot) acc += piece_sums[(2 * p + (p == p0 ? 1 : 0)) * heads + head];
+    for (int o = heads; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane < heads) d_a_dst[r * heads + head] = acc;
+  }
+}
+
 struct GatLayout {
-  size_t hdr, tile_row, tail_row, long_tiles, part_acc, part_ms, stats, total;
+  size_t hdr, tile_row, tail_row, long_tiles, part_acc, part_ms, stats, long_rows, piece_sums, d_edge, total;
   int64_t max_tiles;
   int max_long;
 };
@@ -566,6 +682,13 @@ void gat_layout(int64_t n_stats_rows, int64_t nnz, int heads, int c, GatLayout *
   off = align_up(off + static_cast<size_t>(L->max_tiles) * 2 * heads * 2 * sizeof(float), 256);
   L->stats = off;
   off = align_up(off + static_cast<size_t>(n_stats_rows) * heads * 4 * sizeof(float), 256);
+  // ordered d a_dst of the backward: destinations of more than kLongRowEdges edges, and one value per edge and head
+  L->long_rows = off;
+  off = align_up(off + static_cast<size_t>(nnz / kLongRowEdges + 1) * sizeof(int64_t), 256);
+  L->piece_sums = off;
+  off = align_up(off + static_cast<size_t>(nnz / kPieceEdges + 1) * 2 * heads * sizeof(float), 256);
+  L->d_edge = off;
+  off = align_up(off + static_cast<size_t>(nnz) * heads * sizeof(float), 256);
   L->total = off;
 }
 
@@ -676,7 +799,8 @@ extern "C" int cxg_gat_fused_backward(const void *t_ptr, const void *t_idx, int 
                                       const float *y, const float *x, const float *a_src, const float *a_dst,
                                       const float *row_max, const float *row_sum, float *dx, float *d_a_src,
                                       float *d_a_dst, int64_t n_src, int64_t n_dst, int64_t nnz, int heads, int c,
-                                      float slope, void *workspace, size_t workspace_bytes, void *stream) {
+                                      float slope, const void *t_eid, const void *fwd_ptr, int fwd_ptr_bytes,
+                                      void *workspace, size_t workspace_bytes, void *stream) {
   CXG_REQUIRE(n_src >= 0 && n_dst >= 0 && nnz >= 0, CXG_EINVAL, "cxg_gat_fused_backward: negative size");
   CXG_REQUIRE((ptr_bytes == 4 || ptr_bytes == 8) && (idx_bytes == 4 || idx_bytes == 8), CXG_EINVAL,
               "cxg_gat_fused_backward: index widths %d/%d", ptr_bytes, idx_bytes);
@@ -686,6 +810,10 @@ extern "C" int cxg_gat_fused_backward(const void *t_ptr, const void *t_idx, int 
   CXG_REQUIRE(t_ptr && x && a_src && dx && d_a_src && d_a_dst, CXG_ENULL, "cxg_gat_fused_backward: NULL argument");
   CXG_REQUIRE(n_dst == 0 || (dy && y && a_dst && row_max && row_sum), CXG_ENULL, "cxg_gat_fused_backward: NULL argument");
   CXG_REQUIRE(nnz == 0 || t_idx, CXG_ENULL, "cxg_gat_fused_backward: t_idx is NULL");
+  CXG_REQUIRE((t_eid == nullptr) == (fwd_ptr == nullptr), CXG_EINVAL,
+              "cxg_gat_fused_backward: t_eid and fwd_ptr select the ordered d_a_dst together");
+  CXG_REQUIRE(fwd_ptr == nullptr || fwd_ptr_bytes == 4 || fwd_ptr_bytes == 8, CXG_EINVAL,
+              "cxg_gat_fused_backward: fwd_ptr_bytes %d", fwd_ptr_bytes);
   CXG_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(dy) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0,
               CXG_EINVAL, "cxg_gat_fused_backward: feature matrices must be 16-byte aligned");
@@ -700,6 +828,9 @@ extern "C" int cxg_gat_fused_backward(const void *t_ptr, const void *t_idx, int 
   a.ptr = t_ptr, a.idx = t_idx, a.ptr_bytes = ptr_bytes, a.idx_bytes = idx_bytes;
   a.gathered = dy, a.g_small = stats, a.r_small = a_src, a.r_feat = x;
   a.out = dx, a.d_r_small = d_a_src, a.d_g_small = d_a_dst;
+  const bool ordered = t_eid != nullptr && nnz > 0 && n_dst > 0;
+  a.eid = ordered ? t_eid : nullptr;
+  a.d_edge = ordered ? reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + L.d_edge) : nullptr;
   a.n_rows = n_src;
   cudaStream_t st = as_stream(stream);
   const int cb = heads * c * 4 / 32;
@@ -715,5 +846,19 @@ extern "C" int cxg_gat_fused_backward(const void *t_ptr, const void *t_idx, int 
   }
   cudaError_t e = cb == 4 ? launch_walk<4, true>(a, st) : (cb == 8 ? launch_walk<8, true>(a, st) : launch_walk<16, true>(a, st));
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_gat_fused_backward: %s", cudaGetErrorString(e));
+  if (ordered) {
+    int64_t *long_rows = reinterpret_cast<int64_t *>(reinterpret_cast<char *>(workspace) + L.long_rows);
+    const int max_long = static_cast<int>(nnz / kLongRowEdges + 1);
+    // one warp per destination, all of them resident at once while they fit (a row costs two dependent loads)
+    const unsigned pg = static_cast<unsigned>(n_dst / 8 + 1 < kNumSM * 64 ? n_dst / 8 + 1 : kNumSM * 64);
+    gat_dst_sum_rows<<<pg, 256, 0, st>>>(fwd_ptr, fwd_ptr_bytes, a.d_edge, d_a_dst, n_dst, nnz, heads, a.hshift, a.hdr,
+                                         long_rows, max_long);
+    float *piece_sums = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + L.piece_sums);
+    gat_dst_sum_pieces<<<kNumSM * 2, 256, 0, st>>>(fwd_ptr, fwd_ptr_bytes, a.d_edge, piece_sums, nnz, heads, a.hshift,
+                                                   a.hdr, long_rows, max_long);
+    gat_dst_sum_long<<<kNumSM, 256, 0, st>>>(fwd_ptr, fwd_ptr_bytes, piece_sums, d_a_dst, nnz, heads, a.hshift, a.hdr,
+                                             long_rows, max_long);
+    count_launches(3);
+  }
   return check_launch("cxg_gat_fused_backward");
 }

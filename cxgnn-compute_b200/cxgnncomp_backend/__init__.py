@@ -860,7 +860,10 @@ _gatf_ws = _sig("cxg_gat_fused_workspace_size", [_i64, _i64, _int, _int, ctypes.
 _gatf_fwd = _sig("cxg_gat_fused_forward", [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _f,
                                            _vp, _sz, _vp])
 _gatf_bwd = _sig("cxg_gat_fused_backward", [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
-                                            _i64, _i64, _int, _int, _f, _vp, _sz, _vp])
+                                            _i64, _i64, _int, _int, _f, _vp, _vp, _int, _vp, _sz, _vp])
+# True: the gradient of the destination scores is summed in a fixed order (bit-identical from run to run);
+# False: one atomic add per edge and head, like the reference's backward.
+GAT_ORDERED_ATT_GRAD = True
 
 
 def gat_fused_supported(x_src):
@@ -910,7 +913,8 @@ class _GatFusedFunction(torch.autograd.Function):
         n, (n_src, h, c) = ctx.n, x_src.shape
         dev = x_src.device
         dy = _cuda(dy.contiguous(), "grad_out", (torch.float32,))
-        t_ptr, t_idx, _, _ = _transposed_graph(ptr, idx, n, n_src)
+        t_ptr, t_idx, t_eid, _ = _transposed_graph(ptr, idx, n, n_src)
+        ordered = GAT_ORDERED_ATT_GRAD and t_eid is not None
         dx = torch.empty_like(x_src)
         d_as = torch.empty((n_src, h), dtype=torch.float32, device=dev)
         d_ad = torch.empty((a_dst.shape[0], h), dtype=torch.float32, device=dev)
@@ -922,7 +926,9 @@ class _GatFusedFunction(torch.autograd.Function):
         with torch.cuda.device(dev):
             _check(_gatf_bwd(_p(t_ptr), _p(t_idx), t_ptr.element_size(), t_idx.element_size(), _p(dy), _p(y), _p(x_src),
                              _p(a_src), _p(a_dst), _p(row_max), _p(row_sum), _p(dx), _p(d_as), _p(d_ad), n_src, n,
-                             t_idx.shape[0], h, c, ctx.slope, _p(ws), ws.numel(), _stream()), "cxg_gat_fused_backward")
+                             t_idx.shape[0], h, c, ctx.slope, _p(t_eid) if ordered else None,
+                             _p(ptr) if ordered else None, ptr.element_size(), _p(ws), ws.numel(), _stream()),
+                   "cxg_gat_fused_backward")
         return dx, d_as, d_ad, None, None, None, None
 
 

@@ -230,7 +230,11 @@ int cxg_edge_softmax_backward(const void *ptr, const void *idx, int ptr_bytes,
  *             without edges), which is all the backward needs to recompute p.
  *   backward: walks the TRANSPOSED graph (t_ptr over the n_src sources, t_idx = destinations, as
  *             cxg_csr_transpose builds it): dx [n_src, heads, c], d_a_src [n_src, heads] (both written, fixed
- *             order) and d_a_dst [n_dst, heads] (zeroed, then added into with atomics).
+ *             order) and d_a_dst [n_dst, heads]. With t_eid (the forward edge of every transposed edge, third
+ *             output of cxg_csr_transpose, width idx_bytes) and fwd_ptr (row pointers of the forward graph,
+ *             fwd_ptr_bytes wide) every edge's score gradient is parked at its forward position in the
+ *             workspace and d_a_dst[r] is the sum over row r's edges in a fixed order: every output is the
+ *             same on every run. With both NULL d_a_dst is zeroed and added into with atomics.
  * x [n_src, heads, c], y / dy [n_dst, heads, c] float32; heads a power of two <= 16; heads * c * 4 must be
  * 128, 256 or 512 bytes (CXG_EUNSUPPORTED otherwise: use the separate kernels). exp is the fast __expf, like
  * the reference's fast-math build; results agree with the three-pass formulation to fp32 rounding, not bit
@@ -245,8 +249,8 @@ int cxg_gat_fused_backward(const void *t_ptr, const void *t_idx, int ptr_bytes, 
                            const float *dy, const float *y, const float *x, const float *a_src,
                            const float *a_dst, const float *row_max, const float *row_sum, float *dx,
                            float *d_a_src, float *d_a_dst, int64_t n_src, int64_t n_dst, int64_t nnz,
-                           int heads, int c, float slope, void *workspace, size_t workspace_bytes,
-                           void *stream);
+                           int heads, int c, float slope, const void *t_eid, const void *fwd_ptr,
+                           int fwd_ptr_bytes, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * SDDMM on an edge list: out[e,h] = <src_feat[src[e],h,:], dst_feat[dst[e],:]>, src_feat
