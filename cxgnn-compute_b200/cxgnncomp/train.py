@@ -2,6 +2,8 @@
 seeds -> backward -> optimizer step (the reference's Trainer.cxg_train_epoch, cxgnncomp/trainer.py:140-175, with
 the sampler of this package in place of its external loader)."""
 import math
+import queue
+import threading
 
 import torch
 import torch.nn.functional as F
@@ -12,13 +14,15 @@ def num_batches(num_train, batch_size):
 
 
 def train_epoch(model, optimizer, sampler, x, y, train_nodes, batch_size, epoch=0, max_batches=None, on_batch=None,
-                prefetch=True):
+                prefetch=True, depth=2):
     """One pass over `train_nodes` (int64, on the device) in a seeded random order. Returns the list of per-batch
     losses as a tensor on the device. `on_batch(i, batch, loss)` is called after every step when given.
 
-    prefetch=True (CUDA only) samples batch b + 1 on a side stream while the model trains on batch b: the sampler's
-    host synchronisations (it reads two counts per hop) then wait for the short sampling work only, not for the
-    training step queued before them, and sampling overlaps training on the device. Same batches, same losses."""
+    prefetch (CUDA only): True = a producer thread samples the batches ahead (at most `depth` waiting) on a side
+    stream while this thread issues the training steps, so neither the sampler's host synchronisations (it reads
+    two counts per hop) nor its host work sit between two training steps; "stream" = sample batch b + 1 on a side
+    stream from this thread before issuing step b (device work overlaps, host work does not); False = everything
+    in order on the current stream. Same batches, same losses in all three."""
     model.train()
     gen = torch.Generator(device=train_nodes.device).manual_seed(1234 + epoch)
     order = train_nodes[torch.randperm(train_nodes.shape[0], device=train_nodes.device, generator=gen)]
@@ -26,7 +30,8 @@ def train_epoch(model, optimizer, sampler, x, y, train_nodes, batch_size, epoch=
     if max_batches is not None:
         total = min(total, max_batches)
     losses = torch.zeros(total, device=train_nodes.device)
-    prefetch = prefetch and train_nodes.is_cuda and total > 0
+    if not (train_nodes.is_cuda and total > 0):
+        prefetch = False
     main = torch.cuda.current_stream() if prefetch else None
     side = torch.cuda.Stream() if prefetch else None
 
@@ -42,24 +47,61 @@ def train_epoch(model, optimizer, sampler, x, y, train_nodes, batch_size, epoch=
 
     if prefetch:
         side.wait_stream(main)  # `order` and the model's inputs were produced on the main stream
-    nxt = produce(0) if total > 0 else None
-    for b in range(total):
-        batch, ready = nxt
-        if b + 1 < total:
-            nxt = produce(b + 1)
-        if ready is not None:
-            main.wait_event(ready)
-            for t in (batch.x, batch.ptr, batch.idx, batch.y, batch.target):
-                if isinstance(t, torch.Tensor):
-                    t.record_stream(main)  # allocated on the side stream, used on the main one
-        optimizer.zero_grad(set_to_none=True)
-        out = model(batch)
-        loss = F.nll_loss(out, batch.y)
-        loss.backward()
-        optimizer.step()
-        losses[b] = loss.detach()
-        if on_batch is not None:
-            on_batch(b, batch, loss)
+    producer, stop, q = None, None, None
+    if prefetch is True:
+        q, stop = queue.Queue(maxsize=max(1, int(depth))), threading.Event()
+        device = train_nodes.device
+
+        def offer(item):
+            """Puts `item` unless the consumer has gone; never blocks for good."""
+            while not stop.is_set():
+                try:
+                    q.put(item, timeout=0.1)
+                    return True
+                except queue.Full:
+                    pass
+            return False
+
+        def run():
+            try:
+                with torch.cuda.device(device):
+                    for b in range(total):
+                        if not offer(produce(b)):
+                            return
+            except BaseException as e:  # handed to the consumer, which re-raises it
+                offer(e)
+
+        producer = threading.Thread(target=run, name="cxg-batch-producer", daemon=True)
+        producer.start()
+    try:
+        nxt = produce(0) if (total > 0 and producer is None) else None
+        for b in range(total):
+            if producer is not None:
+                item = q.get()
+                if isinstance(item, BaseException):
+                    raise item
+                batch, ready = item
+            else:
+                batch, ready = nxt
+                if b + 1 < total:
+                    nxt = produce(b + 1)
+            if ready is not None:
+                main.wait_event(ready)
+                for t in (batch.x, batch.ptr, batch.idx, batch.y, batch.target):
+                    if isinstance(t, torch.Tensor):
+                        t.record_stream(main)  # allocated on the side stream, used on the main one
+            optimizer.zero_grad(set_to_none=True)
+            out = model(batch)
+            loss = F.nll_loss(out, batch.y)
+            loss.backward()
+            optimizer.step()
+            losses[b] = loss.detach()
+            if on_batch is not None:
+                on_batch(b, batch, loss)
+    finally:
+        if producer is not None:
+            stop.set()
+            producer.join()
     if prefetch:
         side.wait_stream(main)
     return losses

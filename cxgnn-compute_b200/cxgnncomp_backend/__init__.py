@@ -92,8 +92,40 @@ def _p(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = torch._C._cuda_getCurrentRawStream  # (device index) -> the stream's handle as an int, no Python objects
+
+
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """Handle of the current stream of the current device."""
+    return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
+
+
+def _dev_index(device):
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+class _OnDevice:
+    """`with _on(device):` makes `device` current like torch.cuda.device, but costs one comparison when it already is
+    (the case of every call in a one-GPU process)."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = _dev_index(device)
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+_on = _OnDevice
 
 
 _FEAT_DTYPES = (torch.float32, torch.bfloat16)
@@ -119,7 +151,8 @@ _last_kind = {}
 def _workspace(device, nbytes, kind=None):
     """Scratch buffer per (device, stream); grows on demand, contents never carry over. `kind` names the entry
     point family that uses it now (its status word is the one check_device_status can answer for)."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    idx = _dev_index(device)
+    key = (idx, _raw_stream(idx))
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -178,12 +211,13 @@ def check_device_status(kind="spmm", device=None):
     of spinning forever) or, for "spmm", ptr[num_node] exceeded the length of idx. The calls of one stream share
     a scratch buffer, so only the last call can be asked about; for any other kind nothing is checked."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    idx = _dev_index(device)
+    key = (idx, _raw_stream(idx))
     ws = _workspaces.get(key)
     if ws is None or _last_kind.get(key) != kind:
         return
     fn, name = (_spmm_status, "cxg_spmm_csr_status") if kind == "spmm" else (_tmm_status, "cxg_typed_matmul_status")
-    with torch.cuda.device(device):
+    with _on(device):
         _check(fn(_p(ws), _stream()), name)
 
 
@@ -202,7 +236,7 @@ def _run_spmm(desc, device):
     _check(_spmm_ws(desc.n_dst, desc.nnz, desc.feat, desc.heads, desc.split_edges, ctypes.byref(need)),
            "cxg_spmm_csr_workspace_size")
     ws = _workspace(device, need.value, "spmm")
-    with torch.cuda.device(device):
+    with _on(device):
         _check(_spmm_fwd(ctypes.byref(desc), _p(ws), ws.numel(), _stream()), "cxg_spmm_csr")
 
 
@@ -262,7 +296,7 @@ def csr_transpose(ptr, idx, num_node, num_src, want_eid=True):
     need = _sz(0)
     _check(_transpose_ws(nnz, ctypes.byref(need)), "cxg_csr_transpose_workspace_size")
     ws = _workspace(dev, need.value)
-    with torch.cuda.device(dev):
+    with _on(dev):
         _check(_transpose(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), n, int(num_src), nnz, _p(t_ptr),
                           _p(t_idx), _p(t_eid), _p(inv_deg), _p(ws), ws.numel(), _stream()), "cxg_csr_transpose")
     return t_ptr, t_idx, t_eid, inv_deg
@@ -305,7 +339,7 @@ def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG
         if edge_val is not None:  # the edge values in transposed order
             ev = edge_val.contiguous()
             t_val = torch.empty_like(ev)
-            with torch.cuda.device(ev.device):
+            with _on(ev.device):
                 _check(_gather(_p(ev), _p(t_eid), t_eid.element_size(), _p(t_val), min(t_eid.shape[0], ev.shape[0]),
                                ev.shape[1] if ev.dim() == 2 else 1, 1, _stream()), "cxg_gather_edges")
         dx_t = _spmm_forward(dy.contiguous(), t_ptr, t_idx, x_shape[0], edge_val=t_val)
@@ -327,7 +361,7 @@ def _spmm_backward(grad_out, x, ptr, idx, num_node, *, edge_val=None, reduce=CXG
                       edge_mask=edge_mask, edge_rel=edge_rel, rel_stride=rel_stride, targets=targets,
                       reduce=reduce)
     desc.dtype = _dtype_code(grad_out)
-    with torch.cuda.device(grad_out.device):
+    with _on(grad_out.device):
         _check(_spmm_bwd(ctypes.byref(desc), _p(grad_out), _p(dx), _p(dval), _stream()),
                "cxg_spmm_csr_backward")
     return (dx_t if dx_t is not None else dx), dval
@@ -453,7 +487,7 @@ def gather_rows(x, rows, out=None):
     _cuda(out, "out", (x.dtype,))
     if out.shape[0] < rows.shape[0] or out.shape[1] != x.shape[1]:
         raise RuntimeError("out must be [len(rows), x.shape[1]]")
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _check(_gather_rows(_p(x), _p(rows), _p(out), rows.shape[0], x.shape[1] * x.element_size(), _stream()),
                "cxg_gather_rows")
     return out
@@ -471,7 +505,7 @@ def ipc_export(t):
     _cuda(t, "tensor")
     buf = (ctypes.c_ubyte * 64)()
     off = _i64(0)
-    with torch.cuda.device(t.device):
+    with _on(t.device):
         _check(_ipc_export(_p(t), buf, ctypes.byref(off)), "cxg_ipc_export")
     return bytes(buf), int(off.value)
 
@@ -479,13 +513,13 @@ def ipc_export(t):
 def ipc_open(handle, device):
     """Maps the allocation named by `handle` (from another process) into `device`'s context; returns its base address."""
     base = _vp(0)
-    with torch.cuda.device(device):
+    with _on(device):
         _check(_ipc_open((ctypes.c_ubyte * 64).from_buffer_copy(handle), ctypes.byref(base)), "cxg_ipc_open")
     return int(base.value)
 
 
 def ipc_close(base, device):
-    with torch.cuda.device(device):
+    with _on(device):
         _check(_ipc_close(_vp(base)), "cxg_ipc_close")
 
 
@@ -494,7 +528,7 @@ def copy_async(dst_ptr, src, nbytes=None):
     on the current stream of src's device."""
     _cuda(src, "src")
     nbytes = src.numel() * src.element_size() if nbytes is None else int(nbytes)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         _check(_copy_async(_vp(dst_ptr), _p(src), nbytes, _stream()), "cxg_copy_async")
 
 
@@ -507,7 +541,7 @@ def put_rows(x, rows, peer_ptrs, seg_start):
     n_peer = len(peer_ptrs)
     bases = (ctypes.c_void_p * n_peer)(*[None if not v else int(v) for v in peer_ptrs])
     segs = (ctypes.c_int64 * (n_peer + 1))(*[int(v) for v in seg_start])
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _check(_put_rows(_p(x), _p(rows), bases, segs, n_peer, x.shape[1] * x.element_size(), _stream()), "cxg_put_rows")
 
 
@@ -527,12 +561,12 @@ def sample_neighbors(graph_ptr, graph_idx, frontier, fanout, seed):
     _cuda(frontier, "frontier", (torch.int64,))
     n = frontier.shape[0]
     out_ptr = torch.zeros(n + 1, dtype=torch.int64, device=frontier.device)
-    with torch.cuda.device(frontier.device):
+    with _on(frontier.device):
         _check(_sample_counts(_p(graph_ptr), graph_ptr.element_size(), _p(frontier), n, int(fanout),
                               out_ptr[1:].data_ptr(), _stream()), "cxg_sample_counts")
     out_ptr[1:].cumsum_(0)
     out = torch.empty(int(out_ptr[-1]), dtype=torch.int64, device=frontier.device)
-    with torch.cuda.device(frontier.device):
+    with _on(frontier.device):
         _check(_sample(_p(graph_ptr), _p(graph_idx), graph_ptr.element_size(), graph_idx.element_size(), _p(frontier), n,
                        int(fanout), _p(out_ptr), _p(out), int(seed) & 0xFFFFFFFFFFFFFFFF, _stream()),
                "cxg_sample_neighbors")
@@ -548,7 +582,7 @@ def renumber_claim(picked, local_of, fresh, n_fresh):
     marks them claimed; n_fresh (int64 [1], device) receives the count. See cxg_renumber_claim."""
     for t_, name in ((picked, "picked"), (local_of, "local_of"), (fresh, "fresh"), (n_fresh, "n_fresh")):
         _cuda(t_, name, (torch.int64,))
-    with torch.cuda.device(picked.device):
+    with _on(picked.device):
         _check(_claim(_p(picked), picked.shape[0], _p(local_of), _p(fresh), _p(n_fresh), _stream()),
                "cxg_renumber_claim")
 
@@ -558,7 +592,7 @@ def renumber_assign(fresh_sorted, base, picked, local_of):
     for t_, name in ((picked, "picked"), (local_of, "local_of"), (fresh_sorted, "fresh_sorted")):
         _cuda(t_, name, (torch.int64,))
     out = torch.empty_like(picked)
-    with torch.cuda.device(picked.device):
+    with _on(picked.device):
         _check(_assign(_p(fresh_sorted), fresh_sorted.shape[0], int(base), _p(picked), picked.shape[0], _p(local_of),
                        _p(out), _stream()), "cxg_renumber_assign")
     return out
@@ -594,7 +628,7 @@ def _gspmm_call(rowptr, colind, val, b, re_op, comp_op):
         raise RuntimeError("B must be [n_src, feat]")
     m = rowptr.shape[0] - 1
     out = torch.empty((m, b.shape[1]), dtype=torch.float32, device=b.device)
-    with torch.cuda.device(b.device):
+    with _on(b.device):
         _check(_gspmm(_p(rowptr), _p(colind), 4, 4, _p(val), _p(b), _p(out), m, b.shape[1], int(re_op), int(comp_op),
                       _stream()), "cxg_gspmm_csr")
     return out
@@ -627,7 +661,7 @@ class _GatScoresFunction(torch.autograd.Function):
         n, h, c = feat.shape
         a_s = torch.empty((n, h), dtype=torch.float32, device=feat.device)
         a_d = torch.empty((num_dst, h), dtype=torch.float32, device=feat.device)
-        with torch.cuda.device(feat.device):
+        with _on(feat.device):
             _check(_gat_scores(_p(feat), _p(att_src), _p(att_dst), _p(a_s), _p(a_d), n, num_dst, h, c, _stream()),
                    "cxg_gat_scores")
         ctx.save_for_backward(feat, att_src, att_dst)
@@ -642,7 +676,7 @@ class _GatScoresFunction(torch.autograd.Function):
         grad_feat = grad_as = grad_ad = None
         if ctx.needs_input_grad[0]:
             grad_feat = torch.empty_like(feat)
-            with torch.cuda.device(feat.device):
+            with _on(feat.device):
                 _check(_gat_scores_bwd(_p(g_src), _p(g_dst), _p(att_src), _p(att_dst), _p(grad_feat), n, ctx.num_dst,
                                        h, c, _stream()), "cxg_gat_scores_backward")
         if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
@@ -650,7 +684,7 @@ class _GatScoresFunction(torch.autograd.Function):
             need = _sz(0)
             _check(_gat_att_grad_ws(h, c, ctypes.byref(need)), "cxg_gat_att_grad_workspace_size")
             ws = _workspace(feat.device, need.value)
-            with torch.cuda.device(feat.device):
+            with _on(feat.device):
                 _check(_gat_att_grad(_p(feat), _p(g_src), _p(g_dst), _p(grad_as), _p(grad_ad), n, ctx.num_dst, h, c,
                                      _p(ws), ws.numel(), _stream()), "cxg_gat_att_grad")
         return grad_feat, grad_as, grad_ad, None
@@ -687,7 +721,7 @@ def spmm_multihead(ptr, idx, val, vin, num_node, schedule=SPMM_MULTIHEAD_SCHEDUL
 def _head_sum(out):
     """[n, H, F] -> [n, F]: heads added in head order with one fp32 accumulator per column."""
     res = torch.empty((out.shape[0], out.shape[2]), dtype=out.dtype, device=out.device)
-    with torch.cuda.device(out.device):
+    with _on(out.device):
         _check(_head_sum_c(_p(out), _p(res), out.shape[0], out.shape[1], out.shape[2], _dtype_code(out), _stream()),
                "cxg_head_sum")
     return res
@@ -827,7 +861,7 @@ class _EdgeSoftmaxFunction(torch.autograd.Function):
         out = torch.empty((num_edge, heads), dtype=torch.float32, device=att_dst.device)
         mask = torch.empty((num_edge, heads), dtype=torch.bool, device=att_dst.device)
         ws = _softmax_ws(att_dst.device, n_dst, num_edge)
-        with torch.cuda.device(att_dst.device):
+        with _on(att_dst.device):
             _check(_es_fwd(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(att_dst), _p(att_src), _p(out),
                            _p(mask), n_dst, num_edge, heads, float(relu_l), _p(ws), ws.numel(), _stream()),
                    "cxg_edge_softmax_forward")
@@ -843,7 +877,7 @@ class _EdgeSoftmaxFunction(torch.autograd.Function):
         gd = torch.zeros((n_dst, heads), dtype=torch.float32, device=out.device)
         gs = torch.zeros((n_src, heads), dtype=torch.float32, device=out.device)
         ws = _softmax_ws(out.device, n_dst, num_edge)
-        with torch.cuda.device(out.device):
+        with _on(out.device):
             _check(_es_bwd(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(grad_out), _p(mask), _p(out),
                            _p(gd), _p(gs), n_dst, num_edge, heads, relu_l, _p(ws), ws.numel(), _stream()),
                    "cxg_edge_softmax_backward")
@@ -898,7 +932,7 @@ class _GatFusedFunction(torch.autograd.Function):
         need = _sz(0)
         _check(_gatf_ws(n, idx.shape[0], h, c, ctypes.byref(need)), "cxg_gat_fused_workspace_size")
         ws = _workspace(dev, need.value)
-        with torch.cuda.device(dev):
+        with _on(dev):
             _check(_gatf_fwd(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(x_src), _p(a_src), _p(a_dst),
                              _p(y), _p(row_max), _p(row_sum), n, idx.shape[0], h, c, float(slope), _p(ws), ws.numel(),
                              _stream()), "cxg_gat_fused_forward")
@@ -923,7 +957,7 @@ class _GatFusedFunction(torch.autograd.Function):
         need = _sz(0)
         _check(_gatf_ws(n, idx.shape[0], h, c, ctypes.byref(need)), "cxg_gat_fused_workspace_size")
         ws = _workspace(dev, need.value)
-        with torch.cuda.device(dev):
+        with _on(dev):
             _check(_gatf_bwd(_p(t_ptr), _p(t_idx), t_ptr.element_size(), t_idx.element_size(), _p(dy), _p(y), _p(x_src),
                              _p(a_src), _p(a_dst), _p(row_max), _p(row_sum), _p(dx), _p(d_as), _p(d_ad), n_src, n,
                              t_idx.shape[0], h, c, ctx.slope, _p(t_eid) if ordered else None,
@@ -942,7 +976,7 @@ def edge_value_degree(ptr, num_dst, num_edge):
     """val[e] = 1 / in-degree of e's destination (binding.cpp:24-25)."""
     _cuda(ptr, "ptr", _INDEX_DTYPES)
     out = torch.empty((int(num_edge),), dtype=torch.float32, device=ptr.device)
-    with torch.cuda.device(ptr.device):
+    with _on(ptr.device):
         _check(_evd(_p(ptr), ptr.element_size(), _p(out), int(num_dst), _stream()), "cxg_edge_value_degree")
     return out
 
@@ -951,7 +985,7 @@ def spmv(ptr, idx, x, num_dst):
     """y[d] = sum of x[idx[e]] over row d (binding.cpp:32)."""
     _cuda(x, "x", (torch.float32,))
     y = torch.empty((int(num_dst),), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _check(_spmv(_p(ptr), _p(idx), ptr.element_size(), idx.element_size(), _p(x), _p(y), int(num_dst), _stream()),
                "cxg_spmv_csr")
     return y
@@ -966,7 +1000,7 @@ def run_sddmm(src, dst, src_feat, dst_feat, output, num_edge):
     _cuda(src, "src", _INDEX_DTYPES)
     _cuda(dst, "dst", (src.dtype,))
     heads, feat = src_feat.shape[1], src_feat.shape[-1]
-    with torch.cuda.device(src_feat.device):
+    with _on(src_feat.device):
         _check(_sddmm(_p(src), _p(dst), src.element_size(), _p(src_feat), _p(dst_feat), _p(output), int(num_edge), feat,
                       heads, 1 if dst_feat.dim() == 3 else 0, _stream()), "cxg_sddmm_coo")
     return None
@@ -1010,7 +1044,7 @@ class _GatherFunction(torch.autograd.Function):
             raise RuntimeError("gather: num_node must be positive")
         ctx.save_for_backward(dest)
         out = torch.zeros((num_node, x_edge.shape[1]), dtype=torch.float32, device=x_edge.device)
-        with torch.cuda.device(x_edge.device):
+        with _on(x_edge.device):
             _check(_gather(_p(x_edge), _p(dest), dest.element_size(), _p(out), dest.shape[0], x_edge.shape[1], 0,
                            _stream()), "cxg_gather_edges")
         return out
@@ -1020,7 +1054,7 @@ class _GatherFunction(torch.autograd.Function):
         (dest,) = ctx.saved_tensors
         grad_out = grad_out.contiguous()
         g = torch.empty((dest.shape[0], grad_out.shape[1]), dtype=torch.float32, device=grad_out.device)
-        with torch.cuda.device(grad_out.device):
+        with _on(grad_out.device):
             _check(_gather(_p(grad_out), _p(dest), dest.element_size(), _p(g), dest.shape[0], grad_out.shape[1], 1,
                            _stream()), "cxg_gather_edges")
         return g, None, None

@@ -113,12 +113,15 @@ def test_batch_format_and_training_step(cuda):
         last = cxgnncomp.train_epoch(model, opt, sampler, x.cuda(), y.cuda(), train, 256, epoch=e)
     assert first.shape[0] == cxgnncomp.num_batches(n, 256)
     assert float(last.mean()) < float(first.mean())
-    # sampling the next batch on a side stream while the model trains (the default) changes neither the batches nor
-    # the losses: two fresh, identically seeded models, one epoch each, with and without it
+    # sampling ahead (a producer thread on a side stream, the default; or the next batch from the training thread)
+    # changes neither the batches nor the losses: fresh, identically seeded models, one epoch each
     runs = []
-    for prefetch in (True, False):
+    for prefetch in (True, "stream", False):
         torch.manual_seed(11)
         m2 = cxgnncomp.SAGE(20, 32, classes, 3, dropout=0.0).cuda()
         o2 = torch.optim.Adam(m2.parameters(), lr=0.01)
         runs.append(cxgnncomp.train_epoch(m2, o2, sampler, x.cuda(), y.cuda(), train, 256, epoch=3, prefetch=prefetch))
-    assert torch.equal(runs[0], runs[1])
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+    # a host-side error inside the producer thread (no feature matrix to index) reaches the caller
+    with pytest.raises(TypeError):
+        cxgnncomp.train_epoch(m2, o2, sampler, None, y.cuda(), train, 256, epoch=4)
