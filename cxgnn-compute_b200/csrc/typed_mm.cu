@@ -662,7 +662,8 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   // multiple of one instruction's K (32 bytes)
   auto stage_bytes = [&](int kb) { return static_cast<size_t>(kTileM) * kb * elem * (x3 ? 2 : 1); };
   int kb = k;
-  const int want = x3 ? 4 : (dense ? 3 : 1);
+  // (compensated dense mode: three stages of K-block 32 measured 7 % faster than six of K-block 16)
+  const int want = dense ? 3 : (x3 ? 4 : 1);
   while (b_bytes + want * stage_bytes(kb) > static_cast<size_t>(kSmemBudget) && kb % (4 * epc) == 0) kb /= 2;
   const size_t a_bytes = stage_bytes(kb);
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,

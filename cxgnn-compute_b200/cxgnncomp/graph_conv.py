@@ -462,7 +462,7 @@ class MyGATConv(torch.nn.Module):
             out = out.view(-1, H * C)
         elif out.dim() == 3:
             out = out.mean(dim=1)
-        return out + self.bias if self.bias is not None else out
+        return cxgnncomp_backend.bias_add(out, self.bias) if self.bias is not None else out
 
     def forward_1(self, x, ptr, idx, num_dst, num_src, num_edge):
         w = self.lin_src.T.view(-1, self.heads, self.out_channels)
@@ -474,7 +474,7 @@ class MyGATConv(torch.nn.Module):
             out = sage_sum_forward_edge_value(torch.mm(x, self.lin_src.T), ptr, idx, edge_value, num_dst)
         else:
             out = torch.mm(sage_sum_forward_edge_value(x, ptr, idx, edge_value, num_dst), self.lin_src.T)
-        return out + self.bias if self.bias is not None else out
+        return cxgnncomp_backend.bias_add(out, self.bias) if self.bias is not None else out
 
     def forward(self, x, ptr, idx, num_dst, num_src, num_edge):
         ptr = ptr[:num_dst + 1]
@@ -515,4 +515,4 @@ class MyGCNConv(torch.nn.Module):
             out = AggrOP.apply(out, ptr, idx, num_node)
         if not mm_before:
             out = self.lin(out)
-        return out + self.bias if self.bias is not None else out
+        return cxgnncomp_backend.bias_add(out, self.bias) if self.bias is not None else out

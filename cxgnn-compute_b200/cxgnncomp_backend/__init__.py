@@ -700,6 +700,48 @@ def gat_scores(feat, att_src, att_dst, num_dst):
     return _GatScoresFunction.apply(feat, att_src, att_dst, int(num_dst))
 
 
+_colsum_ws = _sig("cxg_column_sum_workspace_size", [ctypes.c_int, ctypes.POINTER(_sz)])
+_colsum = _sig("cxg_column_sum", [_vp, ctypes.c_int, _i64, ctypes.c_int, _vp, _vp, _sz, _vp])
+
+
+def column_sum(x):
+    """float32 [W]: the sum of the rows of x [N, W] (or [N, ...] flattened to W columns), added in a fixed order."""
+    _cuda(x, "x", _FEAT_DTYPES)
+    n = x.shape[0]
+    width = x.numel() // n if n > 0 else int(torch.tensor(x.shape[1:]).prod())
+    out = torch.empty(width, dtype=torch.float32, device=x.device)
+    need = _sz(0)
+    _check(_colsum_ws(width, ctypes.byref(need)), "cxg_column_sum_workspace_size")
+    ws = _workspace(x.device, need.value)
+    with _on(x.device):
+        _check(_colsum(_p(x), _dtype_code(x), n, width, _p(out), _p(ws), ws.numel(), _stream()), "cxg_column_sum")
+    return out
+
+
+class _BiasAddFunction(torch.autograd.Function):
+    """y + bias over the last dimension(s); the bias gradient is cxg_column_sum of the upstream gradient."""
+
+    @staticmethod
+    def forward(ctx, y, bias):
+        ctx.bias_shape, ctx.bias_dtype = bias.shape, bias.dtype
+        return y + bias
+
+    @staticmethod
+    def backward(ctx, grad):
+        g_bias = None
+        if ctx.needs_input_grad[1]:
+            g_bias = column_sum(grad.contiguous()).view(ctx.bias_shape).to(ctx.bias_dtype)
+        return grad, g_bias
+
+
+def bias_add(y, bias):
+    """y [N, ...] + bias [...] (bias covers all trailing dimensions of y); differentiable in both."""
+    if (not y.is_cuda or y.dtype not in _FEAT_DTYPES or y.dim() < 2 or y.shape[0] == 0
+            or bias.numel() * y.shape[0] != y.numel()):
+        return y + bias
+    return _BiasAddFunction.apply(y, bias)
+
+
 _head_sum_c = _sig("cxg_head_sum", [_vp, _vp, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp])
 
 

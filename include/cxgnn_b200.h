@@ -315,6 +315,16 @@ int cxg_gat_att_grad(const float *feat, const float *g_src, const float *g_dst, 
                      size_t workspace_bytes, void *stream);
 
 /*
+ * out[c] = sum over the n_row rows of x[r, c] (x row-major [n_row, width], dtype CXG_F32 or CXG_BF16, out float32):
+ * the gradient of the bias that MyGATConv / MyGCNConv add to every output row (cxgnncomp/graph_conv.py:493-494,
+ * 543-545, 622-623; the reference leaves it to autograd's sum). Fixed two-level order of additions (contiguous row chunks,
+ * then the chunks in order), no atomics.
+ */
+int cxg_column_sum_workspace_size(int width, size_t *bytes);
+int cxg_column_sum(const void *x, int dtype, int64_t n_row, int width, float *out, void *workspace,
+                   size_t workspace_bytes, void *stream);
+
+/*
  * out[r, f] = sum over heads of in[r, h, f] (heads added in order into one fp32 accumulator): the head
  * reduction of spmm_multihead's PreReduce / Optimal schedules, which return [n, feat]
  * (src/cpp/src/spmm_host.cu:158-196).
