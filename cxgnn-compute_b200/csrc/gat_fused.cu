@@ -44,7 +44,8 @@ constexpr int kGStageBytes = 8192;
 constexpr int kGFar = 1 << 30;
 constexpr float kNegBig = -1e30f;  // "no edge yet": exp(kNegBig - t) is 0 for every finite t
 constexpr int kFixSeq = 32;        // chains of more partials are joined by a whole CTA
-constexpr int kLongRowEdges = 2048;  // ordered d a_dst: destinations with more edges are summed piecewise by CTAs
+constexpr int kLongRowEdges = 256;  // ordered d a_dst: destinations with more edges are summed piecewise by CTAs
+                                    // (a single warp on a longer row is the tail of the kernel)
 
 struct GatArgs {
   const void *ptr;       // graph that is walked: CSR (forward) or transposed CSR (backward)
@@ -578,55 +579,93 @@ __device__ __forceinline__ float strided_sum(const float *v, int64_t lo, int64_t
 __global__ void __launch_bounds__(256) gat_dst_sum_rows(const void *ptr, int ptr_bytes, const float *d_edge, float *d_a_dst,
                                                         int64_t n_dst, int64_t nnz, int heads, int hshift, int32_t *hdr,
                                                         int64_t *long_rows, int max_long) {
+  constexpr int kRows = 4;  // destinations per warp and round: their loads are in flight together
   const int lane = threadIdx.x & 31;
-  const int head = lane & (heads - 1), slot = lane >> hshift;
+  const int head = lane & (heads - 1), slot = lane >> hshift, nslot = 32 >> hshift;
   const int64_t gwarp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  for (int64_t r = gwarp; r < n_dst; r += nwarps) {
-    const int64_t e0 = min(load_ptr(ptr, r, ptr_bytes), nnz), e1 = min(load_ptr(ptr, r + 1, ptr_bytes), nnz);
-    if (e1 - e0 > kLongRowEdges) {
-      if (lane == 0) {
-        const int s = atomicAdd(hdr + 1, 1);  // the list's order does not enter any sum
-        if (s < max_long) long_rows[s] = r;
+  for (int64_t r0 = gwarp * kRows; r0 < n_dst; r0 += nwarps * kRows) {
+    // ptr[r0 .. r0 + kRows] through the first lanes
+    int64_t pe = 0;
+    if (lane <= kRows && r0 + lane <= n_dst) pe = min(load_ptr(ptr, r0 + lane, ptr_bytes), nnz);
+    int64_t e[kRows + 1];
+#pragma unroll
+    for (int j = 0; j <= kRows; ++j) e[j] = __shfl_sync(0xffffffffu, pe, j);
+    // rows of at most 4 * nslot edges: all their values requested before any is used; a lane's (up to) four values
+    // are added as (v0 + v1) + (v2 + v3), which is the order strided_sum gives the same values
+    float v[kRows][4];
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      const bool row_on = r0 + j < n_dst && e[j + 1] - e[j] <= 4 * nslot;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t ed = e[j] + slot + k * nslot;
+        v[j][k] = (row_on && ed < e[j + 1]) ? __ldg(d_edge + ed * heads + head) : 0.f;
       }
-      continue;
     }
-    // value (e, head) sits at d_edge[e * heads + head]: this lane walks e = e0 + slot, e0 + slot + 32 / heads, ...
-    float acc = strided_sum(d_edge + head, (e0 + slot) * heads, e1 * heads, 32);
-    for (int o = heads; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane < heads) d_a_dst[r * heads + head] = acc;
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      const int64_t r = r0 + j;
+      if (r >= n_dst) break;
+      const int64_t e0 = e[j], e1 = e[j + 1];
+      if (e1 - e0 > kLongRowEdges) {
+        if (lane == 0) {
+          const int s = atomicAdd(hdr + 1, 1);  // the list's order does not enter any sum
+          if (s < max_long) long_rows[s] = r;
+        }
+        continue;
+      }
+      float acc;
+      if (e1 - e0 <= 4 * nslot)
+        acc = (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
+      else  // value (e, head) sits at d_edge[e * heads + head]: this lane walks e = e0 + slot, e0 + slot + nslot, ...
+        acc = strided_sum(d_edge + head, (e0 + slot) * heads, e1 * heads, 32);
+      for (int o = heads; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane < heads) d_a_dst[r * heads + head] = acc;
+    }
   }
 }
 
 // Long destinations, first level: the edge array is cut into pieces of kPieceEdges consecutive edges; every piece of
 // a listed row is summed by one CTA (thread (slot, head) takes every (256 / H)-th edge, then a fixed tree in shared
 // memory) into piece_sums. A piece holds at most one listed row's first edges and at most one listed row's later
-// edges, hence two slots per piece. The CTAs share a row's pieces round-robin.
+// edges, hence two slots per piece. The CTAs share a row's pieces round-robin; the rows' edge ranges are read 128
+// rows at a time into shared memory.
 constexpr int kPieceEdges = 1024;
 __global__ void __launch_bounds__(256) gat_dst_sum_pieces(const void *ptr, int ptr_bytes, const float *d_edge,
                                                           float *piece_sums, int64_t nnz, int heads, int hshift,
                                                           const int32_t *hdr, const int64_t *long_rows, int max_long) {
   __shared__ float red[256];
+  __shared__ int64_t range[2][128];
   const int tid = threadIdx.x;
   const int head = tid & (heads - 1), slot = tid >> hshift;
   const int n_long = min(hdr[1], max_long);
   const int G = gridDim.x;
-  for (int i = 0; i < n_long; ++i) {
-    const int64_t r = long_rows[i];
-    const int64_t e0 = min(load_ptr(ptr, r, ptr_bytes), nnz), e1 = min(load_ptr(ptr, r + 1, ptr_bytes), nnz);
-    const int64_t p0 = e0 / kPieceEdges, p1 = (e1 - 1) / kPieceEdges;
-    const int first = (static_cast<int>(blockIdx.x) + G - (i % G)) % G;
-    for (int64_t p = p0 + first; p <= p1; p += G) {
-      const int64_t lo = max(e0, p * kPieceEdges), hi = min(e1, (p + 1) * kPieceEdges);
-      red[tid] = strided_sum(d_edge + head, (lo + slot) * heads, hi * heads, 256);
-      __syncthreads();
-      for (int o = 128; o >= heads; o >>= 1) {
-        if (tid < o) red[tid] += red[tid + o];
+  for (int i0 = 0; i0 < n_long; i0 += 128) {
+    {
+      const int i = i0 + (tid & 127);
+      if (i < n_long) range[tid >> 7][tid & 127] = min(load_ptr(ptr, long_rows[i] + (tid >> 7), ptr_bytes), nnz);
+    }
+    __syncthreads();
+    const int cnt = min(128, n_long - i0);
+    for (int ii = 0; ii < cnt; ++ii) {
+      const int i = i0 + ii;
+      const int64_t e0 = range[0][ii], e1 = range[1][ii];
+      const int64_t p0 = e0 / kPieceEdges, p1 = (e1 - 1) / kPieceEdges;
+      const int first = (static_cast<int>(blockIdx.x) + G - (i % G)) % G;
+      for (int64_t p = p0 + first; p <= p1; p += G) {
+        const int64_t lo = max(e0, p * kPieceEdges), hi = min(e1, (p + 1) * kPieceEdges);
+        red[tid] = strided_sum(d_edge + head, (lo + slot) * heads, hi * heads, 256);
+        __syncthreads();
+        for (int o = 128; o >= heads; o >>= 1) {
+          if (tid < o) red[tid] += red[tid + o];
+          __syncthreads();
+        }
+        if (tid < heads) piece_sums[(2 * p + (p == p0 ? 1 : 0)) * heads + tid] = red[tid];
         __syncthreads();
       }
-      if (tid < heads) piece_sums[(2 * p + (p == p0 ? 1 : 0)) * heads + tid] = red[tid];
-      __syncthreads();
     }
+    __syncthreads();
   }
 }
 
