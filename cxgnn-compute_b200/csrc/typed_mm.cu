@@ -50,6 +50,8 @@
 // Every wait is bounded: a role that waits longer than about a second raises a CTA-wide abort
 // flag and an error status; all roles then leave their loops, the copies in flight are waited
 // for, the tensor memory is released and the kernel returns.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder is obtained through the runtime, nothing links libcuda
+
 #include "common.cuh"
 
 namespace cxg {
@@ -103,6 +105,28 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint3
   d |= static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32;
   d |= 1ull << 46;  // descriptor version of sm_100
   return d;
+}
+
+// The same for a tile that the bulk tensor copy unit (TMA) wrote with its 128-byte swizzle: rows of 128 bytes (one
+// swizzle span of K), 8-row groups 1024 bytes apart, the 16-byte chunks of a row permuted by (row % 8). The tile must
+// start on a 1024-byte boundary; K advances inside the span by adding bytes to `addr`.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3fff);
+  d |= 1ull << 16;                                   // leading offset: unused with a swizzle, canonical value 1
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;       // next 8-row group
+  d |= 1ull << 46;                                   // descriptor version of sm_100
+  d |= 2ull << 61;                                   // layout type: 128-byte swizzle
+  return d;
+}
+
+// One tiled 2-D bulk tensor copy global -> shared (x = element column, y = row of the tensor map's matrix); its bytes
+// are counted on `bar`. x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
 }
 
 // Instruction descriptor: fp32 accumulate, A and B of format `fmt` (1 = bf16, 2 = tf32), both K-major.
@@ -226,8 +250,11 @@ __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
 
 // PW producer warps; each copies 128 / PW rows of a tile, kSlots of them per thread. X3: error-compensated
 // fp32 (three TF32 products per term), with kConvWarps converter warps behind the producers.
-template <typename T, bool CA, int PW, bool X3>
-__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : kEpiWarps)), 1) typed_mm_tc(TmmArgs a) {
+// TMA: (dense mode, 2-byte elements) the tiles of A are not gathered by the producers' 16-byte copies but fetched by the
+// bulk tensor copy unit, two 128 x 64 boxes per tile with the 128-byte swizzle, issued by one producer thread.
+template <typename T, bool CA, int PW, bool X3, bool TMA>
+__global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : kEpiWarps)), 1)
+    typed_mm_tc(TmmArgs a, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int kProdWarps = PW;
   constexpr int kRowsPerProdWarp = kTileM / kProdWarps;
   constexpr int kSlots = kRowsPerProdWarp / kRpi;
@@ -257,6 +284,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
   const size_t w_bytes = static_cast<size_t>(a.n) * a.k * sizeof(T);        // n rows of W[rel]^T
   uint8_t *smem_b = smem;                                    // W (hi), then W lo in the compensated mode
   uint8_t *smem_a = smem + (X3 ? 2 * w_bytes : w_bytes);     // S stages
+  if (TMA) smem_a += (1024u - (smem_addr(smem_a) & 1023u)) & 1023u;  // swizzled tiles start on 1024-byte boundaries
 
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
@@ -344,14 +372,29 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
           if (!alive) break;
         }
         const uint32_t a0 = smem_addr(smem_a + s * a_bytes);
+        if (TMA) {
+          // one thread announces the tile's bytes on the stage barrier and asks the copy unit for its boxes (rows past
+          // the end of A arrive as zeros); its own arrival below comes after the announcement, so the phase cannot
+          // complete without the bytes
+          if (pw == 0 && lane == 0) {
+            const uint32_t bar = smem_addr(&bars.full[s]);
+            asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar),
+                         "r"(static_cast<uint32_t>(a_bytes))
+                         : "memory");
+            const int span = 128 / static_cast<int>(sizeof(T));  // elements of K per 128-byte swizzle span
+            for (int h = 0; h * span < a.kb; ++h)
+              tma_load_2d(a0 + h * (kTileM * 128), &tmap_a, kb * a.kb + h * span, static_cast<int>(tile * kTileM), bar);
+          }
+        } else {
 #pragma unroll
-        for (int gi = 0; gi < kSlots; ++gi) {
-          const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;  // row of the tile
-          const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
-          const T *src_row = ok ? A + ia[gi] * a.k + kb * a.kb : A;
-          const int bytes = ok ? 16 : 0;  // size 0 writes zeros
-          const uint32_t d0 = a0 + (row >> 3) * sbo_a + (row & 7) * 16;
-          for (int c = cq; c < chunks_blk; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
+          for (int gi = 0; gi < kSlots; ++gi) {
+            const int row = pw * kRowsPerProdWarp + gi * kRpi + rsub;  // row of the tile
+            const bool ok = ia[gi] >= 0 && ia[gi] < a.m_valid;
+            const T *src_row = ok ? A + ia[gi] * a.k + kb * a.kb : A;
+            const int bytes = ok ? 16 : 0;  // size 0 writes zeros
+            const uint32_t d0 = a0 + (row >> 3) * sbo_a + (row & 7) * 16;
+            for (int c = cq; c < chunks_blk; c += kCpi) cp_async16<CA>(d0 + c * 128, src_row + c * EPC, bytes);
+          }
         }
         // the unit's full barrier counts this thread's arrival when all copies it has issued so far (this unit's
         // rows, and W when it was re-copied) have landed: the producer never waits for its own copies
@@ -429,6 +472,10 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
               mma_ss<TF32>(d, da_hi, db_lo, idesc, first);  // the two small terms first, the large one last
               mma_ss<TF32>(d, da_lo, db_hi, idesc, 1u);
               mma_ss<TF32>(d, da_hi, db_hi, idesc, 1u);
+            } else if (TMA) {
+              // step j reads 32 bytes of K: span j / 4 of the stage (16 KiB each), 32-byte offset j % 4 inside it
+              mma_ss<TF32>(d, make_desc_sw128(a0 + (j >> 2) * (kTileM * 128) + (j & 3) * 32),
+                           make_desc(bk + j * 256, lbo, sbo_b), idesc, first);
             } else {
               mma_ss<TF32>(d, make_desc(a0 + j * 256, lbo, sbo_a), make_desc(bk + j * 256, lbo, sbo_b), idesc, first);
             }
@@ -595,6 +642,38 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
 
 using namespace cxg;
 
+namespace {
+
+// Tensor map of a row-major [rows][k] matrix of 2-byte elements for boxes of 128 rows x 64 columns (one 128-byte
+// swizzle span). False when the driver's encoder is not available or refuses the arguments.
+bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      (void)cudaGetLastError();
+    looked = true;
+  }
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTileM)};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
 extern "C" int cxg_typed_matmul_workspace_size(int num_rel, int k, int n, int dtype, size_t *bytes) {
   CXG_REQUIRE(bytes != nullptr, CXG_ENULL, "cxg_typed_matmul_workspace_size: bytes is NULL");
   CXG_REQUIRE(num_rel > 0 && k > 0 && n > 0 && (dtype == CXG_F32 || dtype == CXG_BF16), CXG_EINVAL,
@@ -668,9 +747,16 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   const size_t a_bytes = stage_bytes(kb);
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
               "cxg_typed_matmul: one stage of %zu bytes plus W of %zu bytes exceeds shared memory", a_bytes, b_bytes);
-  int stages = static_cast<int>((kSmemBudget - b_bytes) / a_bytes);
+  // Dense mode, bf16, whole rows per stage: the tiles of A are contiguous row blocks, which the bulk tensor copy unit
+  // fetches as two swizzled boxes per tile (CXG_TMM_NO_TMA keeps the 16-byte copies, for comparison)
+  CUtensorMap tmap;
+  memset(&tmap, 0, sizeof(tmap));
+  const bool tma = dense && dtype == CXG_BF16 && kb == k && k % 64 == 0 && k <= 256 && !(flags & CXG_TMM_NO_TMA) &&
+                   m < (1ll << 31) && encode_a_map(&tmap, a, m_valid, k);
+  const size_t tma_pad = tma ? 1024 : 0;  // the stages start on a 1024-byte boundary
+  int stages = static_cast<int>((kSmemBudget - b_bytes - tma_pad) / a_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
-  const size_t smem = b_bytes + stages * a_bytes;
+  const size_t smem = b_bytes + tma_pad + stages * a_bytes;
   CXG_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (k * elem) % 16 == 0 &&
                   (n * elem) % 16 == 0,
               CXG_EINVAL, "cxg_typed_matmul: A, C and their rows must be 16-byte aligned");
@@ -713,7 +799,7 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   cudaError_t e = cudaSuccess;
   auto launch = [&](auto kernel, int warps) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), 32 * warps, smem, st>>>(t);
+    if (e == cudaSuccess) kernel<<<static_cast<unsigned>(grid), 32 * warps, smem, st>>>(t, tmap);
   };
   if (dtype == CXG_F32) {
     float *wt_f = static_cast<float *>(wt);
@@ -722,15 +808,20 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
                                                ncols);
     constexpr int kW = kEpiWarps + 1 + 8;
     if (x3) {
-      if (ca) launch(typed_mm_tc<float, true, 8, true>, kW + kConvWarps); else launch(typed_mm_tc<float, false, 8, true>, kW + kConvWarps);
+      if (ca) launch(typed_mm_tc<float, true, 8, true, false>, kW + kConvWarps); else launch(typed_mm_tc<float, false, 8, true, false>, kW + kConvWarps);
     } else {
-      if (ca) launch(typed_mm_tc<float, true, 8, false>, kW + kEpiWarps); else launch(typed_mm_tc<float, false, 8, false>, kW + kEpiWarps);
+      if (ca) launch(typed_mm_tc<float, true, 8, false, false>, kW + kEpiWarps); else launch(typed_mm_tc<float, false, 8, false, false>, kW + kEpiWarps);
     }
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),
                                                        static_cast<__nv_bfloat16 *>(wt), nullptr, num_rel, k, ncols);
     constexpr int kW = kEpiWarps + 1 + 4;
-    if (ca) launch(typed_mm_tc<__nv_bfloat16, true, 4, false>, kW + kEpiWarps); else launch(typed_mm_tc<__nv_bfloat16, false, 4, false>, kW + kEpiWarps);
+    if (tma)
+      launch(typed_mm_tc<__nv_bfloat16, false, 4, false, true>, kW + kEpiWarps);
+    else if (ca)
+      launch(typed_mm_tc<__nv_bfloat16, true, 4, false, false>, kW + kEpiWarps);
+    else
+      launch(typed_mm_tc<__nv_bfloat16, false, 4, false, false>, kW + kEpiWarps);
   }
   if (e != cudaSuccess) return set_error(CXG_ECUDA, "cxg_typed_matmul: %s", cudaGetErrorString(e));
   count_launches(2);

@@ -215,7 +215,7 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
     return c
 
 
-def typed_matmul_all_relations(x, w, allow_tf32=None):
+def typed_matmul_all_relations(x, w, allow_tf32=None, extra_flags=0):
     """[R, N, out] = x [N, K] multiplied by every relation's weight w [R, K, out] in one launch of the tensor-core
     kernel (cxg_typed_matmul with CXG_TMM_ALL_RELATIONS): the first half of TypedLinearS2DMMAggrOP
     (cxgnncomp/typed_linear.py:191-221), which the reference runs as num_rel torch.mm calls. No autograd."""
@@ -234,7 +234,7 @@ def typed_matmul_all_relations(x, w, allow_tf32=None):
     _check(_tmm_ws(num_rel, k, n, dtype, ctypes.byref(need)), "cxg_typed_matmul_workspace_size")
     ws = _workspace(x.device, need.value, "typed_matmul")
     with torch.cuda.device(x.device):
-        _check(_tmm(_p(x), _p(w), _p(c), None, None, None, m, m, k, n, num_rel, dtype, precision, 8, _p(ws), ws.numel(),
+        _check(_tmm(_p(x), _p(w), _p(c), None, None, None, m, m, k, n, num_rel, dtype, precision, 8 | int(extra_flags), _p(ws), ws.numel(),
                     _stream()), "cxg_typed_matmul")
     return c
 

@@ -119,7 +119,8 @@ def test_typed_matmul_tensor_cores(cuda, dtype, k, n, tol, thres):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("num_rel,n_rows,k,n", [(8, 5000, 128, 64), (3, 130, 64, 32), (5, 40000, 64, 64), (1, 257, 32, 16)])
+@pytest.mark.parametrize("num_rel,n_rows,k,n", [(8, 5000, 128, 64), (3, 130, 64, 32), (5, 40000, 64, 64), (1, 257, 32, 16),
+                                                (2, 1000, 256, 32), (4, 128, 128, 64)])
 def test_typed_matmul_all_relations(cuda, dtype, tol, num_rel, n_rows, k, n):
     """Dense mode: every row times every relation's weight in one launch, [R, N, out] (the reference runs num_rel
     torch.mm calls, typed_linear.py:195-201); forward against float64, gradients against autograd."""
@@ -132,6 +133,10 @@ def test_typed_matmul_all_relations(cuda, dtype, tol, num_rel, n_rows, k, n):
     want = torch.matmul(x.double().unsqueeze(0), w.double())
     assert got.shape == (num_rel, n_rows, n)
     assert rel_err(got.detach().float().cpu(), want) < tol
+    if dtype == torch.bfloat16:
+        # the tiles of A fetched by tiled bulk tensor copies (default where they apply) or by 16-byte copies: same bits
+        copies = be.typed_matmul_all_relations(x.cuda(), w.cuda(), extra_flags=be.CXG_TMM_NO_TMA)
+        assert torch.equal(copies, got.detach())
     if dtype == torch.float32:
         plain = be.typed_matmul_all_relations(x.cuda(), w.cuda(), allow_tf32=True)
         assert rel_err(plain.cpu(), want) < 2e-3
