@@ -250,8 +250,9 @@ __device__ __forceinline__ void st_global_v4(void *p, uint4 v) {
 
 // PW producer warps; each copies 128 / PW rows of a tile, kSlots of them per thread. X3: error-compensated
 // fp32 (three TF32 products per term), with kConvWarps converter warps behind the producers.
-// TMA: (dense mode, 2-byte elements) the tiles of A are not gathered by the producers' 16-byte copies but fetched by the
-// bulk tensor copy unit, two 128 x 64 boxes per tile with the 128-byte swizzle, issued by one producer thread.
+// TMA: (dense mode) the tiles of A are not gathered by the producers' 16-byte copies but fetched by the bulk tensor copy
+// unit, boxes of 128 rows x 128 bytes with the 128-byte swizzle, issued by one producer thread. The converters of the
+// compensated mode work element by element, so they keep whatever layout the stage has.
 template <typename T, bool CA, int PW, bool X3, bool TMA>
 __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : kEpiWarps)), 1)
     typed_mm_tc(TmmArgs a, const __grid_constant__ CUtensorMap tmap_a) {
@@ -379,7 +380,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
           if (pw == 0 && lane == 0) {
             const uint32_t bar = smem_addr(&bars.full[s]);
             asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar),
-                         "r"(static_cast<uint32_t>(a_bytes))
+                         "r"(static_cast<uint32_t>(half_bytes))
                          : "memory");
             const int span = 128 / static_cast<int>(sizeof(T));  // elements of K per 128-byte swizzle span
             for (int h = 0; h * span < a.kb; ++h)
@@ -465,8 +466,10 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
           for (int j = 0; j < steps; ++j) {
             const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
             if (X3) {
-              const uint64_t da_hi = make_desc(a0 + j * 256, lbo, sbo_a);
-              const uint64_t da_lo = make_desc(a0 + static_cast<uint32_t>(half_bytes) + j * 256, lbo, sbo_a);
+              const uint32_t ao = TMA ? (j >> 2) * (kTileM * 128) + (j & 3) * 32 : j * 256;  // as in the plain branch below
+              const uint64_t da_hi = TMA ? make_desc_sw128(a0 + ao) : make_desc(a0 + ao, lbo, sbo_a);
+              const uint64_t da_lo = TMA ? make_desc_sw128(a0 + static_cast<uint32_t>(half_bytes) + ao)
+                                         : make_desc(a0 + static_cast<uint32_t>(half_bytes) + ao, lbo, sbo_a);
               const uint64_t db_hi = make_desc(bk + j * 256, lbo, sbo_b);
               const uint64_t db_lo = make_desc(bk + static_cast<uint32_t>(w_bytes) + j * 256, lbo, sbo_b);
               mma_ss<TF32>(d, da_hi, db_lo, idesc, first);  // the two small terms first, the large one last
@@ -644,9 +647,9 @@ using namespace cxg;
 
 namespace {
 
-// Tensor map of a row-major [rows][k] matrix of 2-byte elements for boxes of 128 rows x 64 columns (one 128-byte
-// swizzle span). False when the driver's encoder is not available or refuses the arguments.
-bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k) {
+// Tensor map of a row-major [rows][k] matrix of bf16 or fp32 elements for boxes of 128 rows x one 128-byte swizzle
+// span of columns (64 / 32 elements). False when the driver's encoder is not available or refuses the arguments.
+bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k, int elem) {
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -664,10 +667,10 @@ bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k) {
   }
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTileM)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * elem};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem), static_cast<cuuint32_t>(kTileM)};
   const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+  return fn(map, elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -747,12 +750,12 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   const size_t a_bytes = stage_bytes(kb);
   CXG_REQUIRE(a_bytes + b_bytes <= static_cast<size_t>(kSmemBudget), CXG_ELIMIT,
               "cxg_typed_matmul: one stage of %zu bytes plus W of %zu bytes exceeds shared memory", a_bytes, b_bytes);
-  // Dense mode, bf16, whole rows per stage: the tiles of A are contiguous row blocks, which the bulk tensor copy unit
-  // fetches as two swizzled boxes per tile (CXG_TMM_NO_TMA keeps the 16-byte copies, for comparison)
+  // Dense mode: the tiles of A are contiguous row blocks, which the bulk tensor copy unit fetches as swizzled boxes of
+  // 128 rows x 128 bytes, one to four per K-block (CXG_TMM_NO_TMA keeps the 16-byte copies, for comparison)
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
-  const bool tma = dense && dtype == CXG_BF16 && kb == k && k % 64 == 0 && k <= 256 && !(flags & CXG_TMM_NO_TMA) &&
-                   m < (1ll << 31) && encode_a_map(&tmap, a, m_valid, k);
+  const bool tma = dense && (kb * elem) % 128 == 0 && kb * elem <= 512 && !(flags & CXG_TMM_NO_TMA) && m < (1ll << 31) &&
+                   encode_a_map(&tmap, a, m_valid, k, elem);
   const size_t tma_pad = tma ? 1024 : 0;  // the stages start on a 1024-byte boundary
   int stages = static_cast<int>((kSmemBudget - b_bytes - tma_pad) / a_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
@@ -808,9 +811,19 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
                                                ncols);
     constexpr int kW = kEpiWarps + 1 + 8;
     if (x3) {
-      if (ca) launch(typed_mm_tc<float, true, 8, true, false>, kW + kConvWarps); else launch(typed_mm_tc<float, false, 8, true, false>, kW + kConvWarps);
+      if (tma)
+        launch(typed_mm_tc<float, false, 8, true, true>, kW + kConvWarps);
+      else if (ca)
+        launch(typed_mm_tc<float, true, 8, true, false>, kW + kConvWarps);
+      else
+        launch(typed_mm_tc<float, false, 8, true, false>, kW + kConvWarps);
     } else {
-      if (ca) launch(typed_mm_tc<float, true, 8, false, false>, kW + kEpiWarps); else launch(typed_mm_tc<float, false, 8, false, false>, kW + kEpiWarps);
+      if (tma)
+        launch(typed_mm_tc<float, false, 8, false, true>, kW + kEpiWarps);
+      else if (ca)
+        launch(typed_mm_tc<float, true, 8, false, false>, kW + kEpiWarps);
+      else
+        launch(typed_mm_tc<float, false, 8, false, false>, kW + kEpiWarps);
     }
   } else {
     transpose_w<__nv_bfloat16><<<kNumSM, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(w),

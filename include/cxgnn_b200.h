@@ -480,8 +480,8 @@ int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
    (cxgnncomp/typed_linear.py:191-221) as one launch. rel, src_idx, dst_idx must be NULL, m_valid == m,
    precision 1 or 2. */
 #define CXG_TMM_ALL_RELATIONS 8
-/* Measurement aid: the dense mode with bf16 inputs normally fetches the tiles of A with tiled bulk tensor copies
-   (two 128 x 64 boxes per tile, 128-byte swizzle); this flag keeps the 16-byte asynchronous copies. Same results. */
+/* Measurement aid: the dense mode normally fetches the tiles of A with tiled bulk tensor copies (boxes of 128 rows x
+   128 bytes, 128-byte swizzle); this flag keeps the 16-byte asynchronous copies. Same results. */
 #define CXG_TMM_NO_TMA 16
 /* Test hook: the first tile of every CTA is never handed to the tensor-core role, so the bounded
    waits for it run out (status CXG_ETIMEOUT, all roles leave, tensor memory is released). Use it

@@ -133,13 +133,14 @@ def test_typed_matmul_all_relations(cuda, dtype, tol, num_rel, n_rows, k, n):
     want = torch.matmul(x.double().unsqueeze(0), w.double())
     assert got.shape == (num_rel, n_rows, n)
     assert rel_err(got.detach().float().cpu(), want) < tol
-    if dtype == torch.bfloat16:
-        # the tiles of A fetched by tiled bulk tensor copies (default where they apply) or by 16-byte copies: same bits
-        copies = be.typed_matmul_all_relations(x.cuda(), w.cuda(), extra_flags=be.CXG_TMM_NO_TMA)
-        assert torch.equal(copies, got.detach())
+    # the tiles of A fetched by tiled bulk tensor copies (default where they apply) or by 16-byte copies: same bits
+    copies = be.typed_matmul_all_relations(x.cuda(), w.cuda(), extra_flags=be.CXG_TMM_NO_TMA)
+    assert torch.equal(copies, got.detach())
     if dtype == torch.float32:
         plain = be.typed_matmul_all_relations(x.cuda(), w.cuda(), allow_tf32=True)
         assert rel_err(plain.cpu(), want) < 2e-3
+        assert torch.equal(plain, be.typed_matmul_all_relations(x.cuda(), w.cuda(), allow_tf32=True,
+                                                                extra_flags=be.CXG_TMM_NO_TMA))
         go = randn(want.shape, 23)
         got.backward(go.cuda())
         xr, wr = x.double().requires_grad_(True), w.double().requires_grad_(True)
