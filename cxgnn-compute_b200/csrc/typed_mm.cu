@@ -129,6 +129,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+// Four rows of the tensor map's matrix (any four: y0 .. y3), columns [x, x + box width), into 4 x 128 consecutive
+// bytes of shared memory (tile::gather4; the map's box is one row high). Rows outside the matrix arrive as zeros.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *map, int x, int y0, int y1, int y2, int y3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6, %7}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+      : "memory");
+}
+
 // Instruction descriptor: fp32 accumulate, A and B of format `fmt` (1 = bf16, 2 = tf32), both K-major.
 __device__ __forceinline__ uint32_t make_idesc(int fmt, int m, int n) {
   uint32_t d = 0;
@@ -259,6 +270,7 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
   constexpr int kProdWarps = PW;
   constexpr int kRowsPerProdWarp = kTileM / kProdWarps;
   constexpr int kSlots = kRowsPerProdWarp / kRpi;
+  constexpr int kIdx = kSlots < 4 ? 4 : kSlots;  // row indices a producer thread keeps (four for a gathering bulk copy)
   constexpr bool TF32 = sizeof(T) == 4;
   constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
   constexpr int kFirstConvWarp = kMmaWarp + 1 + PW;
@@ -331,23 +343,26 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
     int64_t it = 0;        // units (tile, K-block) issued by this CTA
     bool alive = true;
     // the relation and the row indices of a tile are fetched one tile ahead, off the critical path
-    auto fetch = [&](int64_t tile, int64_t &r, int64_t (&ia)[kSlots]) {
+    auto fetch = [&](int64_t tile, int64_t &r, int64_t (&ia)[kIdx]) {
       const int64_t m0 = tile * kTileM;
       r = rel_of(tile);
 #pragma unroll
-      for (int gi = 0; gi < kSlots; ++gi) {
-        const int64_t pos = m0 + pw * kRowsPerProdWarp + gi * kRpi + rsub;  // warp pw owns kRowsPerProdWarp rows
+      for (int gi = 0; gi < kIdx; ++gi) {
+        // warp pw owns kRowsPerProdWarp rows; with gathering bulk tensor copies lane l of warp 0 asks for rows 4l .. 4l+3
+        const bool g4 = TMA && !dense;
+        const int64_t pos = g4 ? m0 + 4 * lane + gi : m0 + pw * kRowsPerProdWarp + gi * kRpi + rsub;
         ia[gi] = -1;
+        if (g4 ? gi >= 4 : gi >= kSlots) continue;
         if (tile < tile_hi && pos < a.m) ia[gi] = a.src != nullptr ? a.src[pos] : pos;
       }
     };
-    int64_t r_next, ia_next[kSlots];
+    int64_t r_next, ia_next[kIdx];
     fetch(tile_lo, r_next, ia_next);
     for (int64_t tile = tile_lo; tile < tile_hi && alive; ++tile) {
       const int64_t r = r_next;
-      int64_t ia[kSlots];
+      int64_t ia[kIdx];
 #pragma unroll
-      for (int gi = 0; gi < kSlots; ++gi) ia[gi] = ia_next[gi];
+      for (int gi = 0; gi < kIdx; ++gi) ia[gi] = ia_next[gi];
       fetch(tile + 1, r_next, ia_next);
       if (r < 0 || r >= a.num_rel) continue;  // a tile of padding only
       if (r != loaded_rel) {
@@ -377,14 +392,26 @@ __global__ void __launch_bounds__(32 * (kEpiWarps + 1 + PW + (X3 ? kConvWarps : 
           // one thread announces the tile's bytes on the stage barrier and asks the copy unit for its boxes (rows past
           // the end of A arrive as zeros); its own arrival below comes after the announcement, so the phase cannot
           // complete without the bytes
-          if (pw == 0 && lane == 0) {
-            const uint32_t bar = smem_addr(&bars.full[s]);
+          const uint32_t bar = smem_addr(&bars.full[s]);
+          const int span = 128 / static_cast<int>(sizeof(T));  // elements of K per 128-byte swizzle span
+          if (pw == 0 && lane == 0)
             asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar),
                          "r"(static_cast<uint32_t>(half_bytes))
                          : "memory");
-            const int span = 128 / static_cast<int>(sizeof(T));  // elements of K per 128-byte swizzle span
+          if (dense) {
+            if (pw == 0 && lane == 0)
+              for (int h = 0; h * span < a.kb; ++h)
+                tma_load_2d(a0 + h * (kTileM * 128), &tmap_a, kb * a.kb + h * span, static_cast<int>(tile * kTileM), bar);
+          } else if (pw == 0) {
+            // gathered rows: every lane of the first producer warp asks for its four rows of every span; a position
+            // without a row (padding, index out of range) names the row past the matrix and receives zeros
+            __syncwarp();  // the announcement above precedes every request
+            int y[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              y[i] = (ia[i] >= 0 && ia[i] < a.m_valid) ? static_cast<int>(ia[i]) : static_cast<int>(a.m_valid);
             for (int h = 0; h * span < a.kb; ++h)
-              tma_load_2d(a0 + h * (kTileM * 128), &tmap_a, kb * a.kb + h * span, static_cast<int>(tile * kTileM), bar);
+              tma_gather4(a0 + h * (kTileM * 128) + lane * 512, &tmap_a, kb * a.kb + h * span, y[0], y[1], y[2], y[3], bar);
           }
         } else {
 #pragma unroll
@@ -649,7 +676,7 @@ namespace {
 
 // Tensor map of a row-major [rows][k] matrix of bf16 or fp32 elements for boxes of 128 rows x one 128-byte swizzle
 // span of columns (64 / 32 elements). False when the driver's encoder is not available or refuses the arguments.
-bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k, int elem) {
+bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k, int elem, int box_rows) {
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -668,7 +695,7 @@ bool encode_a_map(CUtensorMap *map, const void *base, int64_t rows, int k, int e
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * elem};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem), static_cast<cuuint32_t>(kTileM)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   return fn(map, elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -754,8 +781,15 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
   // 128 rows x 128 bytes, one to four per K-block (CXG_TMM_NO_TMA keeps the 16-byte copies, for comparison)
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
-  const bool tma = dense && (kb * elem) % 128 == 0 && kb * elem <= 512 && !(flags & CXG_TMM_NO_TMA) && m < (1ll << 31) &&
-                   encode_a_map(&tmap, a, m_valid, k, elem);
+  // Rows gathered by index and read once can go through the same copy unit in its gathering form (tile::gather4: four
+  // rows of 128 bytes per request, box one row high) with CXG_TMM_GATHER4. It is not the default: one request per
+  // 512 bytes keeps the copy unit busier than the 16-byte copies keep the producers (config 4, per-edge matmul:
+  // 3.47 vs 2.07 ms in bf16, 6.95 vs 3.73 ms in TF32).
+  const bool ca = src_idx != nullptr && m_valid * 2 <= m;
+  const bool tma = (dense || (!ca && (flags & CXG_TMM_GATHER4))) && (kb * elem) % 128 == 0 && kb * elem <= 512 &&
+                   !(flags & CXG_TMM_NO_TMA) &&
+                   m < (1ll << 31) && m_valid < (1ll << 31) - 1 && m_valid > 0 &&
+                   encode_a_map(&tmap, a, m_valid, k, elem, dense ? kTileM : 1);
   const size_t tma_pad = tma ? 1024 : 0;  // the stages start on a 1024-byte boundary
   int stages = static_cast<int>((kSmemBudget - b_bytes - tma_pad) / a_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
@@ -796,9 +830,8 @@ extern "C" int cxg_typed_matmul(const void *a, const void *w, void *c, const int
     if (groups > n_tiles) groups = n_tiles;
     grid = groups * sets;
   }
-  // rows that are gathered several times each go through L1, rows read once bypass it
+  // rows that are gathered several times each go through L1 (`ca` above), rows read once bypass it
   // (rows read once: L1-allocating copies measured 4-6 % slower on the dense mode as well)
-  const bool ca = src_idx != nullptr && m_valid * 2 <= m;
   cudaError_t e = cudaSuccess;
   auto launch = [&](auto kernel, int warps) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

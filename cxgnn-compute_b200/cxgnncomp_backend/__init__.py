@@ -143,6 +143,7 @@ CXG_SPMM_TMA_INDEX = 64  # source ids staged by bulk copies into a ring in share
 CXG_SPMM_SHARE_SMS = 32
 CXG_TMM_TEST_STALL = 4
 CXG_TMM_NO_TMA = 16  # dense mode: 16-byte copies instead of tiled bulk tensor copies for A
+CXG_TMM_GATHER4 = 32  # gathered rows through the bulk tensor copy unit (tile::gather4); slower, for measurement
 EXTRA_SPMM_FLAGS = int(os.environ.get("CXG_SPMM_FLAGS", "0"))
 
 

@@ -483,6 +483,10 @@ int cxg_rel_schedule_host(const int64_t *ptr_host, const int64_t *idx_host,
 /* Measurement aid: the dense mode normally fetches the tiles of A with tiled bulk tensor copies (boxes of 128 rows x
    128 bytes, 128-byte swizzle); this flag keeps the 16-byte asynchronous copies. Same results. */
 #define CXG_TMM_NO_TMA 16
+/* Measurement aid: rows gathered by index (read once each) are fetched by the bulk tensor copy unit in its gathering
+   form (tile::gather4, four rows of 128 bytes per request) instead of 16-byte asynchronous copies. Same results;
+   slower on every shape measured, hence not the default. */
+#define CXG_TMM_GATHER4 32
 /* Test hook: the first tile of every CTA is never handed to the tensor-core role, so the bounded
    waits for it run out (status CXG_ETIMEOUT, all roles leave, tensor memory is released). Use it
    with a short cxg_set_wait_limit_cycles. */

@@ -104,6 +104,11 @@ def test_typed_matmul_tensor_cores(cuda, dtype, k, n, tol, thres):
     want = oracle.typed_linear_f64(a, w, types)
     assert c.shape == (E, n)
     assert rel_err(c.float().cpu(), want) < tol
+    # rows fetched by gathering bulk tensor copies (an option, where a K-block is a multiple of 128 bytes) or by the
+    # default 16-byte copies: same bits
+    c2 = be.typed_matmul_raw(a.cuda(), w.cuda(), sorted_types, sorted_types.shape[0], E, src_idx=indices,
+                             extra_flags=be.CXG_TMM_GATHER4)
+    assert torch.equal(c, c2)
     # every real row was computed (the reference launches cdiv(E, BLOCK_M) tiles over the padded array and
     # leaves the last rows unset, triton_typed_matmul.py:776-782; not reproduced)
     row_err = (c.float().cpu().double() - want).abs().amax(1) / want.abs().amax().clamp(min=1e-30)
