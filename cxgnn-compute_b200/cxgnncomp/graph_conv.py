@@ -436,7 +436,8 @@ class MyGATConv(torch.nn.Module):
     def forward_many(self, x, ptr, idx, num_dst, num_src, num_edge):
         H, C = self.heads, self.out_channels
         assert x.dim() == 2
-        x_src = F.linear(x[:num_src], self.lin_src).view(-1, H, C)
+        # the layer's linear transform on the tensor-core kernel (fp32 accuracy kept by the compensated TF32 mode)
+        x_src = cxgnncomp_backend.dense_linear(x[:num_src], self.lin_src).view(-1, H, C)
         if x_src.dtype == torch.float32 and self.fused_scores:
             alpha_src, alpha_dst = cxgnncomp_backend.gat_scores(x_src.contiguous(), self.att_src.contiguous(),
                                                                 self.att_dst.contiguous(), num_dst)

@@ -281,3 +281,39 @@ class _TransformAllFunction(torch.autograd.Function):
 def transform_all_relations(x, w):
     """Differentiable typed_matmul_all_relations."""
     return _TransformAllFunction.apply(x, w)
+
+
+class _DenseLinearFunction(torch.autograd.Function):
+    """y = x @ weight^T (weight [out, in], torch.nn.functional.linear without bias) on the tensor-core kernel in its
+    dense mode with one relation: fp32 inputs keep fp32 accuracy (error-compensated TF32), where the library GEMM
+    torch would call runs on the fp32 SIMT pipe. dx = g @ weight goes the same way; dW = g^T @ x, a reduction over
+    the rows, stays with torch."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return typed_matmul_all_relations(x, weight.t().contiguous().unsqueeze(0))[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors
+        dx = dw = None
+        g = g.contiguous()
+        if ctx.needs_input_grad[0]:
+            w3 = weight.contiguous().unsqueeze(0)  # [1, out, in]: K = out, N = in
+            if typed_matmul_all_relations_supported(g, w3):
+                dx = typed_matmul_all_relations(g, w3)[0]
+            else:
+                dx = g @ weight
+        if ctx.needs_input_grad[1]:
+            dw = g.t() @ x
+        return dx, dw
+
+
+def dense_linear(x, weight):
+    """torch.nn.functional.linear(x, weight) for a 2-D x on the library's tensor-core kernel where its dense mode
+    covers the shape (same dtype fp32 / bf16, in a multiple of 8 / 16, out a multiple of 16 up to 256), else torch."""
+    if (x.dim() == 2 and x.is_cuda and x.shape[0] > 0 and weight.dtype == x.dtype and x.is_contiguous()
+            and typed_matmul_all_relations_supported(x, weight.t().unsqueeze(0))):
+        return _DenseLinearFunction.apply(x, weight)
+    return torch.nn.functional.linear(x, weight)

@@ -248,3 +248,21 @@ def test_status_words_clear_after_normal_calls(cuda):
         be.check_device_status("spmm")
     finally:
         be.EXTRA_SPMM_FLAGS = old
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("n,k,out", [(3000, 128, 128), (130, 64, 32), (1, 32, 16), (777, 100, 47)])
+def test_dense_linear(cuda, dtype, tol, n, k, out):
+    """x @ weight^T on the tensor-core kernel (dense mode, one relation), forward and both gradients against float64;
+    shapes the kernel does not cover (in = 100, out = 47) fall through to torch."""
+    import cxgnncomp_backend as be
+    x, w = randn((n, k), 31).to(dtype), (randn((out, k), 32) * 0.2).to(dtype)
+    xg, wg = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    y = be.dense_linear(xg, wg)
+    xr, wr = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    want = xr @ wr.t()
+    assert y.shape == (n, out) and rel_err(y.detach().float().cpu(), want.detach()) < tol
+    go = randn((n, out), 33)
+    y.backward(go.cuda().to(dtype))
+    want.backward(go.to(dtype).double())
+    assert rel_err(xg.grad.float().cpu(), xr.grad) < tol and rel_err(wg.grad.float().cpu(), wr.grad) < max(tol, 2e-5)
