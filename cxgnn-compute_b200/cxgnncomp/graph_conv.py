@@ -237,6 +237,11 @@ class RGCNFusedOP(torch.autograd.Function):
                                                dst_idx=src_sorted, atomic_out=gx)
             grad_x = gx.to(x.dtype)
         if ctx.needs_input_grad[1]:
+            if cxgnncomp_backend.typed_wgrad_supported(x, grad_out):
+                # one tensor-core launch: x rows by source, gradient rows by destination (-1 marks a padding position)
+                gw = cxgnncomp_backend.typed_wgrad(x.contiguous(), grad_out, sorted_types, weights.shape[0],
+                                                   idx=src_sorted, idx_g=dst_sorted)
+                return grad_x, gw.to(weights.dtype), None, None, None, None, None, None, None, None, None
             # the valid positions are sorted by relation: relation r owns count[r] consecutive ones
             grad_w = torch.zeros_like(weights)
             keep = (src_sorted >= 0).nonzero().squeeze(1)

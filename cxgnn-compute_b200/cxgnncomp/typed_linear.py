@@ -69,6 +69,11 @@ class TypedLinearE2EOP(torch.autograd.Function):
             # dW[r] = sum over the edges of relation r of x_e^T g_e. (The reference multiplies the unsorted
             # prefixes x[:count[i]] and grad[:count[i]] for every i, typed_linear.py:130-133, which is not
             # the gradient.)
+            if cxgnncomp_backend.typed_wgrad_supported(x, grad_out):
+                # one tensor-core launch over the sorted, padded positions (rows of padding positions do not exist)
+                gw = cxgnncomp_backend.typed_wgrad(x.contiguous(), grad_out.contiguous(), sorted_types, num_rel,
+                                                   ctx.num_item, idx=indices)
+                return grad_x, gw.to(weights.dtype), None, None, None, None
             grad_w = torch.zeros_like(weights)
             order = torch.sort(types, stable=True).indices
             cnt = torch.bincount(types, minlength=num_rel).tolist()

@@ -1118,7 +1118,7 @@ ALLOW_TF32 = os.environ.get("CXG_ALLOW_TF32", "0") == "1"
 from ._rgcn import (pad_rel, pad_rel_idx, typed_linear, typed_linear_s2e, typed_linear_s2d,  # noqa: E402,F401
                     aggr_rgcn_direct_func, rel_schedule, typed_matmul_raw, topo_sort, aggr_rel_direct,
                     typed_matmul_all_relations, typed_matmul_all_relations_supported, transform_all_relations,
-                    dense_linear)
+                    dense_linear, typed_wgrad, typed_wgrad_supported)
 
 # pybind's export_values(): the enum members are module attributes too
 SUM, MAX, MIN, MEAN = REDUCEOP.SUM, REDUCEOP.MAX, REDUCEOP.MIN, REDUCEOP.MEAN

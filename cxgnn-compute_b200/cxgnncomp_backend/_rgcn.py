@@ -215,6 +215,59 @@ def typed_matmul_raw(a, b, rel, m_positions, m_valid, src_idx=None, dst_idx=None
     return c
 
 
+_wg_ws = _sig("cxg_typed_wgrad_workspace_size", [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_sz)])
+_wg = _sig("cxg_typed_wgrad", [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                               ctypes.c_int, ctypes.c_int, ctypes.c_uint32, _vp, _vp, _sz, _vp])
+_wg_status = _sig("cxg_typed_wgrad_status", [_vp, _vp])
+
+
+def typed_wgrad_supported(x, g, allow_tf32=None):
+    """Shapes cxg_typed_wgrad covers: same fp32 / bf16 dtype, 128 input columns, output rows a multiple of 128 bytes,
+    one stage (both tiles, twice for the error-compensated fp32 mode) within shared memory."""
+    if not (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and g.dtype == x.dtype and x.dim() == 2
+            and g.dim() == 2 and x.shape[1] == 128 and (g.shape[1] * g.element_size()) % 128 == 0
+            and g.shape[1] % 16 == 0 and g.shape[1] <= 256):
+        return False
+    if allow_tf32 is None:
+        allow_tf32 = sys.modules[__package__].ALLOW_TF32
+    split = 2 if (x.dtype == torch.float32 and not allow_tf32) else 1
+    return (128 + g.shape[1]) * x.element_size() * 128 * split <= 224 * 1024
+
+
+def typed_wgrad(x, g, sorted_rel, num_rel, num_valid=None, idx=None, idx_g=None, allow_tf32=None, extra_flags=0,
+                check_status=False):
+    """dW [num_rel, K, N] (float32) = per relation, the sum over its positions of x[row]^T g[row_g]; positions are the
+    sorted, padded ones of TypedLinearE2EOP.preprocess (`sorted_rel` int64 per position, `idx` the row of x per
+    position, `idx_g` the row of g (default: the same row); a position whose row is negative or not below num_valid
+    (default: the tensors' row counts) is padding). One tensor-core launch (cxg_typed_wgrad) instead of a torch.mm
+    per relation (cxgnncomp/typed_linear.py:115-137)."""
+    _cuda(x, "x", (torch.float32, torch.bfloat16))
+    _cuda(g, "g", (x.dtype,))
+    _cuda(sorted_rel, "sorted_rel", (torch.int64,))
+    if idx is not None:
+        _cuda(idx, "idx", (torch.int64,))
+    if idx_g is not None:
+        _cuda(idx_g, "idx_g", (torch.int64,))
+    m = sorted_rel.shape[0]
+    k, n = x.shape[1], g.shape[1]
+    x_rows = min(x.shape[0], int(num_valid)) if num_valid is not None else x.shape[0]
+    g_rows = min(g.shape[0], int(num_valid)) if (num_valid is not None and idx_g is None) else g.shape[0]
+    dw = torch.empty((num_rel, k, n), dtype=torch.float32, device=x.device)
+    dtype = CXG_F32 if x.dtype == torch.float32 else CXG_BF16
+    if allow_tf32 is None:
+        allow_tf32 = sys.modules[__package__].ALLOW_TF32
+    precision = 1 if (allow_tf32 or dtype == CXG_BF16) else 2
+    need = _sz(0)
+    _check(_wg_ws(num_rel, k, n, ctypes.byref(need)), "cxg_typed_wgrad_workspace_size")
+    ws = _workspace(x.device, need.value, "typed_wgrad")
+    with torch.cuda.device(x.device):
+        _check(_wg(_p(x), _p(g), _p(sorted_rel), _p(idx), _p(idx_g), m, x_rows, g_rows, k, n, num_rel, dtype, precision,
+                   int(extra_flags), _p(dw), _p(ws), ws.numel(), _stream()), "cxg_typed_wgrad")
+        if check_status:  # synchronises; raises when a bounded device-side wait ran out
+            _check(_wg_status(_p(ws), _stream()), "cxg_typed_wgrad_status")
+    return dw
+
+
 def typed_matmul_all_relations(x, w, allow_tf32=None, extra_flags=0):
     """[R, N, out] = x [N, K] multiplied by every relation's weight w [R, K, out] in one launch of the tensor-core
     kernel (cxg_typed_matmul with CXG_TMM_ALL_RELATIONS): the first half of TypedLinearS2DMMAggrOP

@@ -132,6 +132,28 @@ int cxg_spmm_csr_status(const void *workspace, void *stream);
 int cxg_typed_matmul_status(const void *workspace, void *stream);
 
 /*
+ * Weight gradient of the typed linear: dW[r] = sum over the positions m with rel[m] == r of x[ix(m), :]^T g[ig(m), :],
+ * dW float32 [num_rel, k, n]. Positions are those of cxg_typed_matmul (sorted by relation, every aligned block of 128
+ * one relation); ix(m) = idx[m] (NULL: m), ig(m) = idx_g[m] (NULL: ix(m)); a position counts only when ix(m) is in
+ * [0, x_rows) and ig(m) in [0, g_rows). Replaces the per-relation loop of torch.mm over row sets in
+ * TypedLinearE2EOP.backward (cxgnncomp/typed_linear.py:115-137) by one launch on the tensor cores (a contraction
+ * over positions, both operands MN-major) plus a fixed-order reduction of per-CTA partial sums: no atomics. An
+ * accumulator in tensor memory takes a few thousand positions at most and the partial sums are added in ordinary
+ * fp32, so the error does not grow with the number of rows. precision 1 = plain bf16 / TF32 products, 2 =
+ * error-compensated TF32 for fp32 inputs (1e-5 class). Shapes: k == 128, n * element size a multiple of 128 bytes,
+ * n <= 256, one stage within shared memory (CXG_EUNSUPPORTED otherwise). cxg_typed_wgrad_status reads back whether a
+ * bounded wait ran out.
+ */
+int cxg_typed_wgrad_workspace_size(int num_rel, int k, int n, size_t *bytes);
+/* Test hook: the first tile of every CTA is never handed to the tensor-core role, so the bounded waits for it run out
+   (status CXG_ETIMEOUT, all roles leave, tensor memory is released). Use it with a short cxg_set_wait_limit_cycles. */
+#define CXG_WGRAD_TEST_STALL 1u
+int cxg_typed_wgrad(const void *x, const void *g, const int64_t *rel, const int64_t *idx, const int64_t *idx_g,
+                    int64_t m, int64_t x_rows, int64_t g_rows, int k, int n, int num_rel, int dtype, int precision,
+                    uint32_t flags, float *dw, void *workspace, size_t workspace_bytes, void *stream);
+int cxg_typed_wgrad_status(const void *workspace, void *stream);
+
+/*
  * Scratch bytes needed by cxg_spmm_csr for a graph with n_dst rows and nnz
  * edges at row width heads*feat (split_edges as in the descriptor). Upper bound;
  * depends on sizes only.

@@ -266,3 +266,74 @@ def test_dense_linear(cuda, dtype, tol, n, k, out):
     y.backward(go.cuda().to(dtype))
     want.backward(go.to(dtype).double())
     assert rel_err(xg.grad.float().cpu(), xr.grad) < tol and rel_err(wg.grad.float().cpu(), wr.grad) < max(tol, 2e-5)
+
+
+@pytest.mark.parametrize("dtype,n,tol,tf32", [(torch.bfloat16, 64, 1e-2, False), (torch.float32, 64, 2e-3, True),
+                                              (torch.float32, 64, 1e-5, False), (torch.float32, 32, 1e-5, False),
+                                              (torch.bfloat16, 128, 1e-2, False), (torch.float32, 256, 2e-3, True)])
+@pytest.mark.parametrize("E,R", [(3000, 5), (100, 3), (40000, 8)])
+def test_typed_wgrad(cuda, dtype, n, tol, tf32, E, R):
+    """dW[r] = sum over the rows of relation r of x_e^T g_e on the tensor cores, against float64; an empty relation
+    gives zeros; two runs give the same bits."""
+    import cxgnncomp_backend as be
+    k = 128
+    g_ = torch.Generator().manual_seed(E + n)
+    types = torch.randint(0, R, (E,), generator=g_)
+    types[types == 1] = 0  # relation 1 has no rows
+    x, go = randn((E, k), 41).to(dtype), randn((E, n), 42).to(dtype)
+    _, sorted_types, indices, _ = _preprocess(types.cuda(), R, 128)
+    assert be.typed_wgrad_supported(x.cuda(), go.cuda(), allow_tf32=tf32)
+    dw = be.typed_wgrad(x.cuda(), go.cuda(), sorted_types, R, E, idx=indices, allow_tf32=tf32)
+    want = torch.zeros(R, k, n, dtype=torch.float64)
+    for r in range(R):
+        sel = types == r
+        want[r] = x[sel].double().t() @ go[sel].double()
+    assert dw.shape == (R, k, n) and dw.dtype == torch.float32
+    scale = want.abs().max()
+    assert float((dw.cpu().double() - want).abs().max() / scale) < tol
+    assert bool((dw[1] == 0).all())
+    assert torch.equal(dw, be.typed_wgrad(x.cuda(), go.cuda(), sorted_types, R, E, idx=indices, allow_tf32=tf32))
+    # the gradient rows through an index of their own (the fused RGCN backward reads x by source and the gradient by
+    # destination; -1 marks a padding position): the same sums from a shuffled copy of the gradient matrix
+    perm = torch.randperm(E, generator=g_)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(E)
+    ok = indices.cpu() < E
+    ix = torch.where(ok, indices.cpu(), torch.full_like(indices.cpu(), -1))
+    ig = torch.where(ok, inv[indices.cpu().clamp(max=E - 1)], torch.full_like(ix, -1))
+    dw2 = be.typed_wgrad(x.cuda(), go[perm].contiguous().cuda(), sorted_types, R, idx=ix.cuda(), idx_g=ig.cuda(),
+                         allow_tf32=tf32)
+    assert torch.equal(dw, dw2)
+
+
+def test_typed_wgrad_long_contraction(cuda):
+    """Two million rows of one relation: the tensor core's accumulator is handed over every few tiles, so the error
+    stays at fp32 level however long the sum is (it grows linearly with the length inside one accumulator)."""
+    import cxgnncomp_backend as be
+    E = 1 << 21
+    x, go = randn((E, 128), 51).cuda(), randn((E, 64), 52).cuda()
+    st = torch.zeros(E, dtype=torch.int64, device="cuda")
+    want = x.double().t() @ go.double()
+    dw = be.typed_wgrad(x, go, st, 1, E, allow_tf32=False)[0]
+    assert float((dw.double() - want).abs().max() / want.abs().max()) < 1e-5
+    plain = be.typed_wgrad(x, go, st, 1, E, allow_tf32=True)[0]
+    assert float((plain.double() - want).abs().max() / want.abs().max()) < 2e-3
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_typed_linear_backward_uses_wgrad_kernel(cuda, dtype, tol):
+    """TypedLinearE2EOP with 128 input columns: both gradients through the tensor-core kernels, against float64."""
+    import cxgnncomp
+    E, R, K, N = 5000, 4, 128, 64
+    g_ = torch.Generator().manual_seed(3)
+    types = torch.randint(0, R, (E,), generator=g_)
+    x, w = randn((E, K), 61).to(dtype), (randn((R, K, N), 62) * 0.2).to(dtype)
+    xg, wg = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    out = cxgnncomp.TypedLinearE2EOP.apply(xg, wg, types.cuda())
+    go = randn((E, N), 63).to(dtype)
+    out.backward(go.cuda())
+    xr, wr = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    ref = torch.bmm(xr.unsqueeze(1), wr[types]).squeeze(1)
+    ref.backward(go.double())
+    assert rel_err(out.detach().float().cpu(), ref.detach()) < tol
+    assert rel_err(xg.grad.float().cpu(), xr.grad) < tol and rel_err(wg.grad.float().cpu(), wr.grad) < tol

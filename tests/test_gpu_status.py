@@ -146,3 +146,22 @@ def test_status_answers_only_for_the_last_kind(cuda):
     out = torch.zeros(600, 64, device="cuda")
     be.selective_aggr(x.cuda(), ptr.cuda(), idx.cuda(), mask.cuda(), out, 600)
     be.check_device_status("spmm")
+
+
+def test_typed_wgrad_bounded_wait_runs_out(cuda):
+    """The weight-gradient kernel: the producers never hand over their first tile; the roles give up after the limit,
+    the status says so, and the next call is right."""
+    import cxgnncomp_backend as be
+    E = 4096
+    st = torch.zeros(E, dtype=torch.int64, device="cuda")
+    for dtype in (torch.bfloat16, torch.float32):
+        x, g = randn((E, 128), 97).to(dtype).cuda(), randn((E, 64), 98).to(dtype).cuda()
+        be.set_wait_limit_cycles(200_000)
+        try:
+            with pytest.raises(RuntimeError, match="wait ran out"):
+                be.typed_wgrad(x, g, st, 1, E, extra_flags=1, check_status=True)
+        finally:
+            be.set_wait_limit_cycles(0)
+        dw = be.typed_wgrad(x, g, st, 1, E, check_status=True)[0]
+        want = x.double().t() @ g.double()
+        assert rel_err(dw.cpu(), want.cpu()) < (1e-5 if dtype == torch.float32 else 1e-2)
