@@ -231,7 +231,8 @@ def typed_wgrad_supported(x, g, allow_tf32=None):
     if allow_tf32 is None:
         allow_tf32 = sys.modules[__package__].ALLOW_TF32
     split = 2 if (x.dtype == torch.float32 and not allow_tf32) else 1
-    return (128 + g.shape[1]) * x.element_size() * 128 * split <= 224 * 1024
+    positions = 64 if split == 2 else 128  # per tile, as the kernel chooses them
+    return (128 + g.shape[1]) * x.element_size() * positions * split <= 224 * 1024
 
 
 def typed_wgrad(x, g, sorted_rel, num_rel, num_valid=None, idx=None, idx_g=None, allow_tf32=None, extra_flags=0,
@@ -336,11 +337,24 @@ def transform_all_relations(x, w):
     return _TransformAllFunction.apply(x, w)
 
 
+_one_rel_cache = {}
+
+
+def _one_relation(n, device):
+    """int64 zeros [n]: the position array of a weight gradient whose rows all belong to one relation (kept and
+    re-sliced, it never changes)."""
+    key = str(device)
+    t = _one_rel_cache.get(key)
+    if t is None or t.shape[0] < n:
+        t = _one_rel_cache[key] = torch.zeros(max(n, 1 << 16), dtype=torch.int64, device=device)
+    return t[:n]
+
+
 class _DenseLinearFunction(torch.autograd.Function):
     """y = x @ weight^T (weight [out, in], torch.nn.functional.linear without bias) on the tensor-core kernel in its
     dense mode with one relation: fp32 inputs keep fp32 accuracy (error-compensated TF32), where the library GEMM
     torch would call runs on the fp32 SIMT pipe. dx = g @ weight goes the same way; dW = g^T @ x, a reduction over
-    the rows, stays with torch."""
+    the rows, is the weight-gradient kernel with a single relation when the layer has 128 outputs, else torch."""
 
     @staticmethod
     def forward(ctx, x, weight):
@@ -359,7 +373,10 @@ class _DenseLinearFunction(torch.autograd.Function):
             else:
                 dx = g @ weight
         if ctx.needs_input_grad[1]:
-            dw = g.t() @ x
+            if typed_wgrad_supported(g, x):  # out == 128: one relation holding every row
+                dw = typed_wgrad(g, x, _one_relation(x.shape[0], x.device), 1)[0].to(weight.dtype)
+            else:
+                dw = g.t() @ x
         return dx, dw
 
 

@@ -251,7 +251,7 @@ def test_status_words_clear_after_normal_calls(cuda):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("n,k,out", [(3000, 128, 128), (130, 64, 32), (1, 32, 16), (777, 100, 47)])
+@pytest.mark.parametrize("n,k,out", [(3000, 128, 128), (130, 64, 32), (1, 32, 16), (777, 100, 47), (500, 64, 128)])
 def test_dense_linear(cuda, dtype, tol, n, k, out):
     """x @ weight^T on the tensor-core kernel (dense mode, one relation), forward and both gradients against float64;
     shapes the kernel does not cover (in = 100, out = 47) fall through to torch."""
