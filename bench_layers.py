@@ -392,6 +392,10 @@ def config4(steps, flush, scale=1.0, cpu=True, quick=False):
             t_mm = gpu_ms(lambda: be.typed_matmul_raw(xe, conv.linear.data, st, st.shape[0], nnz, src_idx=indices),
                           steps, flush)
             y = conv(x, ptr, idx, rel_t, n)
+            # weight gradient of the per-edge typed linear (one launch; the reference loops torch.mm over the relations)
+            ge = torch.randn(nnz, 64, device=dev).to(dtype)
+            t_wg = gpu_ms(lambda: be.typed_wgrad(xe, ge, st, 8, nnz, idx=indices), steps, flush)
+            del ge
         elem = 2 if dtype == torch.bfloat16 else 4
         flops = 2.0 * nnz * 128 * 64
         b_mm = nnz * (128 + 64) * elem + 8 * 128 * 64 * elem + nnz * 9
@@ -411,6 +415,8 @@ def config4(steps, flush, scale=1.0, cpu=True, quick=False):
                      "typed_matmul_ms": t_mm, "typed_matmul_tflops": flops / t_mm / 1e9,
                      "typed_matmul_frac_tensor_peak": flops / t_mm / 1e9 / tens,
                      "typed_matmul_b_alg_GBps": b_mm / t_mm / 1e6, "typed_matmul_frac_hbm_peak": b_mm / t_mm / 1e6 / hbm,
+                     "typed_wgrad_ms": t_wg, "typed_wgrad_b_alg_GBps": nnz * (128 + 64) * elem / t_wg / 1e6,
+                     "typed_wgrad_frac_hbm_peak": nnz * (128 + 64) * elem / t_wg / 1e6 / hbm,
                      "max_rel_err_sampled_rows": max(errs)}
         del conv, x, xe, y
         torch.cuda.empty_cache()
