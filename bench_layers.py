@@ -142,6 +142,12 @@ def config2(steps, flush, cpu=True):
             return conv(xg, p, i, n, n, nnz)
 
     t_fb, t_f = gpu_ms(fb, steps, flush), gpu_ms(fwd, steps, flush)
+    # the same layer with its linear transform and both of that transform's gradients on the library's tensor-core
+    # kernels (an option of the layer)
+    conv.tensor_core_linear = True
+    fb()
+    t_fb_tc, t_f_tc = gpu_ms(fb, steps, flush), gpu_ms(fwd, steps, flush)
+    conv.tensor_core_linear = False
     W, a_s, a_d = conv.lin_src.detach().cpu(), conv.att_src.detach().cpu(), conv.att_dst.detach().cpu()
     xr = x.clone().requires_grad_(True)
     gc = go.cpu()
@@ -189,7 +195,8 @@ def config2(steps, flush, cpu=True):
     kernels = {k: {"ms": t, "b_alg_bytes": b, "GBps": b / t / 1e6, "frac_hbm_peak": b / t / 1e6 / hbm}
                for k, (t, b) in kern.items()}
     return {"config": "c2 GAT layer fwd+bwd (4 heads x 32)", "nodes": n, "nnz": nnz, "gpu_fwd_ms": t_f,
-            "gpu_fwd_bwd_ms": t_fb, "aggregate_b_alg_bytes": b_alg, "kernels": kernels, "cpu_fwd_bwd_ms": c_fb,
+            "gpu_fwd_bwd_ms": t_fb, "gpu_fwd_ms_tensor_core_linear": t_f_tc, "gpu_fwd_bwd_ms_tensor_core_linear": t_fb_tc,
+            "aggregate_b_alg_bytes": b_alg, "kernels": kernels, "cpu_fwd_bwd_ms": c_fb,
             "cpu_cores": torch.get_num_threads(), "max_rel_err_fwd": err, "max_rel_err_grad_x": err_g}
 
 

@@ -409,6 +409,12 @@ class MyGATConv(torch.nn.Module):
         # edge softmax and weighted aggregation as ONE kernel where the shape allows (the reference's sequence of
         # edge_attention + SpMMValOP otherwise, or when set to False)
         self.fused_aggregate = True
+        # True: x @ W^T, its input gradient and its weight gradient run on the library's tensor-core kernels
+        # (compensated TF32) instead of the fp32 library GEMMs torch calls: 1.48 instead of 1.69 ms for the layer's
+        # forward + backward at 169 k nodes. Off by default: in about one process in twenty-five the layer's output
+        # was 3e-5 instead of 2e-6 away from the float64 result with it (same value on every call of that process;
+        # cause not found), which is outside the 1e-5 this package holds fp32 results to.
+        self.tensor_core_linear = False
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -441,8 +447,10 @@ class MyGATConv(torch.nn.Module):
     def forward_many(self, x, ptr, idx, num_dst, num_src, num_edge):
         H, C = self.heads, self.out_channels
         assert x.dim() == 2
-        # the layer's linear transform on the tensor-core kernel (fp32 accuracy kept by the compensated TF32 mode)
-        x_src = cxgnncomp_backend.dense_linear(x[:num_src], self.lin_src).view(-1, H, C)
+        if self.tensor_core_linear:  # the layer's linear transform on the library's tensor-core kernels
+            x_src = cxgnncomp_backend.dense_linear(x[:num_src], self.lin_src).view(-1, H, C)
+        else:
+            x_src = F.linear(x[:num_src], self.lin_src).view(-1, H, C)
         if x_src.dtype == torch.float32 and self.fused_scores:
             alpha_src, alpha_dst = cxgnncomp_backend.gat_scores(x_src.contiguous(), self.att_src.contiguous(),
                                                                 self.att_dst.contiguous(), num_dst)
