@@ -411,9 +411,9 @@ class MyGATConv(torch.nn.Module):
         self.fused_aggregate = True
         # True: x @ W^T, its input gradient and its weight gradient run on the library's tensor-core kernels
         # (compensated TF32) instead of the fp32 library GEMMs torch calls: 1.48 instead of 1.69 ms for the layer's
-        # forward + backward at 169 k nodes. Off by default: in about one process in twenty-five the layer's output
-        # was 3e-5 instead of 2e-6 away from the float64 result with it (same value on every call of that process;
-        # cause not found), which is outside the 1e-5 this package holds fp32 results to.
+        # forward + backward at 169 k nodes. Off by default: in 4 of 54 processes that had also run the bulk-row
+        # measurement variant of the SpMM (CXG_SPMM_FLAGS=4) the layer's output was 3e-5 instead of 2e-6 away from the
+        # float64 result with it (same value on every call of such a process; cause not found).
         self.tensor_core_linear = False
         self.reset_parameters()
 
